@@ -1,0 +1,85 @@
+"""ctypes binding of ``libcrownest_b200.so`` (the C ABI declared in ``include/crownest_ops.h``).
+
+There is no fallback: when the shared library is missing or a call returns a non-zero status the
+caller gets an exception. ``build()`` compiles the library in tree with nvcc for sm_100a.
+"""
+import ctypes as C
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "libcrownest_b200.so")
+CSRC = os.path.join(_HERE, "csrc")
+
+CN_F32, CN_BF16 = 0, 1
+CN_MAX_M = 8
+
+
+class CrownestError(RuntimeError):
+    pass
+
+
+def build(force=False, jobs=8):
+    """nvcc -gencode arch=compute_100a,code=sm_100a over csrc/*.cu (cross-compiles without a GPU)."""
+    cmd = ["make", "-C", CSRC, f"-j{jobs}"]
+    if force:
+        cmd.append("-B")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise CrownestError("building libcrownest_b200.so failed:\n" + r.stdout[-4000:] + r.stderr[-4000:])
+    return SO_PATH
+
+
+_lib = None
+
+_vp, _i, _f = C.c_void_p, C.c_int, C.c_float
+
+# name -> argtypes; every entry point returns int status unless listed in _RESTYPES
+_SIGS = {
+    "cn_nvfp4_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "cn_nvfp4_gemv_gu": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "cn_nvfp4_dequant": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "cn_device_status": [C.POINTER(C.c_int)],
+    "cn_set_tuning": [_i, _i],
+    "cn_last_error_string": [],
+    "cn_version": [],
+}
+_RESTYPES = {"cn_last_error_string": C.c_char_p, "cn_version": C.c_char_p, "cn_set_tuning": None}
+
+
+def exported_symbols():
+    """Names the header declares; the CPU test checks the library exports each of them."""
+    return sorted(_SIGS)
+
+
+def register(name, argtypes, restype=C.c_int):
+    """Other modules of the package add their entry points here before the first load."""
+    _SIGS[name] = argtypes
+    if restype is not C.c_int:
+        _RESTYPES[name] = restype
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise CrownestError(f"{SO_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                                "(there is no CPU or PyTorch fallback for these kernels)")
+        L = C.CDLL(SO_PATH)
+        for name, args in _SIGS.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = _RESTYPES.get(name, C.c_int)
+        _lib = L
+    return _lib
+
+
+def check(status):
+    if status != 0:
+        raise CrownestError(lib().cn_last_error_string().decode() or f"status {status}")
+
+
+def device_status():
+    code = C.c_int(0)
+    check(lib().cn_device_status(C.byref(code)))
+    return code.value

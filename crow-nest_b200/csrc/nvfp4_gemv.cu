@@ -1,0 +1,528 @@
+// NVFP4 GEMV for M = 1..8 activation rows on sm_100a: the decode projection of the dense family
+// and its small-M (speculative verify) form, plain or with the fused gate/up activation.
+//
+// Supersedes gemv_nvfp4_w / _gu / _wm / _gum (engine/src/kernels_p2.rs:355-530) and the record
+// kernels gemv_fp4(_b) (engine/src/kernels.rs:118-189), glm5_gemv_fp4 (engine/src/kernels_glm5_moe.cu:284).
+//
+// Shape of the kernel (HBM-bound; the container layout is consumed as it lies, no repack):
+//   - a CTA owns ROWS output rows over the whole K. A producer warp streams the rows' bytes
+//     through a ring of shared-memory stages with 1-D bulk copies (TMA, completion counted on an
+//     mbarrier), one piece of TX 36-byte blocks per row and stage; it never waits for anything
+//     but a free stage, so the weight stream runs ahead of the arithmetic;
+//   - a second helper warp stages the matching slice of the M activation rows, converted once
+//     per CTA: bf16 -> f16 with a power-of-two scale per 64-value block (exact; the inverse is
+//     applied with the block's partial sum), or f32 kept as f32;
+//   - consumer warps: lane (ry, tx) owns k-block tx of the stage for RT rows; the nine words of a
+//     block are read with conflict-free 4-byte loads (36-byte stride), codes are decoded in
+//     registers (cvt.rn.f16x2.e2m1x2: every E2M1 value is exact in f16) and multiplied with
+//     fma.rn.f32.f16 (f16 x f16 product exact, f32 accumulate; measured at the FFMA rate on
+//     B200), each 16-value sub-block's partial sum is multiplied by its UE4M3 scale * tensor
+//     scale (a 256-entry table, the reference's scale_lut) and accumulated in f32; the K split
+//     over the TX lanes is reduced with xor shuffles in a fixed order.
+// Each (row, m) pair runs the same instruction sequence whatever M is, so row m of an M-row call
+// is bit-identical to a one-row call (the batch invariance of engine/src/kernels_p2.rs:391-396).
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int NW = 4;  // consumer warps
+constexpr int NTHREADS = (NW + 2) * 32;
+constexpr int MAX_STAGES = 8;
+constexpr int XB_F16 = 144;  // bytes of one k-block's 64 activations as f16, padded: conflict-free 16-byte loads
+constexpr int XB_F32 = 272;  // the same as f32
+constexpr int HDR_BYTES = 128 + 2048;  // barriers, two scale tables
+
+struct GemvParams {
+    const uint8_t* w0;  // plain: the matrix; gate/up: gate
+    const uint8_t* w1;  // gate/up: up (else null)
+    const float* gs0;
+    const float* gs1;
+    const void* x;
+    void* y;
+    int rows;  // output rows (gate/up: inter)
+    int k;
+    int m;  // live activation rows (<= MP)
+    int ldy;
+    float limit;
+    int tx;      // lanes across K per row: 16, 8 or 4
+    int stages;  // ring depth
+};
+
+__device__ __forceinline__ float act_gu(float g, float u, float limit) {
+    if (limit > 0.0f) {
+        g = g > limit ? limit : g;
+        u = u > limit ? limit : (u < -limit ? -limit : u);
+    }
+    return (g / (1.0f + expf(-g))) * u;
+}
+
+// one load group of eight activation values: raw words in flight, widened exactly to f32 on use
+template <int XT>
+struct XRaw {
+    uint4 a;
+    uint4 b;  // f32 input only
+};
+template <int XT>
+__device__ __forceinline__ void load_x8(const void* x, size_t at, XRaw<XT>& r) {
+    if (XT == 1) {
+        r.a = *(const uint4*)((const __nv_bfloat16*)x + at);
+    } else {
+        r.a = *(const uint4*)((const float*)x + at);
+        r.b = *(const uint4*)((const float*)x + at + 4);
+    }
+}
+template <int XT>
+__device__ __forceinline__ void widen_x8(const XRaw<XT>& r, float v[8]) {
+    if (XT == 1) {
+        const uint32_t u[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v[2 * i] = __uint_as_float(u[i] << 16);
+            v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    } else {
+        v[0] = __uint_as_float(r.a.x), v[1] = __uint_as_float(r.a.y), v[2] = __uint_as_float(r.a.z), v[3] = __uint_as_float(r.a.w);
+        v[4] = __uint_as_float(r.b.x), v[5] = __uint_as_float(r.b.y), v[6] = __uint_as_float(r.b.z), v[7] = __uint_as_float(r.b.w);
+    }
+}
+
+// XT: 0 = f32 activations/outputs, 1 = bf16. MP: activation rows compiled in (1, 2, 4, 8).
+// RT: rows per consumer thread. MODE: 0 = f32 FMA, 1 = f16 x f16 + f32 mixed FMA (bf16 input only).
+template <int XT, int MP, int RT, int MODE>
+__global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int XB = MODE == 1 ? XB_F16 : XB_F32;
+    const int TX = p.tx;
+    const int G = NW * (32 / TX);  // row groups per CTA
+    const int ROWS = G * RT;       // row slots per stage
+    const int piece = TX * 36;     // bytes of one row's share of a stage
+    const int bpr = p.k >> 6;
+    const size_t row_bytes = (size_t)bpr * 36;
+    const int nchunks = bpr / TX;
+    const bool gu = p.w1 != nullptr;
+    const int S = p.stages;
+
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = full + MAX_STAGES;
+    float* lut = (float*)(smem + 128);  // [2][256]
+    uint8_t* stage0 = smem + HDR_BYTES;
+    const int wbytes = ROWS * piece;
+    const int xbytes = MP * TX * XB;
+    const int stage_bytes = wbytes + xbytes + MP * TX * 4;  // weights, activations, per-block inverse scales
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // output rows of this CTA: plain ROWS consecutive rows; gate/up ROWS/2 consecutive indices
+    const int per_cta = gu ? ROWS / 2 : ROWS;
+    const int row0 = blockIdx.x * per_cta;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 33);  // the producer's expect_tx arrive + the 32 lanes of the activation warp
+            mbar_init(&empty[s], NW);
+        }
+        mbar_fence_init();
+    }
+    // scale tables: ue4m3(rule(byte)) * gs, the product the reference tabulates (cpu_nvfp4.rs:98)
+    {
+        const float g0 = p.gs0[0], g1 = gu ? p.gs1[0] : g0;
+        for (int b = tid; b < 256; b += NTHREADS) {
+            const float u = ue4m3_f32((uint32_t)b, true);
+            lut[b] = u * g0;
+            lut[256 + b] = u * g1;
+        }
+    }
+    __syncthreads();
+    // let the next kernel of the stream begin its own weight prefetch while this one drains
+    pdl_launch_dependents();
+
+    if (warp == NW) {
+        // ------------------------------------------------------------ weight producer warp
+        // source row of slot sl = j*G + g: plain row0 + sl; gate/up: matrix j & 1, index row0 + (j>>1)*G + g
+        const uint64_t pol = l2_policy_evict_first();
+        const uint8_t* src[4];
+        uint32_t total = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int sl = lane + 32 * i;
+            src[i] = nullptr;
+            if (sl < ROWS) {
+                const int j = sl / G, g = sl % G;
+                const int r = gu ? row0 + (j >> 1) * G + g : row0 + sl;
+                const uint8_t* base = (gu && (j & 1)) ? p.w1 : p.w0;
+                if (r < p.rows) src[i] = base + (size_t)r * row_bytes;
+            }
+            total += src[i] ? piece : 0;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        for (int c = 0; c < nchunks; c++) {
+            const int s = c % S;
+            if (c >= S && !mbar_wait(&empty[s], ((c / S) - 1) & 1)) {
+                cn_dev_fail(CN_DEV_WAIT_EMPTY);
+                return;
+            }
+            uint8_t* st = stage0 + (size_t)s * stage_bytes;
+            if (lane == 0) {
+                mbar_expect_tx(&full[s], total);
+                mbar_arrive(&full[s]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (src[i]) bulk_g2s_stream(st + (size_t)(lane + 32 * i) * piece, src[i] + (size_t)c * piece, piece, &full[s], pol);
+        }
+        return;
+    }
+
+    if (warp == NW + 1) {
+        // ------------------------------------------------------------ activation staging warp
+        // Per stage: the slice x[m][c*TX*64 .. +TX*64] of every activation row, in groups of 8
+        // values (lane & 7 = position in the 64-value block, so the 8 lanes of a block sit side by
+        // side). All loads of a batch are issued before the first conversion.
+        pdl_wait();  // activations may come from the previous kernel of the stream
+        constexpr int BATCH = XT == 1 ? 8 : 4;
+        const int per_lane = MP * TX / 4;  // groups per lane and stage
+        for (int c = 0; c < nchunks; c++) {
+            const int s = c % S;
+            if (c >= S && !mbar_wait(&empty[s], ((c / S) - 1) & 1)) {
+                cn_dev_fail(CN_DEV_WAIT_EMPTY);
+                return;
+            }
+            uint8_t* xs = stage0 + (size_t)s * stage_bytes + wbytes;
+            float* xinv = (float*)(xs + xbytes);
+            for (int i0 = 0; i0 < per_lane; i0 += BATCH) {
+                XRaw<XT> raw[BATCH];
+#pragma unroll
+                for (int b = 0; b < BATCH; b++) {
+                    const int g = lane + 32 * (i0 + b);
+                    const int m = g / (8 * TX), gi = g % (8 * TX);
+                    raw[b].a = make_uint4(0, 0, 0, 0);
+                    raw[b].b = make_uint4(0, 0, 0, 0);
+                    if (i0 + b < per_lane && m < p.m)
+                        load_x8<XT>(p.x, (size_t)m * p.k + ((size_t)c * TX + (gi >> 3)) * 64 + (gi & 7) * 8, raw[b]);
+                }
+#pragma unroll
+                for (int b = 0; b < BATCH; b++) {
+                    const int g = lane + 32 * (i0 + b);
+                    const int m = g / (8 * TX), gi = g % (8 * TX), kb = gi >> 3, wi = gi & 7;
+                    const bool live = i0 + b < per_lane;  // warp-uniform
+                    uint8_t* dst = xs + (size_t)(m * TX + kb) * XB;
+                    float vv[8];
+                    widen_x8<XT>(raw[b], vv);
+                    if (MODE == 1) {
+                        // power-of-two scale per 64-value block: |x| * mul < 2^15, exact in f16
+                        float amax = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(vv[i]));
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                        uint32_t e = (__float_as_uint(amax) >> 23) & 0xFF;
+                        float mul = 1.0f, inv = 1.0f;
+                        if (amax > 0.0f && e < 255) {
+                            e = e < 15 ? 15 : e;
+                            mul = __uint_as_float((268u - e) << 23);
+                            inv = __uint_as_float((e - 14u) << 23);
+                        }
+                        if (live) {
+                            uint32_t h[4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const __half2 hh = __floats2half2_rn(vv[2 * i] * mul, vv[2 * i + 1] * mul);
+                                h[i] = *(const uint32_t*)&hh;
+                            }
+                            *(uint4*)(dst + wi * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+                            if (wi == 0) xinv[m * TX + kb] = inv;
+                        }
+                    } else if (live) {
+                        *(float4*)(dst + wi * 32) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+                        *(float4*)(dst + wi * 32 + 16) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+                    }
+                }
+            }
+            mbar_arrive(&full[s]);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumer warps
+    const int txi = lane % TX, ry = lane / TX;
+    const int g = warp * (32 / TX) + ry;
+    float acc[RT][MP];
+#pragma unroll
+    for (int r = 0; r < RT; r++)
+#pragma unroll
+        for (int m = 0; m < MP; m++) acc[r][m] = 0.0f;
+
+    for (int c = 0; c < nchunks; c++) {
+        const int s = c % S;
+        if (!mbar_wait(&full[s], (c / S) & 1)) {
+            cn_dev_fail(CN_DEV_WAIT_FULL);
+            return;
+        }
+        const uint8_t* st = stage0 + (size_t)s * stage_bytes;
+        uint32_t wv[RT][9];
+#pragma unroll
+        for (int r = 0; r < RT; r++) {
+            const uint32_t* wp = (const uint32_t*)(st + (size_t)(r * G + g) * piece + txi * 36);
+#pragma unroll
+            for (int i = 0; i < 9; i++) wv[r][i] = wp[i];
+        }
+        const uint8_t* xs = st + wbytes + (size_t)txi * XB;
+        float blk[RT][MP];
+#pragma unroll
+        for (int r = 0; r < RT; r++)
+#pragma unroll
+            for (int m = 0; m < MP; m++) blk[r][m] = 0.0f;
+#pragma unroll
+        for (int sb = 0; sb < 4; sb++) {
+            if (MODE == 1) {
+                uint4 xa[MP], xb[MP];
+#pragma unroll
+                for (int m = 0; m < MP; m++) {
+                    const uint4* xp = (const uint4*)(xs + (size_t)m * TX * XB + sb * 32);
+                    xa[m] = xp[0];
+                    xb[m] = xp[1];
+                }
+#pragma unroll
+                for (int r = 0; r < RT; r++) {
+                    const float sc = lut[((gu && (r & 1)) ? 256 : 0) + ((wv[r][0] >> (8 * sb)) & 0xFF)];
+                    const uint32_t c0 = wv[r][1 + 2 * sb], c1 = wv[r][2 + 2 * sb];
+                    uint32_t h[8];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        h[i] = e2m1x2_to_f16x2((c0 >> (8 * i)) & 0xFF);
+                        h[4 + i] = e2m1x2_to_f16x2((c1 >> (8 * i)) & 0xFF);
+                    }
+#pragma unroll
+                    for (int m = 0; m < MP; m++) {
+                        const uint32_t xv[8] = {xa[m].x, xa[m].y, xa[m].z, xa[m].w, xb[m].x, xb[m].y, xb[m].z, xb[m].w};
+                        float p0 = 0.0f, p1 = 0.0f;  // even / odd values: two independent chains
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            p0 = fma_f16_f32((uint16_t)(h[i] & 0xffff), (uint16_t)(xv[i] & 0xffff), p0);
+                            p1 = fma_f16_f32((uint16_t)(h[i] >> 16), (uint16_t)(xv[i] >> 16), p1);
+                        }
+                        blk[r][m] = fmaf(p0 + p1, sc, blk[r][m]);
+                    }
+                }
+            } else {
+                float xv[MP][16];
+#pragma unroll
+                for (int m = 0; m < MP; m++) {
+                    const float4* xp = (const float4*)(xs + (size_t)m * TX * XB + sb * 64);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float4 t = xp[i];
+                        xv[m][4 * i] = t.x, xv[m][4 * i + 1] = t.y, xv[m][4 * i + 2] = t.z, xv[m][4 * i + 3] = t.w;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < RT; r++) {
+                    const float sc = lut[((gu && (r & 1)) ? 256 : 0) + ((wv[r][0] >> (8 * sb)) & 0xFF)];
+                    const uint32_t c0 = wv[r][1 + 2 * sb], c1 = wv[r][2 + 2 * sb];
+                    float wf[16];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t h0 = e2m1x2_to_f16x2((c0 >> (8 * i)) & 0xFF), h1 = e2m1x2_to_f16x2((c1 >> (8 * i)) & 0xFF);
+                        wf[2 * i] = f16lo_to_f32(h0), wf[2 * i + 1] = f16hi_to_f32(h0);
+                        wf[8 + 2 * i] = f16lo_to_f32(h1), wf[8 + 2 * i + 1] = f16hi_to_f32(h1);
+                    }
+#pragma unroll
+                    for (int m = 0; m < MP; m++) {
+                        float p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            p0 = fmaf(wf[2 * i], xv[m][2 * i], p0);
+                            p1 = fmaf(wf[2 * i + 1], xv[m][2 * i + 1], p1);
+                        }
+                        blk[r][m] = fmaf(p0 + p1, sc, blk[r][m]);
+                    }
+                }
+            }
+        }
+        if (MODE == 1) {
+            const float* xinv = (const float*)(st + wbytes + xbytes);
+#pragma unroll
+            for (int m = 0; m < MP; m++) {
+                const float inv = xinv[m * TX + txi];
+#pragma unroll
+                for (int r = 0; r < RT; r++) acc[r][m] = fmaf(blk[r][m], inv, acc[r][m]);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < RT; r++)
+#pragma unroll
+                for (int m = 0; m < MP; m++) acc[r][m] += blk[r][m];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+
+    // K split over the TX lanes: xor-shuffle tree, fixed order
+#pragma unroll
+    for (int r = 0; r < RT; r++)
+#pragma unroll
+        for (int m = 0; m < MP; m++) {
+            float v = acc[r][m];
+            for (int o = TX >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            acc[r][m] = v;
+        }
+    if (txi == 0) {
+        if (!gu) {
+#pragma unroll
+            for (int r = 0; r < RT; r++) {
+                const int row = row0 + r * G + g;
+                if (row < p.rows) {
+#pragma unroll
+                    for (int m = 0; m < MP; m++)
+                        if (m < p.m) {
+                            if (XT == 1)
+                                ((__nv_bfloat16*)p.y)[(size_t)m * p.ldy + row] = __float2bfloat16_rn(acc[r][m]);
+                            else
+                                ((float*)p.y)[(size_t)m * p.ldy + row] = acc[r][m];
+                        }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r + 1 < RT; r += 2) {
+                const int row = row0 + (r >> 1) * G + g;
+                if (row < p.rows) {
+#pragma unroll
+                    for (int m = 0; m < MP; m++)
+                        if (m < p.m) {
+                            const float h = act_gu(acc[r][m], acc[r + 1][m], p.limit);
+                            if (XT == 1)
+                                ((__nv_bfloat16*)p.y)[(size_t)m * p.ldy + row] = __float2bfloat16_rn(h);
+                            else
+                                ((float*)p.y)[(size_t)m * p.ldy + row] = h;
+                        }
+                }
+            }
+        }
+    }
+}
+
+// out[r][c] = e2m1(code) * (ue4m3(byte) * gs): one thread per 8 values (one code word)
+__global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ w, const float* __restrict__ gs, float* __restrict__ out,
+                                     long long nwords, int rule) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nwords) return;
+    const long long blk = i >> 3;
+    const int wi = (int)(i & 7);
+    const uint8_t* b = w + blk * 36;
+    const float s = ue4m3_f32(b[wi >> 1], rule != 0) * gs[0];
+    const uint32_t cw = *(const uint32_t*)(b + 4 + 4 * wi);
+    float* o = out + blk * 64 + wi * 8;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t h = e2m1x2_to_f16x2((cw >> (8 * j)) & 0xFF);
+        o[2 * j] = f16lo_to_f32(h) * s;
+        o[2 * j + 1] = f16hi_to_f32(h) * s;
+    }
+}
+
+int g_tune_mode = 0, g_tune_rt = 0, g_tune_stages = 0, g_tune_pdl = 1;
+
+template <int XT, int MP, int RT, int MODE>
+int launch_one(const GemvParams& p, int grid, size_t smem, cudaStream_t stream) {
+    static bool attr_done = false;
+    auto kern = nvfp4_gemv_kernel<XT, MP, RT, MODE>;
+    if (!attr_done) {
+        CN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = g_tune_pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    CN_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    return CN_OK;
+}
+
+template <int XT, int MODE>
+int launch_m(const GemvParams& p, int mp, int rt, int grid, size_t smem, cudaStream_t stream) {
+#define CN_CASE(MPV, RTV) \
+    if (mp == MPV && rt == RTV) return launch_one<XT, MPV, RTV, MODE>(p, grid, smem, stream);
+    CN_CASE(1, 2) CN_CASE(1, 4) CN_CASE(2, 2) CN_CASE(2, 4) CN_CASE(4, 2) CN_CASE(4, 4) CN_CASE(8, 2) CN_CASE(8, 4)
+#undef CN_CASE
+    CN_FAIL(CN_ERR_SHAPE, "nvfp4 gemv: no kernel for m %d, rows per thread %d", mp, rt);
+}
+
+int gemv_common(const void* w0, const void* w1, const float* gs0, const float* gs1, const void* x, void* y, int rows, int k, int m,
+                int ldy, float limit, int dtype, cudaStream_t stream, const char* who) {
+    if (rows <= 0 || k <= 0 || k % 256 != 0) CN_FAIL(CN_ERR_SHAPE, "%s: k = %d must be a positive multiple of 256 (rows of 16-byte multiples)", who, k);
+    if (m < 1 || m > CN_MAX_M) CN_FAIL(CN_ERR_LIMIT, "%s: m = %d, the kernel takes 1..%d activation rows", who, m, CN_MAX_M);
+    if (ldy < rows) CN_FAIL(CN_ERR_SHAPE, "%s: ldy %d < rows %d", who, ldy, rows);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "%s: dtype %d is neither CN_F32 nor CN_BF16", who, dtype);
+    if (((uintptr_t)w0 & 15) || ((uintptr_t)w1 & 15) || ((uintptr_t)x & 15))
+        CN_FAIL(CN_ERR_SHAPE, "%s: weight and activation pointers must be 16-byte aligned", who);
+    const int bpr = k / 64;
+    const int tx = bpr % 16 == 0 ? 16 : (bpr % 8 == 0 ? 8 : 4);
+    const int mp = m == 1 ? 1 : (m == 2 ? 2 : (m <= 4 ? 4 : 8));
+    int mode = dtype == CN_BF16 ? 1 : 0;
+    if (g_tune_mode == 1) mode = 0;
+    if (g_tune_mode == 2 && dtype == CN_BF16) mode = 1;
+    const int G = NW * (32 / tx);
+    int rt = 4;
+    const long long slots = (long long)rows * (w1 ? 2 : 1);
+    if (slots / (G * 4) < 2 * 148) rt = 2;
+    if (g_tune_rt == 2 || g_tune_rt == 4) rt = g_tune_rt;
+    const int ROWS = G * rt;
+    const int per_cta = w1 ? ROWS / 2 : ROWS;
+    const int grid = (rows + per_cta - 1) / per_cta;
+    const int xb = mode == 1 ? XB_F16 : XB_F32;
+    const size_t stage_bytes = (size_t)ROWS * tx * 36 + (size_t)mp * tx * xb + (size_t)mp * tx * 4;
+    const int nchunks = bpr / tx;
+    int stages = (int)((64 * 1024) / stage_bytes);
+    if (g_tune_stages > 0) stages = g_tune_stages;
+    stages = stages < 2 ? 2 : (stages > MAX_STAGES ? MAX_STAGES : stages);
+    if (stages > nchunks) stages = nchunks < 1 ? 1 : nchunks;
+    const size_t smem = HDR_BYTES + stages * stage_bytes;
+    if (smem > 200 * 1024) CN_FAIL(CN_ERR_LIMIT, "%s: %zu B of shared memory per block", who, smem);
+    GemvParams p;
+    p.w0 = (const uint8_t*)w0, p.w1 = (const uint8_t*)w1, p.gs0 = gs0, p.gs1 = gs1, p.x = x, p.y = y;
+    p.rows = rows, p.k = k, p.m = m, p.ldy = ldy, p.limit = limit, p.tx = tx, p.stages = stages;
+    if (dtype == CN_BF16) return mode == 1 ? launch_m<1, 1>(p, mp, rt, grid, smem, stream) : launch_m<1, 0>(p, mp, rt, grid, smem, stream);
+    return launch_m<0, 0>(p, mp, rt, grid, smem, stream);
+}
+
+}  // namespace
+
+extern "C" int cn_nvfp4_gemv(const void* w, const float* gs, const void* x, void* y, int rows, int k, int m, int ldy, int dtype,
+                             cn_stream_t stream) {
+    return gemv_common(w, nullptr, gs, nullptr, x, y, rows, k, m, ldy, 0.0f, dtype, (cudaStream_t)stream, "cn_nvfp4_gemv");
+}
+
+extern "C" int cn_nvfp4_gemv_gu(const void* wg, const void* wu, const float* gs_g, const float* gs_u, const void* x, void* h, int inter,
+                                int k, int m, int ldh, float limit, int dtype, cn_stream_t stream) {
+    if (!wu) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_gu: the up matrix is null");
+    return gemv_common(wg, wu, gs_g, gs_u, x, h, inter, k, m, ldh, limit, dtype, (cudaStream_t)stream, "cn_nvfp4_gemv_gu");
+}
+
+extern "C" int cn_nvfp4_dequant(const void* w, const float* gs, float* out, int rows, int k, int rule, cn_stream_t stream) {
+    if (rows <= 0 || k <= 0 || k % 64 != 0) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_dequant: %d columns are not whole 64-value NVFP4 blocks", k);
+    const long long nwords = (long long)rows * (k / 64) * 8;
+    const int threads = 256;
+    const long long blocks = (nwords + threads - 1) / threads;
+    nvfp4_dequant_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>((const uint8_t*)w, gs, out, nwords, rule);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+extern "C" void cn_set_tuning(int key, int value) {
+    if (key == CN_TUNE_GEMV_MODE) g_tune_mode = value;
+    if (key == CN_TUNE_GEMV_RT) g_tune_rt = value;
+    if (key == CN_TUNE_GEMV_STAGES) g_tune_stages = value;
+    if (key == 4) g_tune_pdl = value;
+}

@@ -1,0 +1,93 @@
+"""Host-side mirror of the reference engine's NVFP4 operator interface over the C ABI.
+
+The reference's Rust host code holds ``Fp4 { w, gs }`` device buffers (engine/src/weights.rs:9-12)
+and calls ``PW::launch_gemv`` / ``Engine::dense_proj`` / ``Engine::dense_ffn_w``
+(engine/src/gen.rs:234-266, :3915, :3974), which enqueue kernels on the current stream and
+return. The classes below keep those names and argument meanings; torch is used only to own
+device memory and to name the current stream.
+"""
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import CN_BF16, CN_F32, CrownestError, check, lib
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype_code(t):
+    if t.dtype == torch.bfloat16:
+        return CN_BF16
+    if t.dtype == torch.float32:
+        return CN_F32
+    raise CrownestError(f"activations must be bf16 or f32, got {t.dtype}")
+
+
+class Fp4:
+    """One NVFP4 matrix on the device: ``w`` the container bytes [rows][k/64][36], ``gs`` a one-float
+    device buffer with the tensor scale (engine/src/weights.rs:9-12, GpuNvfp4 engine/src/glm5_moe.rs:353)."""
+
+    def __init__(self, w, gs, rows, cols):
+        if cols <= 0 or cols % 64 != 0:
+            raise CrownestError(f"cpu_nvfp4: {cols} columns are not whole 64-value NVFP4 blocks")
+        want = rows * (cols // 64) * 36
+        if w.numel() != want or w.dtype != torch.uint8:
+            raise CrownestError(f"cpu_nvfp4: [{rows}, {cols}] needs {want} B, got {w.numel()}")
+        self.w, self.gs, self.rows, self.cols = w, gs, rows, cols
+
+    @classmethod
+    def from_host(cls, bytes_, rows, cols, global_scale, device="cuda"):
+        w = torch.from_numpy(np.ascontiguousarray(bytes_, np.uint8)).to(device)
+        gs = torch.tensor([global_scale], dtype=torch.float32, device=device)
+        return cls(w, gs, rows, cols)
+
+    def rows_slice(self, r0, r1):
+        """Rows r0..r1 as a view (the tensor-parallel shard of an [out][in] matrix)."""
+        rb = self.cols // 64 * 36
+        return Fp4(self.w[r0 * rb:r1 * rb], self.gs, r1 - r0, self.cols)
+
+
+def launch_gemv(w: Fp4, x, y=None, ldy=None):
+    """y[m][r] = sum_k W[r][k] x[m][k] for x [M][k] (M <= 8) - PW::launch_gemv / launch_gemv1,
+    Engine::proj_m (engine/src/gen.rs:234-266, :5455). Enqueues and returns ``y``."""
+    x2 = x.reshape(-1, w.cols)
+    m = x2.shape[0]
+    if y is None:
+        y = torch.empty((m, w.rows), dtype=x.dtype, device=x.device)
+    ld = ldy if ldy is not None else (y.stride(0) if y.dim() == 2 else w.rows)
+    check(lib().cn_nvfp4_gemv(w.w.data_ptr(), w.gs.data_ptr(), x2.data_ptr(), y.data_ptr(), w.rows, w.cols, m, ld,
+                              _dtype_code(x), _stream()))
+    return y
+
+
+dense_proj = launch_gemv  # Engine::dense_proj (engine/src/gen.rs:3915): same operator at t == 1 and t <= 4
+
+
+def launch_gemv_gu(gate: Fp4, up: Fp4, x, h=None, limit=0.0):
+    """h = act(gate x, up x): gemv_nvfp4_gu / _gum, the first half of Engine::dense_ffn_w
+    (engine/src/gen.rs:3974-3981). limit > 0 selects the clamped SwiGLU."""
+    if (gate.rows, gate.cols) != (up.rows, up.cols):
+        raise CrownestError(f"cpu_nvfp4: expert shapes gate [{gate.rows}, {gate.cols}], up [{up.rows}, {up.cols}] do not fit together")
+    x2 = x.reshape(-1, gate.cols)
+    m = x2.shape[0]
+    if h is None:
+        h = torch.empty((m, gate.rows), dtype=x.dtype, device=x.device)
+    check(lib().cn_nvfp4_gemv_gu(gate.w.data_ptr(), up.w.data_ptr(), gate.gs.data_ptr(), up.gs.data_ptr(), x2.data_ptr(),
+                                 h.data_ptr(), gate.rows, gate.cols, m, h.stride(0) if h.dim() == 2 else gate.rows,
+                                 float(limit), _dtype_code(x), _stream()))
+    return h
+
+
+def dense_ffn_w(gate: Fp4, up: Fp4, down: Fp4, x, limit=0.0):
+    """y = down(act(gate x, up x)) - Engine::dense_ffn_w (engine/src/gen.rs:3974), GpuFfnPlan::run
+    (engine/src/glm5_moe.rs:461) with limit > 0."""
+    return launch_gemv(down, launch_gemv_gu(gate, up, x, limit=limit))
+
+
+def dequant(w: Fp4, rule=False):
+    """f32 [rows][cols] = e2m1(code) * (ue4m3(byte) * gs): dequant_fp4_flat (engine/src/kernels.rs:1460)."""
+    out = torch.empty((w.rows, w.cols), dtype=torch.float32, device=w.w.device)
+    check(lib().cn_nvfp4_dequant(w.w.data_ptr(), w.gs.data_ptr(), out.data_ptr(), w.rows, w.cols, int(rule), _stream()))
+    return out
