@@ -29,7 +29,7 @@
 namespace {
 
 constexpr int NW = 4;  // consumer warps
-constexpr int NTHREADS = (NW + 2) * 32;
+constexpr int NTHREADS = (NW + 1) * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int XB_F16 = 144;  // bytes of one k-block's 64 activations as f16, padded: conflict-free 16-byte loads
 constexpr int XB_F32 = 272;  // the same as f32
@@ -108,10 +108,10 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + MAX_STAGES;
     float* lut = (float*)(smem + 128);  // [2][256]
-    uint8_t* stage0 = smem + HDR_BYTES;
-    const int wbytes = ROWS * piece;
-    const int xbytes = MP * TX * XB;
-    const int stage_bytes = wbytes + xbytes + MP * TX * 4;  // weights, activations, per-block inverse scales
+    uint8_t* xs0 = smem + HDR_BYTES;                              // [MP][bpr][XB] staged activations
+    float* xinv0 = (float*)(xs0 + (size_t)MP * bpr * XB);         // [MP][bpr] inverse block scales
+    uint8_t* stage0 = (uint8_t*)(xinv0 + ((MP * bpr + 3) & ~3));  // the weight ring
+    const int stage_bytes = ROWS * piece;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // output rows of this CTA: plain ROWS consecutive rows; gate/up ROWS/2 consecutive indices
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
 
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
-            mbar_init(&full[s], 33);  // the producer's expect_tx arrive + the 32 lanes of the activation warp
+            mbar_init(&full[s], 1);  // the producer's expect_tx arrive; the copies count bytes
             mbar_init(&empty[s], NW);
         }
         mbar_fence_init();
@@ -177,78 +177,67 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
         return;
     }
 
-    if (warp == NW + 1) {
-        // ------------------------------------------------------------ activation staging warp
-        // Per stage: the slice x[m][c*TX*64 .. +TX*64] of every activation row, in groups of 8
-        // values (lane & 7 = position in the 64-value block, so the 8 lanes of a block sit side by
-        // side). All loads of a batch are issued before the first conversion.
-        pdl_wait();  // activations may come from the previous kernel of the stream
-        constexpr int BATCH = XT == 1 ? 8 : 4;
-        const int per_lane = MP * TX / 4;  // groups per lane and stage
-        for (int c = 0; c < nchunks; c++) {
-            const int s = c % S;
-            if (c >= S && !mbar_wait(&empty[s], ((c / S) - 1) & 1)) {
-                cn_dev_fail(CN_DEV_WAIT_EMPTY);
-                return;
-            }
-            uint8_t* xs = stage0 + (size_t)s * stage_bytes + wbytes;
-            float* xinv = (float*)(xs + xbytes);
-            for (int i0 = 0; i0 < per_lane; i0 += BATCH) {
-                XRaw<XT> raw[BATCH];
-#pragma unroll
-                for (int b = 0; b < BATCH; b++) {
-                    const int g = lane + 32 * (i0 + b);
-                    const int m = g / (8 * TX), gi = g % (8 * TX);
-                    raw[b].a = make_uint4(0, 0, 0, 0);
-                    raw[b].b = make_uint4(0, 0, 0, 0);
-                    if (i0 + b < per_lane && m < p.m)
-                        load_x8<XT>(p.x, (size_t)m * p.k + ((size_t)c * TX + (gi >> 3)) * 64 + (gi & 7) * 8, raw[b]);
-                }
-#pragma unroll
-                for (int b = 0; b < BATCH; b++) {
-                    const int g = lane + 32 * (i0 + b);
-                    const int m = g / (8 * TX), gi = g % (8 * TX), kb = gi >> 3, wi = gi & 7;
-                    const bool live = i0 + b < per_lane;  // warp-uniform
-                    uint8_t* dst = xs + (size_t)(m * TX + kb) * XB;
-                    float vv[8];
-                    widen_x8<XT>(raw[b], vv);
-                    if (MODE == 1) {
-                        // power-of-two scale per 64-value block: |x| * mul < 2^15, exact in f16
-                        float amax = 0.0f;
-#pragma unroll
-                        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(vv[i]));
-                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                        uint32_t e = (__float_as_uint(amax) >> 23) & 0xFF;
-                        float mul = 1.0f, inv = 1.0f;
-                        if (amax > 0.0f && e < 255) {
-                            e = e < 15 ? 15 : e;
-                            mul = __uint_as_float((268u - e) << 23);
-                            inv = __uint_as_float((e - 14u) << 23);
-                        }
-                        if (live) {
-                            uint32_t h[4];
-#pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const __half2 hh = __floats2half2_rn(vv[2 * i] * mul, vv[2 * i + 1] * mul);
-                                h[i] = *(const uint32_t*)&hh;
-                            }
-                            *(uint4*)(dst + wi * 16) = make_uint4(h[0], h[1], h[2], h[3]);
-                            if (wi == 0) xinv[m * TX + kb] = inv;
-                        }
-                    } else if (live) {
-                        *(float4*)(dst + wi * 32) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-                        *(float4*)(dst + wi * 32 + 16) = make_float4(vv[4], vv[5], vv[6], vv[7]);
-                    }
-                }
-            }
-            mbar_arrive(&full[s]);
-        }
-        return;
-    }
-
     // ---------------------------------------------------------------- consumer warps
+    // First the activations: every row, the whole K, staged once per CTA while the producer fills
+    // the weight ring. Groups of 8 values; lane & 7 = position in the 64-value block, so the 8
+    // lanes of a block sit side by side. All loads of a batch are in flight before the first
+    // conversion (one L2 round trip per batch, not per group).
+    {
+        pdl_wait();  // activations may come from the previous kernel of the stream
+        constexpr int BATCH = 4;
+        const int groups = MP * bpr * 8;
+        for (int g0 = 0; g0 < groups; g0 += BATCH * NW * 32) {
+            XRaw<XT> raw[BATCH];
+#pragma unroll
+            for (int b = 0; b < BATCH; b++) {
+                const int gq = g0 + b * NW * 32 + tid;
+                const int m = gq / (bpr * 8), gi = gq % (bpr * 8);
+                raw[b].a = make_uint4(0, 0, 0, 0);
+                raw[b].b = make_uint4(0, 0, 0, 0);
+                if (gq < groups && m < p.m) load_x8<XT>(p.x, (size_t)m * p.k + (size_t)gi * 8, raw[b]);
+            }
+#pragma unroll
+            for (int b = 0; b < BATCH; b++) {
+                const int gq = g0 + b * NW * 32 + tid;
+                const int m = gq / (bpr * 8), gi = gq % (bpr * 8), kb = gi >> 3, wi = gi & 7;
+                const bool live = gq < groups;  // uniform over each aligned group of 8 lanes
+                uint8_t* dst = xs0 + (size_t)(m * bpr + kb) * XB;
+                float vv[8];
+                widen_x8<XT>(raw[b], vv);
+                if (MODE == 1) {
+                    // power-of-two scale per 64-value block: |x| * mul < 2^15, exact in f16
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(vv[i]));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                    uint32_t e = (__float_as_uint(amax) >> 23) & 0xFF;
+                    float mul = 1.0f, inv = 1.0f;
+                    if (amax > 0.0f && e < 255) {
+                        e = e < 15 ? 15 : e;
+                        mul = __uint_as_float((268u - e) << 23);
+                        inv = __uint_as_float((e - 14u) << 23);
+                    }
+                    if (live) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const __half2 hh = __floats2half2_rn(vv[2 * i] * mul, vv[2 * i + 1] * mul);
+                            h[i] = *(const uint32_t*)&hh;
+                        }
+                        *(uint4*)(dst + wi * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+                        if (wi == 0) xinv0[m * bpr + kb] = inv;
+                    }
+                } else if (live) {
+                    *(float4*)(dst + wi * 32) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+                    *(float4*)(dst + wi * 32 + 16) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+                }
+            }
+        }
+        // the consumer warps only (the producer warp is streaming): named barrier 1
+        asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+    }
     const int txi = lane % TX, ry = lane / TX;
     const int g = warp * (32 / TX) + ry;
     float acc[RT][MP];
@@ -271,7 +260,7 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
 #pragma unroll
             for (int i = 0; i < 9; i++) wv[r][i] = wp[i];
         }
-        const uint8_t* xs = st + wbytes + (size_t)txi * XB;
+        const uint8_t* xs = xs0 + (size_t)(c * TX + txi) * XB;
         float blk[RT][MP];
 #pragma unroll
         for (int r = 0; r < RT; r++)
@@ -283,7 +272,7 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
                 uint4 xa[MP], xb[MP];
 #pragma unroll
                 for (int m = 0; m < MP; m++) {
-                    const uint4* xp = (const uint4*)(xs + (size_t)m * TX * XB + sb * 32);
+                    const uint4* xp = (const uint4*)(xs + (size_t)m * bpr * XB + sb * 32);
                     xa[m] = xp[0];
                     xb[m] = xp[1];
                 }
@@ -292,20 +281,14 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
                     const float sc = lut[((gu && (r & 1)) ? 256 : 0) + ((wv[r][0] >> (8 * sb)) & 0xFF)];
                     const uint32_t c0 = wv[r][1 + 2 * sb], c1 = wv[r][2 + 2 * sb];
                     uint32_t h[8];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        h[i] = e2m1x2_to_f16x2((c0 >> (8 * i)) & 0xFF);
-                        h[4 + i] = e2m1x2_to_f16x2((c1 >> (8 * i)) & 0xFF);
-                    }
+                    e2m1x8_to_f16x2(c0, h);
+                    e2m1x8_to_f16x2(c1, h + 4);
 #pragma unroll
                     for (int m = 0; m < MP; m++) {
                         const uint32_t xv[8] = {xa[m].x, xa[m].y, xa[m].z, xa[m].w, xb[m].x, xb[m].y, xb[m].z, xb[m].w};
                         float p0 = 0.0f, p1 = 0.0f;  // even / odd values: two independent chains
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            p0 = fma_f16_f32((uint16_t)(h[i] & 0xffff), (uint16_t)(xv[i] & 0xffff), p0);
-                            p1 = fma_f16_f32((uint16_t)(h[i] >> 16), (uint16_t)(xv[i] >> 16), p1);
-                        }
+                        for (int i = 0; i < 8; i++) fma2_f16_f32(p0, p1, h[i], xv[i]);
                         blk[r][m] = fmaf(p0 + p1, sc, blk[r][m]);
                     }
                 }
@@ -313,7 +296,7 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
                 float xv[MP][16];
 #pragma unroll
                 for (int m = 0; m < MP; m++) {
-                    const float4* xp = (const float4*)(xs + (size_t)m * TX * XB + sb * 64);
+                    const float4* xp = (const float4*)(xs + (size_t)m * bpr * XB + sb * 64);
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const float4 t = xp[i];
@@ -345,10 +328,9 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
             }
         }
         if (MODE == 1) {
-            const float* xinv = (const float*)(st + wbytes + xbytes);
 #pragma unroll
             for (int m = 0; m < MP; m++) {
-                const float inv = xinv[m * TX + txi];
+                const float inv = xinv0[m * bpr + c * TX + txi];
 #pragma unroll
                 for (int r = 0; r < RT; r++) acc[r][m] = fmaf(blk[r][m], inv, acc[r][m]);
             }
@@ -482,14 +464,27 @@ int gemv_common(const void* w0, const void* w1, const float* gs0, const float* g
     const int per_cta = w1 ? ROWS / 2 : ROWS;
     const int grid = (rows + per_cta - 1) / per_cta;
     const int xb = mode == 1 ? XB_F16 : XB_F32;
-    const size_t stage_bytes = (size_t)ROWS * tx * 36 + (size_t)mp * tx * xb + (size_t)mp * tx * 4;
+    const size_t stage_bytes = (size_t)ROWS * tx * 36;
+    const size_t xbytes = (size_t)mp * bpr * xb + (size_t)((mp * bpr + 3) & ~3) * 4;
     const int nchunks = bpr / tx;
-    int stages = (int)((64 * 1024) / stage_bytes);
+    // ring depth: aim at four resident CTAs per SM (about 52 KB each), at least two stages
+    long long room = 52 * 1024 - (long long)HDR_BYTES - (long long)xbytes;
+    int stages = (int)(room / (long long)stage_bytes);
     if (g_tune_stages > 0) stages = g_tune_stages;
     stages = stages < 2 ? 2 : (stages > MAX_STAGES ? MAX_STAGES : stages);
     if (stages > nchunks) stages = nchunks < 1 ? 1 : nchunks;
-    const size_t smem = HDR_BYTES + stages * stage_bytes;
-    if (smem > 200 * 1024) CN_FAIL(CN_ERR_LIMIT, "%s: %zu B of shared memory per block", who, smem);
+    const size_t smem = HDR_BYTES + xbytes + stages * stage_bytes;
+    if (smem > 200 * 1024) {
+        // the staged activations of all m rows do not fit one CTA: two calls over half the rows each
+        // (each row's arithmetic is the same whatever the split, so results do not change)
+        if (m == 1) CN_FAIL(CN_ERR_LIMIT, "%s: k = %d needs %zu B of shared memory per block", who, k, smem);
+        const int m0 = m / 2;
+        const size_t es = dtype == CN_BF16 ? 2 : 4;
+        int rc = gemv_common(w0, w1, gs0, gs1, x, y, rows, k, m0, ldy, limit, dtype, stream, who);
+        if (rc) return rc;
+        return gemv_common(w0, w1, gs0, gs1, (const char*)x + (size_t)m0 * k * es, (char*)y + (size_t)m0 * ldy * es, rows, k, m - m0, ldy,
+                           limit, dtype, stream, who);
+    }
     GemvParams p;
     p.w0 = (const uint8_t*)w0, p.w1 = (const uint8_t*)w1, p.gs0 = gs0, p.gs1 = gs1, p.x = x, p.y = y;
     p.rows = rows, p.k = k, p.m = m, p.ldy = ldy, p.limit = limit, p.tx = tx, p.stages = stages;
