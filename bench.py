@@ -1,0 +1,237 @@
+"""Benchmark of the quantized GEMV hot path: the NVFP4 dense decode layer stack (27B-shaped, 64
+layers, M = 1) on N B200 GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--impl reference]
+
+A step is one token through the whole stack (4 GEMV launches per layer). `value` is the algorithmic
+bytes of a step (every weight byte once + activations) over the device time of a step, inputs
+resident in HBM; `e2e` is the same through the host-facing call with pinned host buffers copied in
+and out every step. One JSON line on stdout (rank 0).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "nvfp4_gemv_hbm_gbs"
+UNIT = "GB/s"
+
+
+def measured_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([f.strip() for f in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_baseline_run(host_layers, threads, seconds_budget, m=1):
+    """The CPU checker's NVFP4 GEMV (AVX2 arm of the reference's operation order, rows split over
+    `threads`) over whole layers, rotating over the given distinct layers. Returns (GB/s, passes)."""
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(0)
+    xs = {}
+    for mats in host_layers:
+        for _, (_, _, k) in mats.items():
+            xs.setdefault(k, rng.standard_normal((m, k)).astype(np.float32))
+    path = 1 if oracle.lib().cn_o_have_avx2() else 0
+    layer_bytes = sum(w.size for w, _, _ in host_layers[0].values())
+    t_total, passes = 0.0, 0
+    # one untimed pass: page faults, thread start
+    for name, (w, rows, k) in host_layers[0].items():
+        oracle.nvfp4_gemv(w, rows, k, 1.0, xs[k], threads=threads, path=path)
+    while t_total < seconds_budget and passes < 64:
+        mats = host_layers[passes % len(host_layers)]
+        t0 = time.perf_counter()
+        for name, (w, rows, k) in mats.items():
+            oracle.nvfp4_gemv(w, rows, k, 1.0, xs[k], threads=threads, path=path)
+        t_total += time.perf_counter() - t0
+        passes += 1
+    return (layer_bytes * passes / t_total / 1e9 if t_total > 0 else 0.0), passes
+
+
+def reference_arm(args, rank):
+    """`--impl reference`: the reference's CPU implementation of the path (its Rust source cannot be
+    built here - no Rust toolchain - so the C port under oracle/ stands in, kind "port"), all host
+    threads, each step one layer of the stack's shapes (186 MB of NVFP4)."""
+    if rank != 0:
+        return
+    import numpy as np
+    from crownest_b200 import synth
+    threads = os.cpu_count() or 1
+    rng = np.random.default_rng(0)
+    layers = [{n: (synth.nvfp4_matrix(r, k, rng), r, k) for n, r, k in synth.dense_layer_shapes()} for _ in range(2)]
+    import oracle
+    path = 1 if oracle.lib().cn_o_have_avx2() else 0
+    xs = {k: rng.standard_normal((args.m, k)).astype(np.float32) for _, _, k in synth.dense_layer_shapes()}
+    for s in range(max(1, args.warmup)):
+        for name, (w, rows, k) in layers[s % len(layers)].items():
+            oracle.nvfp4_gemv(w, rows, k, 1.0, xs[k], threads=threads, path=path)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        for name, (w, rows, k) in layers[s % len(layers)].items():
+            oracle.nvfp4_gemv(w, rows, k, 1.0, xs[k], threads=threads, path=path)
+    dt = time.perf_counter() - t0
+    gbs = synth.dense_layer_bytes() * args.steps / dt / 1e9
+    sample = f"{args.steps} steps, each one layer of the stack (qkv, o, gate, up, down = {synth.dense_layer_bytes()} B), 2 distinct layers rotated"
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "nvfp4 dense decode stack 27B-shaped, M=%d (CPU: one layer per step)" % args.m},
+            "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 decode, 4 = MTP verify)")
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--impl", default="crownest")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return reference_arm(args, rank)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    from crownest_b200 import _lib, dense
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _lib.lib()  # fail loudly when the CUDA library is missing: there is no fallback
+
+    stack = dense.DenseStack(layers=args.layers, device=f"cuda:{local}", seed=0, rank=rank, world=world, group=group, max_m=args.m)
+    m = args.m
+    gen = torch.Generator(device="cpu").manual_seed(1)
+    x_host = torch.randn((m, stack.hidden), generator=gen).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty((m, stack.hidden), dtype=torch.bfloat16).pin_memory()
+    stack.x[:m].copy_(x_host)
+    use_graph = world == 1
+    if use_graph:
+        stack.capture(m)
+    step = (lambda: stack.graph.replay()) if use_graph else (lambda: stack.run_layers(m))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # end to end through the host-facing call: pinned host in, pinned host out, every step
+    for _ in range(2):
+        stack.decode_step(x_host, y_host)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        stack.decode_step(x_host, y_host)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+    status = _lib.device_status()
+
+    if rank == 0:
+        bytes_step = stack.bytes_per_step(m)
+        ms_step = ms / args.steps
+        value = bytes_step / (ms_step * 1e-3) / 1e9
+        peak, peak_kind = measured_peak()
+        per_gpu = value / world
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
+                "config": {"workload": f"nvfp4 dense decode stack 27B-shaped (hidden 5120, qkv 7168, inter 17408, {stack.layers} layers), M={m}",
+                           "activations": "bf16 in/out, f32 accumulate", "parallelism": f"tp{world} row split + all-gather" if world > 1 else "none",
+                           "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (bytes_step / 1e9),
+                           "launch": "CUDA graph replay" if use_graph else "eager launches", "tokens_per_s": m / (ms_step * 1e-3)},
+                "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "traffic": None,
+                             "peak_kind": peak_kind, "kernel": "nvfp4_gemv_kernel", "bytes_per_launch": bytes_step / world / stack.launches_per_step,
+                             "us_per_launch": ms_step * 1e3 / stack.launches_per_step},
+                "e2e": {"value": bytes_step / (e2e_s / args.steps) / 1e9, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
+                        "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_s / args.steps * 1e3},
+                "gpu_launches": stack.launches_per_step * args.steps, "clocks": clocks, "device_status": status}
+        if world == 1 and not args.no_cpu_baseline:
+            host_layers = [stack.host_copy(i) for i in range(min(3, stack.layers))]
+            threads = os.cpu_count() or 1
+            gbs, passes = cpu_baseline_run(host_layers, threads, 12.0, m)
+            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"{passes} passes over whole layers ({host_layers and sum(w.size for w, _, _ in host_layers[0].values())} B each), "
+                                              f"{len(host_layers)} distinct layers rotated, AVX2 arm"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,136 @@
+"""The dense decode layer stack: the operator sequence the reference's ``Engine::decode_step`` runs
+per layer (engine/src/gen.rs:6117-6190) reduced to its quantized projections - fused QKV, o_proj,
+fused gate/up + SiLU, down - with everything that is not a GEMV left out (attention, norms and
+residuals are other operators). One token (M = 1) or M <= 8 rows (``Engine::verify_rows``,
+engine/src/gen.rs:5572).
+
+Data flow per layer, chosen so that magnitudes stay bounded without the norms: the layer input x
+feeds qkv, o_proj and gate/up; down reads the gate/up output h; the stack's output is the last
+layer's down output. Every launch waits for its predecessor (programmatic dependent launch), as
+the projections of a real decode step do.
+
+Tensor parallelism (``world`` > 1): every matrix is split by output rows into contiguous ranges,
+gate and up rows paired so the activation stays local; each rank's slice of every output is
+all-gathered (NCCL) so that x and h are replicated again for the next projection.
+"""
+import numpy as np
+import torch
+
+from . import ops, synth
+from ._lib import CrownestError
+
+
+def _rand_nvfp4_device(rows, cols, gen, device, scale_sigma=0.05):
+    """The benchmark's generator on the device: codes uniform over all 16 values, scale byte =
+    E4M3(|N(0,1)| * sigma) (round to nearest even; never the NaN code at this magnitude)."""
+    blocks = rows * cols // 64
+    w = torch.randint(0, 256, (blocks, 36), dtype=torch.uint8, device=device, generator=gen)
+    s = (torch.randn((blocks, 4), device=device, generator=gen).abs() * scale_sigma).to(torch.float8_e4m3fn)
+    w[:, :4] = s.view(torch.uint8)
+    return w.reshape(-1)
+
+
+class DenseStack:
+    def __init__(self, cfg=None, layers=None, device="cuda", seed=0, rank=0, world=1, group=None, max_m=1, dtype=torch.bfloat16):
+        cfg = dict(cfg or synth.DENSE_27B)
+        self.hidden, self.qkv, self.inter = cfg["hidden"], cfg["qkv"], cfg["inter"]
+        self.layers = layers if layers is not None else cfg["layers"]
+        self.rank, self.world, self.group, self.device, self.dtype = rank, world, group, device, dtype
+        for n in (self.qkv, self.hidden, self.inter):
+            if n % world:
+                raise CrownestError(f"tensor parallel: {n} output rows do not split over {world} ranks")
+        gen = torch.Generator(device=device)
+        self.w = []
+        gs = torch.ones(1, dtype=torch.float32, device=device)
+        for layer in range(self.layers):
+            mats = {}
+            for name, rows, k in synth.dense_layer_shapes(cfg):
+                # every rank draws its own row range from a stream keyed by (seed, layer, matrix, rank)
+                gen.manual_seed(((seed * 1000 + layer) * 8 + len(mats)) * 64 + rank)
+                r = rows // world
+                mats[name] = ops.Fp4(_rand_nvfp4_device(r, k, gen, device), gs, r, k)
+            self.w.append(mats)
+        self.max_m = max_m
+        m = max_m
+        self.x = torch.zeros((m, self.hidden), dtype=dtype, device=device)
+        self.q = torch.empty((m, self.qkv), dtype=dtype, device=device)
+        self.o = torch.empty((m, self.hidden), dtype=dtype, device=device)
+        self.h = torch.empty((m, self.inter), dtype=dtype, device=device)
+        self.y = torch.empty((m, self.hidden), dtype=dtype, device=device)
+        if world > 1:
+            # per-rank slices land here, then one all-gather per projection
+            self.part = {n: torch.empty((m, r // world), dtype=dtype, device=device) for n, r in
+                         (("q", self.qkv), ("o", self.hidden), ("h", self.inter), ("y", self.hidden))}
+        self.launches_per_step = 4 * self.layers
+        self.graph = None
+
+    # algorithmic bytes of one step over all ranks: every weight byte once, plus the tensor scale and the
+    # activations in and out of each projection at the boundary dtype
+    def bytes_per_step(self, m=1):
+        es = 2 if self.dtype == torch.bfloat16 else 4
+        per_layer_w = sum(r * k // 64 * 36 for _, r, k in synth.dense_layer_shapes(dict(hidden=self.hidden, qkv=self.qkv, inter=self.inter)))
+        act = ((self.hidden + self.qkv) + 2 * self.hidden + (self.hidden + self.inter) + (self.inter + self.hidden)) * es * m
+        return self.layers * (per_layer_w + act + 5 * 4)
+
+    def weight_bytes_local(self):
+        return sum(t.w.numel() for mats in self.w for t in mats.values())
+
+    def _gather(self, name, full, m):
+        import torch.distributed as dist
+        # [world][m][n/world] -> [m][n]: gather into a staging view, then interleave
+        part = self.part[name][:m]
+        if m == 1:
+            dist.all_gather_into_tensor(full[:1].view(-1), part.reshape(-1), group=self.group)
+        else:
+            tmp = torch.empty((self.world, m, part.shape[1]), dtype=part.dtype, device=part.device)
+            dist.all_gather_into_tensor(tmp.view(-1), part.reshape(-1), group=self.group)
+            full[:m].copy_(tmp.permute(1, 0, 2).reshape(m, -1))
+
+    def _proj(self, w, x, name, full, m, gu=None):
+        out = full[:m] if self.world == 1 else self.part[name][:m]
+        if gu is None:
+            ops.launch_gemv(w, x, out)
+        else:
+            ops.launch_gemv_gu(w, gu, x, out)
+        if self.world > 1:
+            self._gather(name, full, m)
+
+    def run_layers(self, m=1):
+        """Enqueue the whole stack on the current stream (4 launches per layer)."""
+        x = self.x[:m]
+        for mats in self.w:
+            self._proj(mats["qkv"], x, "q", self.q, m)
+            self._proj(mats["o"], x, "o", self.o, m)
+            self._proj(mats["gate"], x, "h", self.h, m, gu=mats["up"])
+            self._proj(mats["down"], self.h[:m], "y", self.y, m)
+        return self.y[:m]
+
+    def capture(self, m=1):
+        """Record the stack into a CUDA graph (the reference captures its decode step the same way,
+        engine/src/gen.rs:6100-6225)."""
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            self.run_layers(m)
+            st.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                self.run_layers(m)
+        self.graph, self.graph_m = g, m
+        return g
+
+    def decode_step(self, x_host, y_host):
+        """Host-facing step: pinned host activations in, pinned host output back (the reference's
+        embedding-row upload and result readback, engine/src/gen.rs:6071-6077, :6238-6242)."""
+        m = x_host.shape[0]
+        self.x[:m].copy_(x_host, non_blocking=True)
+        if self.graph is not None and self.graph_m == m:
+            self.graph.replay()
+        else:
+            self.run_layers(m)
+        y_host.copy_(self.y[:m], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return y_host
+
+    def host_copy(self, layer):
+        """One layer's matrices as numpy bytes (for the CPU checker)."""
+        return {n: (t.w.cpu().numpy(), t.rows, t.cols) for n, t in self.w[layer].items()}
