@@ -53,12 +53,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false after ~2^22 polls (each try_wait itself blocks for a hardware time slice),
-// far beyond any legitimate wait of these kernels.
+// Bounded wait: gives up (false) about one second after it started, far beyond any legitimate
+// wait of these kernels (each try_wait itself blocks for a short hardware time slice).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (int i = 0; i < (1 << 22); i++)
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-    return false;
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
 }
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier. Both addresses
 // 16-byte aligned, size a multiple of 16. No multicast.

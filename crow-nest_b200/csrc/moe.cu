@@ -1,0 +1,171 @@
+// The routed-expert decode step over NVFP4 experts: grouped expert GEMVs after top-k routing, the
+// shared expert, and the weighted combine.
+//
+// Supersedes the routed half of Engine::moe_run (engine/src/gen.rs:4168-4532): gemv_fp4_ptrb over
+// the gate|up and down pointer tables (engine/src/kernels.rs:195-233), silu_mul_combo (:1562),
+// acc_combo (:1583) and gate_shared (:1593); the operator shape follows GpuMoePlan
+// (engine/src/glm5_moe.rs:518-793): a plan owns its scratch, run() only enqueues.
+//
+// B200 shape of the step: combos (token, rank) are sorted by expert on the device, so the CTAs
+// that read one expert's matrices run back to back and every expert's bytes cross HBM once per
+// step (repeats are L2 hits); gate, up and the activation are one launch; a null table entry
+// skips the combo (the expert lives on another rank).
+#include "common.cuh"
+#include "nvfp4_gemv.cuh"
+
+namespace {
+
+// order[] = combos sorted by expert id (negative ids last); one CTA, counting sort in shared memory
+__global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ order, int n, int E) {
+    extern __shared__ int cnt[];  // [E + 2]
+    for (int i = threadIdx.x; i <= E + 1; i += blockDim.x) cnt[i] = 0;
+    __syncthreads();
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const int e = ids[c];
+        atomicAdd(&cnt[(e < 0 || e >= E) ? E : e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i <= E; i++) {
+            const int c = cnt[i];
+            cnt[i] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    // stable within an expert: each combo counts the earlier combos of its expert (n is small)
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        int e = ids[c];
+        e = (e < 0 || e >= E) ? E : e;
+        int before = 0;
+        for (int d = 0; d < c; d++) {
+            int f = ids[d];
+            f = (f < 0 || f >= E) ? E : f;
+            before += f == e;
+        }
+        order[cnt[e] + before] = c;
+    }
+}
+
+// y[t][c] = base + sum_j w[t][j] * eo[t*K + j][c], j in pick order; base = shared[t][c]
+// (times sigmoid(sgate[t]) when gated), 0 without a shared expert. A combo whose expert has no
+// local matrix contributes nothing.
+template <int YT>
+__global__ void moe_combine_kernel(const float* __restrict__ eo, const float* __restrict__ wts, const int32_t* __restrict__ ids,
+                                   const unsigned long long* __restrict__ tab, const float* __restrict__ shared,
+                                   const float* __restrict__ sgate, void* __restrict__ y, int H, int K) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (c >= H) return;
+    float acc = 0.0f;
+    for (int j = 0; j < K; j++) {
+        const int e = ids[t * K + j];
+        if (e < 0 || (tab && tab[e] == 0ull)) continue;
+        acc = __fadd_rn(acc, __fmul_rn(wts[t * K + j], eo[((size_t)t * K + j) * H + c]));
+    }
+    float base = shared ? shared[(size_t)t * H + c] : 0.0f;
+    if (shared && sgate) base = __fmul_rn(1.0f / (1.0f + expf(-sgate[t])), base);
+    const float v = __fadd_rn(base, acc);
+    if (YT == 1)
+        ((__nv_bfloat16*)y)[(size_t)t * H + c] = __float2bfloat16_rn(v);
+    else
+        ((float*)y)[(size_t)t * H + c] = v;
+}
+
+struct MoePlan {
+    int hidden, inter, experts, topk, max_tokens, device;
+    float* h;        // [max_tokens * topk][inter]
+    float* eo;       // [max_tokens * topk][hidden]
+    float* hs;       // [max_tokens][shared inter <= inter_s]
+    float* ys;       // [max_tokens][hidden]
+    int32_t* order;  // [max_tokens * topk]
+    int shared_inter;
+};
+
+}  // namespace
+
+extern "C" int cn_moe_sort(const int32_t* ids, int32_t* order, int combos, int experts, cn_stream_t stream) {
+    if (combos < 1 || experts < 1 || experts > 8192) CN_FAIL(CN_ERR_SHAPE, "cn_moe_sort: %d combos over %d experts", combos, experts);
+    moe_sort_kernel<<<1, 1024, (experts + 2) * sizeof(int), (cudaStream_t)stream>>>(ids, order, combos, experts);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+extern "C" int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const unsigned long long* table, const float* shared,
+                              const float* sgate, void* y, int tokens, int hidden, int topk, int dtype, cn_stream_t stream) {
+    if (tokens < 1 || hidden < 1 || topk < 1) CN_FAIL(CN_ERR_SHAPE, "cn_moe_combine: tokens %d hidden %d topk %d", tokens, hidden, topk);
+    dim3 grid((hidden + 255) / 256, tokens);
+    if (dtype == CN_BF16)
+        moe_combine_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(eo, wts, ids, table, shared, sgate, y, hidden, topk);
+    else
+        moe_combine_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(eo, wts, ids, table, shared, sgate, y, hidden, topk);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+extern "C" int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, int shared_inter, int experts, int topk, int max_tokens) {
+    if (!plan_out || hidden % 256 || inter % 256 || shared_inter % 256 || experts < 1 || topk < 1 || max_tokens < 1)
+        CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_plan_create: hidden %d, inter %d, shared inter %d must be multiples of 256", hidden, inter, shared_inter);
+    MoePlan* p = new MoePlan();
+    p->hidden = hidden, p->inter = inter, p->experts = experts, p->topk = topk, p->max_tokens = max_tokens, p->shared_inter = shared_inter;
+    CN_CUDA(cudaGetDevice(&p->device));
+    const size_t combos = (size_t)max_tokens * topk;
+    CN_CUDA(cudaMalloc(&p->h, combos * inter * sizeof(float)));
+    CN_CUDA(cudaMalloc(&p->eo, combos * hidden * sizeof(float)));
+    CN_CUDA(cudaMalloc(&p->hs, (size_t)max_tokens * (shared_inter > 0 ? shared_inter : 1) * sizeof(float)));
+    CN_CUDA(cudaMalloc(&p->ys, (size_t)max_tokens * hidden * sizeof(float)));
+    CN_CUDA(cudaMalloc(&p->order, combos * sizeof(int32_t)));
+    *plan_out = p;
+    return CN_OK;
+}
+
+extern "C" int cn_moe_nvfp4_plan_destroy(void* plan) {
+    MoePlan* p = (MoePlan*)plan;
+    if (!p) return CN_OK;
+    cudaFree(p->h), cudaFree(p->eo), cudaFree(p->hs), cudaFree(p->ys), cudaFree(p->order);
+    delete p;
+    return CN_OK;
+}
+
+extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, const unsigned long long* table_up,
+                                const unsigned long long* table_dn, const float* gs_gu, const float* gs_up, const float* gs_dn,
+                                const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs,
+                                const float* sgate, const int32_t* ids, const float* wts, const void* x, void* y, int tokens, float limit,
+                                int dtype, cn_stream_t stream_) {
+    MoePlan* p = (MoePlan*)plan;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!p) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_run: null plan");
+    if (tokens < 1 || tokens > p->max_tokens) CN_FAIL(CN_ERR_LIMIT, "cn_moe_nvfp4_run: %d tokens, the plan holds %d", tokens, p->max_tokens);
+    const int combos = tokens * p->topk;
+    if (int rc = cn_moe_sort(ids, p->order, combos, p->experts, stream_)) return rc;
+    // routed gate|up + activation: h[c] = act(gate_e x_t, up_e x_t), c = t * topk + j
+    GemvCall a = {};
+    a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
+    a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = p->order, a.tab0 = table_gu, a.tab1 = table_up;
+    a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = p->topk, a.combos = combos;
+    if (int rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4_run (gate/up)")) return rc;
+    // routed down: eo[c] = down_e h[c]
+    GemvCall d = {};
+    d.gs0 = gs_dn, d.x = p->h, d.y = p->eo, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
+    d.x_f16_ok = 1, d.ids = ids, d.order = p->order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
+    if (int rc = cn_gemv_launch(d, stream, "cn_moe_nvfp4_run (down)")) return rc;
+    // shared expert on every token, up to 8 rows per pass
+    const float* shared = nullptr;
+    if (shared_gate) {
+        const size_t es = dtype == CN_BF16 ? 2 : 4;
+        for (int t0 = 0; t0 < tokens; t0 += CN_MAX_M) {
+            const int m = tokens - t0 < CN_MAX_M ? tokens - t0 : CN_MAX_M;
+            GemvCall g = {};
+            g.w0 = shared_gate, g.w1 = shared_up, g.gs0 = shared_gs, g.gs1 = shared_gs + 1, g.x = (const char*)x + (size_t)t0 * p->hidden * es;
+            g.y = p->hs + (size_t)t0 * p->shared_inter, g.rows = p->shared_inter, g.k = p->hidden, g.m = m, g.ldy = p->shared_inter;
+            g.limit = limit, g.dtype = dtype, g.out_f32 = 1;
+            if (int rc = cn_gemv_launch(g, stream, "cn_moe_nvfp4_run (shared gate/up)")) return rc;
+            GemvCall s = {};
+            s.w0 = shared_down, s.gs0 = shared_gs + 2, s.x = p->hs + (size_t)t0 * p->shared_inter, s.y = p->ys + (size_t)t0 * p->hidden;
+            s.rows = p->hidden, s.k = p->shared_inter, s.m = m, s.ldy = p->hidden, s.dtype = CN_F32, s.out_f32 = 1, s.x_f16_ok = 1;
+            if (int rc = cn_gemv_launch(s, stream, "cn_moe_nvfp4_run (shared down)")) return rc;
+        }
+        shared = p->ys;
+    }
+    return cn_moe_combine(p->eo, wts, ids, table_dn, shared, sgate, y, tokens, p->hidden, p->topk, dtype, stream_);
+}

@@ -1,0 +1,531 @@
+// EXL3 "MUL1" trellis GEMV / expert FFN on sm_100a: y = x W with W = diag(suh) H W_hat H diag(svh) / 128,
+// W_hat decoded from the 16-bit trellis states in the inner loop.
+//
+// Supersedes mul1_had_in / mul1_gemv / mul1_gemv2 / mul1_had_out / mul1_act_had_in
+// (engine/src/kernels_mul1.cu:114, :280, :553, :669, :688) behind the plan interface of
+// kernels::mul1::GemvPlan / FfnPlan (engine/src/kernels.rs:6644-6850); CPU twin cpu_mul1::gemv
+// (engine/src/cpu_mul1.rs:1626). Format: converter/src/mul1.rs:10-34.
+//
+// Three steps per GEMV, none of which writes a dequantised weight:
+//   had_in   xh = H128(x * suh) per 128-block, stored f16 with a power-of-two scale per block
+//   gemv     y' = xh W_hat over a k-split: each CTA owns 8 adjacent tile columns (128 outputs) and
+//            k/(16 S) tile rows; the 768-byte run of 8 tiles per tile row arrives by 1-D bulk copy
+//            (TMA) into a shared-memory ring; warp w decodes tile column w: lane g extracts its 8
+//            states from a 64-bit window (compile-time shifts at K = 3), multiplies by 0x83DCD12D,
+//            sums the bytes with dp4a (+0x6400 = the f16 pattern of 1024 + s), maps pairs through
+//            one HFMA2 to the codec's f16 weights (bit-exact) and accumulates with f16 x f16 -> f32
+//            mixed FMAs; partial sums of the k-split go to scratch
+//   had_out  y = H128(sum of partials) / 128 * svh
+// The inner loop is instruction-bound, not HBM-bound: about 7 issue slots per 3-bit weight.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MUL1_MAXT = CN_MAX_M;  // activation rows per slot
+constexpr int RING = 4;              // stages of the tile ring
+constexpr int UROWS = 4;             // tile rows per stage
+
+struct Mul1Spec {
+    int k, n;        // in, out
+    int bits, half;  // bitrate
+    int n32;         // u32 words per tile
+    long long tr_off, suh_off, svh_off;  // byte offsets into the record
+};
+
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// natural-order FWHT of 128 values over one warp, element 4*lane + j in v[j]; stages (a+b, a-b)
+__device__ __forceinline__ void fwht128(float v[4], int lane) {
+    const float a0 = __fadd_rn(v[0], v[1]), a1 = __fsub_rn(v[0], v[1]), a2 = __fadd_rn(v[2], v[3]), a3 = __fsub_rn(v[2], v[3]);
+    v[0] = __fadd_rn(a0, a2), v[1] = __fadd_rn(a1, a3), v[2] = __fsub_rn(a0, a2), v[3] = __fsub_rn(a1, a3);
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+            v[j] = (lane & m) ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
+        }
+    }
+}
+
+// power-of-two scale of a 128-block so that |v| * mul < 2^15 (f16 exact range); returns mul, sets inv
+__device__ __forceinline__ float block_scale(float amax, float& inv) {
+    uint32_t e = (__float_as_uint(amax) >> 23) & 0xFF;
+    inv = 1.0f;
+    if (!(amax > 0.0f) || e == 255) return 1.0f;
+    e = e < 15 ? 15 : e;
+    inv = __uint_as_float((e - 14u) << 23);
+    return __uint_as_float((268u - e) << 23);
+}
+
+// xh16[slot][t][k] = f16(H128(x * suh) * mul), xinv[slot][t][k/128] = 1/mul.
+// grid (k/128, T, slots), block 32. XT: 0 f32, 1 bf16 input. x row of slot: x + (slot / x_div) * T * k.
+template <int XT>
+__global__ void mul1_had_in_kernel(const unsigned long long* __restrict__ ptrs, const void* __restrict__ x, uint16_t* __restrict__ xh,
+                                   float* __restrict__ xinv, int k, int T, long long suh_off, int x_div) {
+    const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
+    if (ptrs[slot] == 0ull) return;  // a null record: nothing to read or write
+    const uint16_t* suh = (const uint16_t*)(ptrs[slot] + (unsigned long long)suh_off);
+    const size_t xrow = ((size_t)(slot / x_div) * T + t) * k, row = ((size_t)slot * T + t) * k;
+    const int c0 = blk * 128 + 4 * lane;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float xv = XT == 1 ? __bfloat162float(((const __nv_bfloat16*)x)[xrow + c0 + j]) : ((const float*)x)[xrow + c0 + j];
+        v[j] = __fmul_rn(xv, h2f(suh[c0 + j]));
+    }
+    fwht128(v, lane);
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float inv;
+    const float mul = block_scale(amax, inv);
+    const __half2 h0 = __floats2half2_rn(v[0] * mul, v[1] * mul), h1 = __floats2half2_rn(v[2] * mul, v[3] * mul);
+    *(uint2*)(xh + row + c0) = make_uint2(*(const uint32_t*)&h0, *(const uint32_t*)&h1);
+    if (lane == 0) xinv[((size_t)slot * T + t) * (k / 128) + blk] = inv;
+}
+
+// the codec's f16 weights of two states (bit-exact): sum16 = 0x6400 + bytesum(state * 0x83DCD12D) is the
+// f16 pattern of 1024 + s; w = fma(sum16, 0x1eee, 0xc931) in f16 with one rounding (converter/src/mul1.rs:135-143)
+__device__ __forceinline__ uint32_t mul1_pair(uint32_t s0, uint32_t s1) {
+    const uint32_t a = __dp4a(s0 * 0x83DCD12Du, 0x01010101u, 0x6400u), b = __dp4a(s1 * 0x83DCD12Du, 0x01010101u, 0x6400u);
+    const uint32_t packed = __byte_perm(a, b, 0x5410);
+    uint32_t w;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(w) : "r"(packed), "r"(0x1eee1eeeu), "r"(0xc931c931u));
+    return w;
+}
+
+// Lane g's eight 16-bit states of one tile. K3: bits = 3, whole bitrate, every shift a constant after the
+// window is aligned to the lane's first bit. Otherwise the general circular extraction.
+template <bool K3>
+__device__ __forceinline__ void lane_states(const uint32_t* tile, int n32, const int lo[8], int wi0, int sh0, uint32_t st[8]) {
+    if (K3) {
+        // words wi0, wi0+1, wi0+2 (circular) hold bits [24g - 13, 24g + 24); align the window to bit 0
+        const uint32_t w0 = tile[wi0], w1 = tile[wi0 + 1 >= n32 ? wi0 + 1 - n32 : wi0 + 1], w2 = tile[wi0 + 2 >= n32 ? wi0 + 2 - n32 : wi0 + 2];
+        const uint32_t hi = __funnelshift_l(w1, w0, sh0), lw = __funnelshift_l(w2, w1, sh0);
+        // state j = bits [3j, 3j + 16) of the 64-bit window hi:lw (MSB first)
+        st[0] = hi >> 16;
+        st[1] = (hi >> 13) & 0xffffu;
+        st[2] = (hi >> 10) & 0xffffu;
+        st[3] = (hi >> 7) & 0xffffu;
+        st[4] = (hi >> 4) & 0xffffu;
+        st[5] = (hi >> 1) & 0xffffu;
+        st[6] = __funnelshift_l(lw, hi, 18) >> 16;
+        st[7] = __funnelshift_l(lw, hi, 21) >> 16;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = lo[j] >> 5, o = lo[j] & 31, i1 = i + 1 == n32 ? 0 : i + 1;
+            st[j] = __funnelshift_l(tile[i1], tile[i], o) >> 16;
+        }
+    }
+}
+
+// y' partials of one k-split. grid (n/128, S, slots), block 288 = 8 decode warps + 1 copy warp.
+// part[slot][sp][t][n]; xh16 [slot][T][k] f16, xinv [slot][T][k/128].
+template <bool K3>
+__global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long* __restrict__ ptrs, const uint16_t* __restrict__ xh,
+                                                        const float* __restrict__ xinv, float* __restrict__ part, Mul1Spec sp_, int S, int T) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int slot = blockIdx.z, sp = blockIdx.y;
+    const unsigned long long rec = ptrs[slot];
+    if (rec == 0ull) return;  // uniform, before any barrier
+    const int k = sp_.k, n = sp_.n, n32 = sp_.n32;
+    const int tiles_n = n >> 4, tps = (k >> 4) / S, kb0 = sp * tps, rows = tps * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb0 = blockIdx.x * 8;
+    const int run_bytes = 32 * n32;  // 8 tiles of one tile row
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = full + RING;
+    uint32_t* ring = (uint32_t*)(smem + 128);                                   // [RING][UROWS][8][n32]
+    uint16_t* xs = (uint16_t*)(smem + 128 + (size_t)RING * UROWS * run_bytes);  // [T][rows] f16
+    float* xi = (float*)(xs + (size_t)T * rows + ((T * rows) & 1));             // [T][rows/128]
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RING; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 8);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const int nst = (tps + UROWS - 1) / UROWS;
+    if (warp == 8) {
+        const uint8_t* base = (const uint8_t*)(rec + (unsigned long long)sp_.tr_off);
+        if (((uintptr_t)base & 15) != 0) {
+            cn_dev_fail(103);  // a trellis that is not 16-byte aligned cannot be bulk-copied
+            return;
+        }
+        for (int c = 0; c < nst; c++) {
+            const int s = c % RING;
+            if (c >= RING && !mbar_wait(&empty[s], ((c / RING) - 1) & 1)) {
+                cn_dev_fail(CN_DEV_WAIT_EMPTY);
+                return;
+            }
+            const int live = min(UROWS, tps - c * UROWS);
+            if (lane == 0) {
+                mbar_expect_tx(&full[s], (uint32_t)(live * run_bytes));
+                mbar_arrive(&full[s]);
+            }
+            __syncwarp();
+            if (lane < live) {
+                const size_t off = ((size_t)(kb0 + c * UROWS + lane) * tiles_n + nb0) * n32 * 4;
+                bulk_g2s((uint8_t*)ring + ((size_t)s * UROWS + lane) * run_bytes, base + off, (uint32_t)run_bytes, &full[s]);
+            }
+        }
+        return;
+    }
+    // the activation rows of this k-split, and their block scales
+    for (int i = threadIdx.x; i < T * rows / 2; i += 256) {
+        const int t = i / (rows / 2), r = i - t * (rows / 2);
+        ((uint32_t*)xs)[i] = ((const uint32_t*)(xh + ((size_t)slot * T + t) * k + (size_t)kb0 * 16))[r];
+    }
+    const int nblk = rows / 128;
+    for (int i = threadIdx.x; i < T * nblk; i += 256) {
+        const int t = i / nblk, b = i - t * nblk;
+        xi[i] = xinv[((size_t)slot * T + t) * (k / 128) + kb0 / 8 + b];
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+
+    int lo[8];
+    const int sbits = n32 * 32;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int tpos = 8 * lane + j;
+        const int eb = !sp_.half ? (tpos + 1) * sp_.bits : ((tpos & 1) ? (tpos / 2 + 1) * (2 * sp_.bits + 1) : (tpos / 2) * (2 * sp_.bits + 1) + sp_.bits);
+        lo[j] = (eb - 16 + sbits) % sbits;
+    }
+    const int wi0 = lo[0] >> 5, sh0 = lo[0] & 31;
+    const int q2 = 2 * (lane & 3);
+    float tot0[MUL1_MAXT], tot1[MUL1_MAXT];
+#pragma unroll
+    for (int t = 0; t < MUL1_MAXT; t++) tot0[t] = tot1[t] = 0.0f;
+    float a0e[MUL1_MAXT], a0o[MUL1_MAXT], a1e[MUL1_MAXT], a1o[MUL1_MAXT];
+#pragma unroll
+    for (int t = 0; t < MUL1_MAXT; t++) a0e[t] = a0o[t] = a1e[t] = a1o[t] = 0.0f;
+    for (int c = 0; c < nst; c++) {
+        const int s = c % RING;
+        if (!mbar_wait(&full[s], (c / RING) & 1)) {
+            cn_dev_fail(CN_DEV_WAIT_FULL);
+            return;
+        }
+        const int live = min(UROWS, tps - c * UROWS);
+        for (int u = 0; u < live; u++) {
+            const int kt = c * UROWS + u;  // tile row within the split
+            const uint32_t* tile = ring + ((size_t)(s * UROWS + u) * 8 + warp) * n32;
+            uint32_t st[8];
+            lane_states<K3>(tile, n32, lo, wi0, sh0, st);
+            const uint32_t w01 = mul1_pair(st[0], st[1]), w23 = mul1_pair(st[2], st[3]);
+            const uint32_t w45 = mul1_pair(st[4], st[5]), w67 = mul1_pair(st[6], st[7]);
+#pragma unroll
+            for (int t = 0; t < MUL1_MAXT; t++) {
+                if (t < T) {
+                    const uint32_t* xr = (const uint32_t*)(xs + (size_t)t * rows + kt * 16 + q2);
+                    const uint32_t x01 = xr[0], x89 = xr[4];
+                    fma2_f16_f32(a0e[t], a0o[t], w01, x01);
+                    fma2_f16_f32(a0e[t], a0o[t], w23, x89);
+                    fma2_f16_f32(a1e[t], a1o[t], w45, x01);
+                    fma2_f16_f32(a1e[t], a1o[t], w67, x89);
+                }
+            }
+            if ((kt & 7) == 7) {
+                // end of a 128-row block: undo its activation scale
+#pragma unroll
+                for (int t = 0; t < MUL1_MAXT; t++) {
+                    if (t < T) {
+                        const float inv = xi[t * nblk + (kt >> 3)];
+                        tot0[t] = fmaf(a0e[t] + a0o[t], inv, tot0[t]);
+                        tot1[t] = fmaf(a1e[t] + a1o[t], inv, tot1[t]);
+                        a0e[t] = a0o[t] = a1e[t] = a1o[t] = 0.0f;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    // the four lanes of a column (g % 4): two xor-shuffle adds, then one store per column
+#pragma unroll
+    for (int t = 0; t < MUL1_MAXT; t++) {
+        if (t < T) {
+            float a = tot0[t], b = tot1[t];
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+            b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 1));
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+            b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 2));
+            if ((lane & 3) == 0) {
+                float* pp = part + (((size_t)slot * S + sp) * T + t) * n + (size_t)(nb0 + warp) * 16 + (lane >> 2);
+                pp[0] = a;
+                pp[8] = b;
+            }
+        }
+    }
+}
+
+// v = H128(sum_sp part[slot][sp][t][blk*128 ..]) / 128 * svh
+__device__ __forceinline__ void out_block(float v[4], const float* __restrict__ part, const uint16_t* __restrict__ svh, int slot, int S, int T,
+                                          int t, int n, int blk, int lane) {
+    const int c0 = blk * 128 + 4 * lane;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        float s = part[(((size_t)slot * S + 0) * T + t) * n + c0 + j];
+        for (int q = 1; q < S; q++) s = __fadd_rn(s, part[(((size_t)slot * S + q) * T + t) * n + c0 + j]);
+        v[j] = s;
+    }
+    fwht128(v, lane);
+#pragma unroll
+    for (int j = 0; j < 4; j++) v[j] = __fmul_rn(__fmul_rn(v[j], 0.0078125f), h2f(svh[c0 + j]));
+}
+
+// grid (n/128, T, slots), block 32. YT: 0 f32, 1 bf16 output; y row = slot * T + t
+template <int YT>
+__global__ void mul1_had_out_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part, void* __restrict__ y, int n,
+                                    int S, int T, long long svh_off) {
+    const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
+    if (ptrs[slot] == 0ull) return;
+    float v[4];
+    out_block(v, part, (const uint16_t*)(ptrs[slot] + (unsigned long long)svh_off), slot, S, T, t, n, blk, lane);
+    const size_t at = ((size_t)slot * T + t) * n + blk * 128 + 4 * lane;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (YT == 1)
+            ((__nv_bfloat16*)y)[at + j] = __float2bfloat16_rn(v[j]);
+        else
+            ((float*)y)[at + j] = v[j];
+    }
+}
+
+// The middle of the FFN in one launch: had_out of gate and of up, h = act(g, u), had_in of down.
+// grid (inter/128, T, slots), block 32.
+__global__ void mul1_act_had_in_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part_g,
+                                       const float* __restrict__ part_u, uint16_t* __restrict__ xh_d, float* __restrict__ xinv_d, int inter, int S,
+                                       int T, long long svh_g, long long svh_u, long long suh_d, float limit) {
+    const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
+    if (ptrs[slot] == 0ull) return;
+    float g[4], u[4], v[4];
+    out_block(g, part_g, (const uint16_t*)(ptrs[slot] + (unsigned long long)svh_g), slot, S, T, t, inter, blk, lane);
+    out_block(u, part_u, (const uint16_t*)(ptrs[slot] + (unsigned long long)svh_u), slot, S, T, t, inter, blk, lane);
+    const uint16_t* suh = (const uint16_t*)(ptrs[slot] + (unsigned long long)suh_d);
+    const int c0 = blk * 128 + 4 * lane;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        float gv = g[j], uv = u[j];
+        if (limit > 0.0f) {
+            gv = gv > limit ? limit : gv;
+            uv = uv > limit ? limit : (uv < -limit ? -limit : uv);
+        }
+        const float h = __fmul_rn(gv / (1.0f + expf(-gv)), uv);
+        v[j] = __fmul_rn(h, h2f(suh[c0 + j]));
+    }
+    fwht128(v, lane);
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float inv;
+    const float mul = block_scale(amax, inv);
+    const __half2 h0 = __floats2half2_rn(v[0] * mul, v[1] * mul), h1 = __floats2half2_rn(v[2] * mul, v[3] * mul);
+    const size_t row = ((size_t)slot * T + t) * inter;
+    *(uint2*)(xh_d + row + c0) = make_uint2(*(const uint32_t*)&h0, *(const uint32_t*)&h1);
+    if (lane == 0) xinv_d[((size_t)slot * T + t) * (inter / 128) + blk] = inv;
+}
+
+// W_hat as fp16 bits, row major [k][n]: one thread per (tile, position) - the codec self-check
+__global__ void mul1_reconstruct_kernel(const uint32_t* __restrict__ trellis, uint16_t* __restrict__ w, int k, int n, int bits, int half, int n32) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)(k / 16) * (n / 16) * 256;
+    if (i >= total) return;
+    const int p = (int)(i & 255);
+    const long long tile = i >> 8;
+    const int kb = (int)(tile / (n / 16)), nb = (int)(tile % (n / 16));
+    const int sbits = n32 * 32;
+    const int eb = !half ? (p + 1) * bits : ((p & 1) ? (p / 2 + 1) * (2 * bits + 1) : (p / 2) * (2 * bits + 1) + bits);
+    const int lo = (eb - 16 + sbits) % sbits;
+    const uint32_t* t = trellis + tile * n32;
+    const int wi = lo >> 5, o = lo & 31, w1 = wi + 1 == n32 ? 0 : wi + 1;
+    const uint32_t st = __funnelshift_l(t[w1], t[wi], o) >> 16;
+    const uint32_t pr = mul1_pair(st, st);
+    const int lane = p >> 3, j = p & 7;
+    const int off[4] = {0, 1, 8, 9};
+    const int row = 2 * (lane & 3) + off[j & 3], col = (lane >> 2) + 8 * (j >> 2);
+    w[(size_t)(kb * 16 + row) * n + nb * 16 + col] = (uint16_t)(pr & 0xffff);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- host side
+namespace {
+
+struct Mul1Plan {
+    int hidden, inter, bits, half, n32, max_slots, max_t;
+    size_t kmax;
+    uint16_t *xh_a, *xh_b;  // [slots][T][kmax] f16
+    float *xinv_a, *xinv_b;  // [slots][T][kmax/128]
+    float *part_a, *part_b;  // [slots][16][T][kmax]
+    unsigned long long* ptrs;  // [slots] gathered record addresses (MoE form)
+    float* eo;                 // [slots][T][hidden] expert outputs (MoE form)
+};
+
+int ksplit(int k) {
+    // the largest divisor of k/128 that is <= 16: k-splits end on Hadamard blocks
+    const int blocks = k / 128;
+    for (int s = 16; s >= 1; s--)
+        if (blocks % s == 0) return s;
+    return 1;
+}
+
+long long trellis_bytes(int k, int n, int n32) { return (long long)(k / 16) * (n / 16) * n32 * 4; }
+
+Mul1Spec spec_of(const Mul1Plan* p, int which) {
+    const long long tb = trellis_bytes(p->hidden, p->inter, p->n32), h2 = 2LL * p->hidden, i2 = 2LL * p->inter;
+    Mul1Spec s;
+    s.bits = p->bits, s.half = p->half, s.n32 = p->n32;
+    if (which == 0) s.k = p->hidden, s.n = p->inter, s.tr_off = 0, s.suh_off = 3 * tb, s.svh_off = 3 * tb + h2;
+    if (which == 1) s.k = p->hidden, s.n = p->inter, s.tr_off = tb, s.suh_off = 3 * tb + h2 + i2, s.svh_off = 3 * tb + 2 * h2 + i2;
+    if (which == 2) s.k = p->inter, s.n = p->hidden, s.tr_off = 2 * tb, s.suh_off = 3 * tb + 2 * h2 + 2 * i2, s.svh_off = 3 * tb + 2 * h2 + 3 * i2;
+    return s;
+}
+
+int launch_had_in(const unsigned long long* ptrs, const void* x, uint16_t* xh, float* xinv, const Mul1Spec& s, int slots, int T, int x_div,
+                  int dtype, cudaStream_t st) {
+    dim3 grid(s.k / 128, T, slots);
+    if (dtype == CN_BF16)
+        mul1_had_in_kernel<1><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div);
+    else
+        mul1_had_in_kernel<0><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float* xinv, float* part, const Mul1Spec& s, int slots, int T,
+                cudaStream_t st) {
+    const int S = ksplit(s.k), tps = (s.k / 16) / S, rows = tps * 16;
+    const size_t smem = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)T * rows * 2 + 8 + (size_t)T * (rows / 128) * 4;
+    dim3 grid(s.n / 128, S, slots);
+    static bool attr = false;
+    if (!attr) {
+        CN_CUDA(cudaFuncSetAttribute(mul1_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        CN_CUDA(cudaFuncSetAttribute(mul1_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        attr = true;
+    }
+    if (smem > 160 * 1024) CN_FAIL(CN_ERR_LIMIT, "mul1 gemv: %zu B of shared memory per block", smem);
+    if (s.bits == 3 && !s.half)
+        mul1_gemv_kernel<true><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T);
+    else
+        mul1_gemv_kernel<false><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+int check_run(const Mul1Plan* p, int slots, int T, const char* who) {
+    if (!p) CN_FAIL(CN_ERR_SHAPE, "%s: null plan", who);
+    if (slots < 1 || slots > p->max_slots || T < 1 || T > p->max_t)
+        CN_FAIL(CN_ERR_LIMIT, "%s: %d slots x %d rows, the plan holds %d x %d", who, slots, T, p->max_slots, p->max_t);
+    return CN_OK;
+}
+
+__global__ void mul1_gather_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ ids, unsigned long long* ptrs, int n) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < n) ptrs[c] = ids[c] < 0 ? 0ull : table[ids[c]];
+}
+
+}  // namespace
+
+extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int bits, int half, int max_slots, int max_t) {
+    if (!plan_out || hidden <= 0 || inter <= 0 || hidden % 128 || inter % 128)
+        CN_FAIL(CN_ERR_SHAPE, "cn_mul1_plan_create: [%d, %d] is not a positive multiple of 128 on both sides", hidden, inter);
+    if (bits < 1 || bits > 8 || (half && bits > 3)) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_plan_create: unsupported bitrate %d%s", bits, half ? ".5" : "");
+    if (max_slots < 1 || max_t < 1 || max_t > MUL1_MAXT) CN_FAIL(CN_ERR_LIMIT, "cn_mul1_plan_create: %d slots, %d rows (rows <= %d)", max_slots, max_t, MUL1_MAXT);
+    Mul1Plan* p = new Mul1Plan();
+    p->hidden = hidden, p->inter = inter, p->bits = bits, p->half = half, p->n32 = 8 * bits + (half ? 4 : 0), p->max_slots = max_slots, p->max_t = max_t;
+    p->kmax = hidden > inter ? hidden : inter;
+    const size_t rows = (size_t)max_slots * max_t;
+    CN_CUDA(cudaMalloc(&p->xh_a, rows * p->kmax * 2));
+    CN_CUDA(cudaMalloc(&p->xh_b, rows * p->kmax * 2));
+    CN_CUDA(cudaMalloc(&p->xinv_a, rows * (p->kmax / 128) * 4));
+    CN_CUDA(cudaMalloc(&p->xinv_b, rows * (p->kmax / 128) * 4));
+    CN_CUDA(cudaMalloc(&p->part_a, rows * 16 * p->kmax * 4));
+    CN_CUDA(cudaMalloc(&p->part_b, rows * 16 * p->kmax * 4));
+    CN_CUDA(cudaMalloc(&p->ptrs, (size_t)max_slots * 8));
+    CN_CUDA(cudaMalloc(&p->eo, rows * hidden * 4));
+    *plan_out = p;
+    return CN_OK;
+}
+
+extern "C" int cn_mul1_plan_destroy(void* plan) {
+    Mul1Plan* p = (Mul1Plan*)plan;
+    if (!p) return CN_OK;
+    cudaFree(p->xh_a), cudaFree(p->xh_b), cudaFree(p->xinv_a), cudaFree(p->xinv_b), cudaFree(p->part_a), cudaFree(p->part_b), cudaFree(p->ptrs),
+        cudaFree(p->eo);
+    delete p;
+    return CN_OK;
+}
+
+extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, int dtype,
+                            cn_stream_t stream) {
+    Mul1Plan* p = (Mul1Plan*)plan;
+    if (int rc = check_run(p, slots, t, "cn_mul1_gemv")) return rc;
+    if (which < 0 || which > 2 || x_div < 1) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv: matrix %d (0 gate, 1 up, 2 down), x_div %d", which, x_div);
+    cudaStream_t st = (cudaStream_t)stream;
+    const Mul1Spec s = spec_of(p, which);
+    if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, s, slots, t, x_div, dtype, st)) return rc;
+    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, s, slots, t, st)) return rc;
+    dim3 grid(s.n / 128, t, slots);
+    if (dtype == CN_BF16)
+        mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off);
+    else
+        mul1_had_out_kernel<0><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+// y[slot][t] = down(act(gate x, up x)) as f32 when out_f32, else in `dtype`
+static int mul1_ffn(Mul1Plan* p, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, float limit, int dtype,
+                    int out_f32, cudaStream_t st) {
+    const Mul1Spec g = spec_of(p, 0), u = spec_of(p, 1), d = spec_of(p, 2);
+    if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, st)) return rc;
+    if (int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, st)) return rc;
+    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, st)) return rc;
+    if (int rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, st)) return rc;
+    mul1_act_had_in_kernel<<<dim3(p->inter / 128, t, slots), 32, 0, st>>>(ptrs, p->part_a, p->part_b, p->xh_a, p->xinv_a, p->inter, ksplit(p->hidden), t,
+                                                                         g.svh_off, u.svh_off, d.suh_off, limit);
+    CN_CUDA(cudaGetLastError());
+    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, d, slots, t, st)) return rc;
+    dim3 grid(d.n / 128, t, slots);
+    if (dtype == CN_BF16 && !out_f32)
+        mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off);
+    else
+        mul1_had_out_kernel<0><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+extern "C" int cn_mul1_ffn(void* plan, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, float limit, int dtype,
+                           cn_stream_t stream) {
+    Mul1Plan* p = (Mul1Plan*)plan;
+    if (int rc = check_run(p, slots, t, "cn_mul1_ffn")) return rc;
+    if (x_div < 1) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_ffn: x_div %d", x_div);
+    return mul1_ffn(p, ptrs, x, y, slots, t, x_div, limit, dtype, 0, (cudaStream_t)stream);
+}
+
+extern "C" int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const unsigned long long* table, const float* shared,
+                              const float* sgate, void* y, int tokens, int hidden, int topk, int dtype, cn_stream_t stream);
+
+extern "C" int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared, const void* x,
+                               void* y, int tokens, int topk, float limit, int dtype, cn_stream_t stream) {
+    Mul1Plan* p = (Mul1Plan*)plan;
+    const int combos = tokens * topk;
+    if (int rc = check_run(p, combos, 1, "cn_moe_mul1_run")) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    mul1_gather_kernel<<<(combos + 127) / 128, 128, 0, st>>>(table, ids, p->ptrs, combos);
+    CN_CUDA(cudaGetLastError());
+    if (int rc = mul1_ffn(p, p->ptrs, x, p->eo, combos, 1, topk, limit, dtype, 1, st)) return rc;
+    return cn_moe_combine(p->eo, wts, ids, table, shared, nullptr, y, tokens, p->hidden, topk, dtype, stream);
+}
+
+extern "C" int cn_mul1_reconstruct(const void* trellis, void* w_out, int k, int n, int bits, int half, cn_stream_t stream) {
+    if (k <= 0 || n <= 0 || k % 16 || n % 16) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_reconstruct: [%d, %d] is not a multiple of 16", k, n);
+    const int n32 = 8 * bits + (half ? 4 : 0);
+    const long long total = (long long)(k / 16) * (n / 16) * 256;
+    mul1_reconstruct_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint32_t*)trellis, (uint16_t*)w_out, k, n, bits, half, n32);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}

@@ -25,6 +25,7 @@
 #include <cstdio>
 
 #include "common.cuh"
+#include "nvfp4_gemv.cuh"
 
 namespace {
 
@@ -49,6 +50,16 @@ struct GemvParams {
     float limit;
     int tx;      // lanes across K per row: 16, 8 or 4
     int stages;  // ring depth
+    int out_f32;  // store f32 whatever the activation type (MoE intermediates)
+    // routed-expert form (ids != null): blockIdx.y walks the combos, combo c = t * topk + j reads the
+    // matrix of expert ids[c] from a device pointer table (a null entry skips the combo), activation
+    // row c / x_div, output row c
+    const int32_t* ids;
+    const int32_t* order;           // combos sorted by expert (null: identity)
+    const unsigned long long* tab0;  // [experts] plain matrix or gate (or the fused gate|up slab)
+    const unsigned long long* tab1;  // [experts] up (null with a fused slab or a plain matrix)
+    int fused_up_rows;               // > 0: up = gate + fused_up_rows rows of the same slab
+    int x_div;
 };
 
 __device__ __forceinline__ float act_gu(float g, float u, float limit) {
@@ -102,8 +113,22 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
     const int bpr = p.k >> 6;
     const size_t row_bytes = (size_t)bpr * 36;
     const int nchunks = bpr / TX;
-    const bool gu = p.w1 != nullptr;
     const int S = p.stages;
+    const uint8_t* w0 = p.w0;
+    const uint8_t* w1 = p.w1;
+    const char* xbase = (const char*)p.x;
+    char* ybase = (char*)p.y;
+    if (p.ids) {
+        const int c = p.order ? p.order[blockIdx.y] : (int)blockIdx.y;
+        const int e = p.ids[c];
+        if (e < 0) return;  // uniform over the CTA, before any barrier
+        w0 = (const uint8_t*)p.tab0[e];
+        if (!w0) return;  // the expert is not resident here: nothing to read or write
+        w1 = p.tab1 ? (const uint8_t*)p.tab1[e] : (p.fused_up_rows > 0 ? w0 + (size_t)p.fused_up_rows * row_bytes : nullptr);
+        xbase += (size_t)(c / p.x_div) * p.k * (XT == 1 ? 2 : 4);
+        ybase += (size_t)c * p.ldy * ((XT == 1 && !p.out_f32) ? 2 : 4);
+    }
+    const bool gu = w1 != nullptr;
 
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + MAX_STAGES;
@@ -151,7 +176,7 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
             if (sl < ROWS) {
                 const int j = sl / G, g = sl % G;
                 const int r = gu ? row0 + (j >> 1) * G + g : row0 + sl;
-                const uint8_t* base = (gu && (j & 1)) ? p.w1 : p.w0;
+                const uint8_t* base = (gu && (j & 1)) ? w1 : w0;
                 if (r < p.rows) src[i] = base + (size_t)r * row_bytes;
             }
             total += src[i] ? piece : 0;
@@ -194,7 +219,7 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
                 const int m = gq / (bpr * 8), gi = gq % (bpr * 8);
                 raw[b].a = make_uint4(0, 0, 0, 0);
                 raw[b].b = make_uint4(0, 0, 0, 0);
-                if (gq < groups && m < p.m) load_x8<XT>(p.x, (size_t)m * p.k + (size_t)gi * 8, raw[b]);
+                if (gq < groups && m < p.m) load_x8<XT>(xbase, (size_t)m * p.k + (size_t)gi * 8, raw[b]);
             }
 #pragma unroll
             for (int b = 0; b < BATCH; b++) {
@@ -362,10 +387,10 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
 #pragma unroll
                     for (int m = 0; m < MP; m++)
                         if (m < p.m) {
-                            if (XT == 1)
-                                ((__nv_bfloat16*)p.y)[(size_t)m * p.ldy + row] = __float2bfloat16_rn(acc[r][m]);
+                            if (XT == 1 && !p.out_f32)
+                                ((__nv_bfloat16*)ybase)[(size_t)m * p.ldy + row] = __float2bfloat16_rn(acc[r][m]);
                             else
-                                ((float*)p.y)[(size_t)m * p.ldy + row] = acc[r][m];
+                                ((float*)ybase)[(size_t)m * p.ldy + row] = acc[r][m];
                         }
                 }
             }
@@ -378,10 +403,10 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
                     for (int m = 0; m < MP; m++)
                         if (m < p.m) {
                             const float h = act_gu(acc[r][m], acc[r + 1][m], p.limit);
-                            if (XT == 1)
-                                ((__nv_bfloat16*)p.y)[(size_t)m * p.ldy + row] = __float2bfloat16_rn(h);
+                            if (XT == 1 && !p.out_f32)
+                                ((__nv_bfloat16*)ybase)[(size_t)m * p.ldy + row] = __float2bfloat16_rn(h);
                             else
-                                ((float*)p.y)[(size_t)m * p.ldy + row] = h;
+                                ((float*)ybase)[(size_t)m * p.ldy + row] = h;
                         }
                 }
             }
@@ -411,7 +436,7 @@ __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ w, const float*
 int g_tune_mode = 0, g_tune_rt = 0, g_tune_stages = 0, g_tune_pdl = 1;
 
 template <int XT, int MP, int RT, int MODE>
-int launch_one(const GemvParams& p, int grid, size_t smem, cudaStream_t stream) {
+int launch_one(const GemvParams& p, int grid, int gy, size_t smem, cudaStream_t stream) {
     static bool attr_done = false;
     auto kern = nvfp4_gemv_kernel<XT, MP, RT, MODE>;
     if (!attr_done) {
@@ -419,7 +444,7 @@ int launch_one(const GemvParams& p, int grid, size_t smem, cudaStream_t stream) 
         attr_done = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)grid, (unsigned)gy);
     cfg.blockDim = dim3(NTHREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -433,35 +458,41 @@ int launch_one(const GemvParams& p, int grid, size_t smem, cudaStream_t stream) 
 }
 
 template <int XT, int MODE>
-int launch_m(const GemvParams& p, int mp, int rt, int grid, size_t smem, cudaStream_t stream) {
+int launch_m(const GemvParams& p, int mp, int rt, int grid, int gy, size_t smem, cudaStream_t stream) {
 #define CN_CASE(MPV, RTV) \
-    if (mp == MPV && rt == RTV) return launch_one<XT, MPV, RTV, MODE>(p, grid, smem, stream);
+    if (mp == MPV && rt == RTV) return launch_one<XT, MPV, RTV, MODE>(p, grid, gy, smem, stream);
     CN_CASE(1, 2) CN_CASE(1, 4) CN_CASE(2, 2) CN_CASE(2, 4) CN_CASE(4, 2) CN_CASE(4, 4) CN_CASE(8, 2) CN_CASE(8, 4)
 #undef CN_CASE
     CN_FAIL(CN_ERR_SHAPE, "nvfp4 gemv: no kernel for m %d, rows per thread %d", mp, rt);
 }
 
-int gemv_common(const void* w0, const void* w1, const float* gs0, const float* gs1, const void* x, void* y, int rows, int k, int m,
-                int ldy, float limit, int dtype, cudaStream_t stream, const char* who) {
+}  // namespace
+
+// One launch of the GEMV family (declared in nvfp4_gemv.cuh for the MoE operator).
+int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
+    const int rows = a.rows, k = a.k, m = a.m;
     if (rows <= 0 || k <= 0 || k % 256 != 0) CN_FAIL(CN_ERR_SHAPE, "%s: k = %d must be a positive multiple of 256 (rows of 16-byte multiples)", who, k);
     if (m < 1 || m > CN_MAX_M) CN_FAIL(CN_ERR_LIMIT, "%s: m = %d, the kernel takes 1..%d activation rows", who, m, CN_MAX_M);
-    if (ldy < rows) CN_FAIL(CN_ERR_SHAPE, "%s: ldy %d < rows %d", who, ldy, rows);
-    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "%s: dtype %d is neither CN_F32 nor CN_BF16", who, dtype);
-    if (((uintptr_t)w0 & 15) || ((uintptr_t)w1 & 15) || ((uintptr_t)x & 15))
+    if (a.ldy < rows) CN_FAIL(CN_ERR_SHAPE, "%s: ldy %d < rows %d", who, a.ldy, rows);
+    if (a.dtype != CN_F32 && a.dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "%s: dtype %d is neither CN_F32 nor CN_BF16", who, a.dtype);
+    if (((uintptr_t)a.w0 & 15) || ((uintptr_t)a.w1 & 15) || ((uintptr_t)a.x & 15))
         CN_FAIL(CN_ERR_SHAPE, "%s: weight and activation pointers must be 16-byte aligned", who);
+    const bool routed = a.ids != nullptr;
+    if (routed && (m != 1 || a.combos < 1 || a.x_div < 1)) CN_FAIL(CN_ERR_SHAPE, "%s: the routed form takes one row per combo", who);
+    const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;
     const int bpr = k / 64;
     const int tx = bpr % 16 == 0 ? 16 : (bpr % 8 == 0 ? 8 : 4);
     const int mp = m == 1 ? 1 : (m == 2 ? 2 : (m <= 4 ? 4 : 8));
-    int mode = dtype == CN_BF16 ? 1 : 0;
+    // f32 activations keep exact f32 arithmetic unless the caller allows rounding them to f16 at staging
+    int mode = (a.dtype == CN_BF16 || a.x_f16_ok) ? 1 : 0;
     if (g_tune_mode == 1) mode = 0;
-    if (g_tune_mode == 2 && dtype == CN_BF16) mode = 1;
     const int G = NW * (32 / tx);
     int rt = 4;
-    const long long slots = (long long)rows * (w1 ? 2 : 1);
+    const long long slots = (long long)rows * (gu ? 2 : 1) * (routed ? a.combos : 1);
     if (slots / (G * 4) < 2 * 148) rt = 2;
     if (g_tune_rt == 2 || g_tune_rt == 4) rt = g_tune_rt;
     const int ROWS = G * rt;
-    const int per_cta = w1 ? ROWS / 2 : ROWS;
+    const int per_cta = gu ? ROWS / 2 : ROWS;
     const int grid = (rows + per_cta - 1) / per_cta;
     const int xb = mode == 1 ? XB_F16 : XB_F32;
     const size_t stage_bytes = (size_t)ROWS * tx * 36;
@@ -479,30 +510,38 @@ int gemv_common(const void* w0, const void* w1, const float* gs0, const float* g
         // (each row's arithmetic is the same whatever the split, so results do not change)
         if (m == 1) CN_FAIL(CN_ERR_LIMIT, "%s: k = %d needs %zu B of shared memory per block", who, k, smem);
         const int m0 = m / 2;
-        const size_t es = dtype == CN_BF16 ? 2 : 4;
-        int rc = gemv_common(w0, w1, gs0, gs1, x, y, rows, k, m0, ldy, limit, dtype, stream, who);
-        if (rc) return rc;
-        return gemv_common(w0, w1, gs0, gs1, (const char*)x + (size_t)m0 * k * es, (char*)y + (size_t)m0 * ldy * es, rows, k, m - m0, ldy,
-                           limit, dtype, stream, who);
+        const size_t es = a.dtype == CN_BF16 ? 2 : 4, eso = (a.dtype == CN_BF16 && !a.out_f32) ? 2 : 4;
+        GemvCall lo = a, hi = a;
+        lo.m = m0;
+        hi.m = m - m0;
+        hi.x = (const char*)a.x + (size_t)m0 * k * es;
+        hi.y = (char*)a.y + (size_t)m0 * a.ldy * eso;
+        int rc = cn_gemv_launch(lo, stream, who);
+        return rc ? rc : cn_gemv_launch(hi, stream, who);
     }
     GemvParams p;
-    p.w0 = (const uint8_t*)w0, p.w1 = (const uint8_t*)w1, p.gs0 = gs0, p.gs1 = gs1, p.x = x, p.y = y;
-    p.rows = rows, p.k = k, p.m = m, p.ldy = ldy, p.limit = limit, p.tx = tx, p.stages = stages;
-    if (dtype == CN_BF16) return mode == 1 ? launch_m<1, 1>(p, mp, rt, grid, smem, stream) : launch_m<1, 0>(p, mp, rt, grid, smem, stream);
-    return launch_m<0, 0>(p, mp, rt, grid, smem, stream);
+    p.w0 = (const uint8_t*)a.w0, p.w1 = (const uint8_t*)a.w1, p.gs0 = a.gs0, p.gs1 = a.gs1 ? a.gs1 : a.gs0, p.x = a.x, p.y = a.y;
+    p.rows = rows, p.k = k, p.m = m, p.ldy = a.ldy, p.limit = a.limit, p.tx = tx, p.stages = stages, p.out_f32 = a.out_f32;
+    p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
+    const int gy = routed ? a.combos : 1;
+    if (a.dtype == CN_BF16) return mode == 1 ? launch_m<1, 1>(p, mp, rt, grid, gy, smem, stream) : launch_m<1, 0>(p, mp, rt, grid, gy, smem, stream);
+    return mode == 1 ? launch_m<0, 1>(p, mp, rt, grid, gy, smem, stream) : launch_m<0, 0>(p, mp, rt, grid, gy, smem, stream);
 }
-
-}  // namespace
 
 extern "C" int cn_nvfp4_gemv(const void* w, const float* gs, const void* x, void* y, int rows, int k, int m, int ldy, int dtype,
                              cn_stream_t stream) {
-    return gemv_common(w, nullptr, gs, nullptr, x, y, rows, k, m, ldy, 0.0f, dtype, (cudaStream_t)stream, "cn_nvfp4_gemv");
+    GemvCall a = {};
+    a.w0 = w, a.gs0 = gs, a.x = x, a.y = y, a.rows = rows, a.k = k, a.m = m, a.ldy = ldy, a.dtype = dtype;
+    return cn_gemv_launch(a, (cudaStream_t)stream, "cn_nvfp4_gemv");
 }
 
 extern "C" int cn_nvfp4_gemv_gu(const void* wg, const void* wu, const float* gs_g, const float* gs_u, const void* x, void* h, int inter,
                                 int k, int m, int ldh, float limit, int dtype, cn_stream_t stream) {
     if (!wu) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_gu: the up matrix is null");
-    return gemv_common(wg, wu, gs_g, gs_u, x, h, inter, k, m, ldh, limit, dtype, (cudaStream_t)stream, "cn_nvfp4_gemv_gu");
+    GemvCall a = {};
+    a.w0 = wg, a.w1 = wu, a.gs0 = gs_g, a.gs1 = gs_u, a.x = x, a.y = h, a.rows = inter, a.k = k, a.m = m, a.ldy = ldh, a.limit = limit,
+    a.dtype = dtype;
+    return cn_gemv_launch(a, (cudaStream_t)stream, "cn_nvfp4_gemv_gu");
 }
 
 extern "C" int cn_nvfp4_dequant(const void* w, const float* gs, float* out, int rows, int k, int rule, cn_stream_t stream) {

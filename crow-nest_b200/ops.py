@@ -91,3 +91,19 @@ def dequant(w: Fp4, rule=False):
     out = torch.empty((w.rows, w.cols), dtype=torch.float32, device=w.w.device)
     check(lib().cn_nvfp4_dequant(w.w.data_ptr(), w.gs.data_ptr(), out.data_ptr(), w.rows, w.cols, int(rule), _stream()))
     return out
+
+
+def fp8_gemv(w, scale, x, rows, cols, y=None):
+    """y[m][r] for E4M3FN weights [rows][cols] (uint8) with f32 scales per 128x128 tile
+    (the codec of converter/src/fp8.rs:44-82); x [M][cols], M <= 8."""
+    x2 = x.reshape(-1, cols)
+    m = x2.shape[0]
+    if w.numel() != rows * cols:
+        raise CrownestError(f"fp8: {w.numel()} FP8 bytes for shape [{rows}, {cols}]")
+    sr, sc = -(-rows // 128), -(-cols // 128)
+    if scale.numel() != sr * sc:
+        raise CrownestError(f"fp8: {scale.numel()} scales, the 128x128 grid of [{rows}, {cols}] needs [{sr}, {sc}] = {sr * sc}")
+    if y is None:
+        y = torch.empty((m, rows), dtype=x.dtype, device=x.device)
+    check(lib().cn_fp8_gemv(w.data_ptr(), scale.data_ptr(), x2.data_ptr(), y.data_ptr(), rows, cols, m, y.stride(0), _dtype_code(x), _stream()))
+    return y

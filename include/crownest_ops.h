@@ -84,6 +84,95 @@ int cn_nvfp4_gemv_gu(const void* wg, const void* wu, const float* gs_g, const fl
  * (engine/src/cnq.rs:1298). rule != 0 reads 0x7F as 0x7E first (the GEMV's reading). */
 int cn_nvfp4_dequant(const void* w, const float* gs, float* out, int rows, int k, int rule, cn_stream_t stream);
 
+/* ---------------------------------------------------------------- MoE routing
+ * Softmax top-k (Flash-Next): p = softmax(logits[t]); k rounds of "largest p, lowest index on
+ * ties"; wts = p_j / (sum of the picked p, in pick order). Replaces the selection half of
+ * router_top10 (engine/src/kernels.rs:3109-3171). logits [tokens][experts] f32; ids, wts
+ * [tokens][k] in pick order. experts <= 1024, k <= 64. */
+int cn_route_softmax_topk(const float* logits, int32_t* ids, float* wts, int tokens, int experts, int k, cn_stream_t stream);
+
+/* Sigmoid top-k (GLM): s = sigmoid(logit); choice = s + bias (NaN -> -inf; bias may be null);
+ * wts = s / (sum_picked s + 1e-20) * scale. Replaces glm5_router_sig_topk
+ * (engine/src/kernels_glm5_moe.cu:44-96), host twin glm5_moe::route_from_logits
+ * (engine/src/glm5_moe.rs:196-236). */
+int cn_route_sigmoid_topk(const float* logits, const float* bias, int32_t* ids, float* wts, int tokens, int experts, int k,
+                          float scale, cn_stream_t stream);
+
+/* ---------------------------------------------------------------- routed NVFP4 experts
+ * order[] = the combos 0..combos-1 sorted by expert id (stable; ids outside 0..experts-1 last).
+ * The grouping step in front of the routed GEMVs; the reference's analogue is moe_count / moe_plan /
+ * moe_scatter of its prefill path (engine/src/kernels.rs:3334-3420). */
+int cn_moe_sort(const int32_t* ids, int32_t* order, int combos, int experts, cn_stream_t stream);
+
+/* y[t] = base[t] + sum_j wts[t][j] * eo[t*topk + j], j in pick order; base = shared[t] (times
+ * sigmoid(sgate[t]) when sgate != null), 0 when shared == null. A combo whose table entry is null
+ * adds nothing (table may be null: every combo counts). Replaces acc_combo + gate_shared
+ * (engine/src/kernels.rs:1583-1599) and glm5_moe_combine (engine/src/kernels_glm5_moe.cu:141).
+ * eo, shared f32; y in `dtype`. */
+int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const unsigned long long* table, const float* shared,
+                   const float* sgate, void* y, int tokens, int hidden, int topk, int dtype, cn_stream_t stream);
+
+/* The routed-expert decode step, GpuMoePlan-shaped (engine/src/glm5_moe.rs:518-793; Flash-Next call
+ * site Engine::moe_run, engine/src/gen.rs:4168-4532). The plan owns the scratch (the only
+ * allocation; run() allocates nothing and does not synchronise).
+ * Tables are device arrays [experts] of device addresses (0 = expert not resident: its combos are
+ * skipped, the contract of engine/src/kernels_mul1.cu:118-119): table_gu = gate [inter][hidden], or
+ * the fused gate|up slab [2*inter][hidden] when table_up == null; table_dn = down [hidden][inter].
+ * gs_gu / gs_up / gs_dn: device f32 tensor scales shared by all experts (gs_up may be null = gs_gu).
+ * shared_*: the shared expert's matrices (null = none) with shared_gs a device f32[3] (gate, up,
+ * down); sgate: optional device f32 [tokens] gate logits of the shared expert (engine/src/kernels.rs:1593).
+ * ids, wts [tokens][topk] from a router above; x, y [tokens][hidden] in `dtype`. */
+int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, int shared_inter, int experts, int topk, int max_tokens);
+int cn_moe_nvfp4_plan_destroy(void* plan);
+int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, const unsigned long long* table_up,
+                     const unsigned long long* table_dn, const float* gs_gu, const float* gs_up, const float* gs_dn,
+                     const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs,
+                     const float* sgate, const int32_t* ids, const float* wts, const void* x, void* y, int tokens, float limit,
+                     int dtype, cn_stream_t stream);
+
+/* ---------------------------------------------------------------- EXL3 "MUL1" trellis experts
+ * A record holds one expert (converter/src/mul1.rs:30-34, engine/src/cpu_mul1.rs:7-12):
+ * [gate.trellis][up.trellis][down.trellis][gate.suh][gate.svh][up.suh][up.svh][down.suh][down.svh],
+ * gate/up [hidden -> inter], down [inter -> hidden], bitrate K = bits (+0.5 when half), records
+ * 16-byte aligned. ptrs: device array [slots] of record addresses, 0 = skip the slot
+ * (engine/src/kernels_mul1.cu:118-119). The plan owns the scratch (transformed activations and the
+ * k-split partial sums); run calls allocate nothing. Replaces mul1::GemvPlan / FfnPlan / FusedFfn
+ * (engine/src/kernels.rs:6644-6850) and their kernels (engine/src/kernels_mul1.cu:114-700). */
+int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int bits, int half, int max_slots, int max_t);
+int cn_mul1_plan_destroy(void* plan);
+
+/* y[slot][t] = x[slot / x_div][t] W for matrix `which` of each slot's record (0 gate, 1 up, 2 down);
+ * x [slots / x_div][t][k], y [slots][t][n] in `dtype`; t <= 8. GemvPlan::run_slots
+ * (engine/src/kernels.rs:6683-6717), CPU twin cpu_mul1::gemv (engine/src/cpu_mul1.rs:1626). */
+int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div,
+                 int dtype, cn_stream_t stream);
+
+/* y[slot][t] = down(act(gate x, up x)), act = silu(g) * u, or the clamped SwiGLU when limit > 0.
+ * FfnPlan / FusedFfn (engine/src/kernels.rs:6731-6850), CPU twin cpu_mul1::expert_ffn
+ * (engine/src/cpu_mul1.rs:1665) / glm5_moe::expert_ffn_mul1_cpu (engine/src/glm5_moe.rs:280). */
+int cn_mul1_ffn(void* plan, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, float limit,
+                int dtype, cn_stream_t stream);
+
+/* The GLM-style routed step over MUL1 experts: ptrs[c] = table[ids[c]] (glm5_moe_gather), one slot
+ * per (token, rank) combo, the FFN of every slot, then y[t] = sum_j wts[t][j] * eo[t*topk + j] +
+ * shared[t] (shared: optional f32 [tokens][hidden], e.g. the NVFP4 shared expert's output).
+ * GpuMoePlan::experts (engine/src/glm5_moe.rs:741-793). The plan needs max_slots >= tokens * topk. */
+int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared,
+                    const void* x, void* y, int tokens, int topk, float limit, int dtype, cn_stream_t stream);
+
+/* W_hat [k][n] as fp16 bits from a trellis (the codec self-check; converter/src/mul1.rs:177-195
+ * `reconstruct`, GPU test mul1_gpu_weight_equals_codec engine/src/kernels.rs:7076). */
+int cn_mul1_reconstruct(const void* trellis, void* w_out, int k, int n, int bits, int half, cn_stream_t stream);
+
+/* ---------------------------------------------------------------- FP8 (E4M3FN) GEMV, M = 1..8
+ * y[m][r] = sum over 128-column tiles cb of (sum_{k in tile} e4m3(q[r][k]) * x[m][k]) * scale[r/128][cb].
+ * w: [rows][cols] E4M3FN bytes; scale: f32 [ceil(rows/128)][ceil(cols/128)], the codec's block grid
+ * (converter/src/fp8.rs:44-82 `dequant_fp8_block`; byte decode engine/src/cnq.rs:1363-1376). The
+ * reference has this codec but no FP8 GEMV; this entry point defines one on it. cols % 16 == 0.
+ * f32 activations are rounded to f16 (11 bits) when staged; bf16 activations are exact. */
+int cn_fp8_gemv(const void* w, const float* scale, const void* x, void* y, int rows, int cols, int m, int ldy, int dtype,
+                cn_stream_t stream);
+
 /* diagnostics: select an inner-loop variant of the NVFP4 GEMV for A/B timing (0 = default) */
 void cn_set_tuning(int key, int value);
 #define CN_TUNE_GEMV_MODE 1 /* 0 default, 1 force f32 FMA path, 2 force f16 mixed-FMA path */
