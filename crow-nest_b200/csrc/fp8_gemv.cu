@@ -113,7 +113,14 @@ int launch(const void* w, const float* scale, const void* x, void* y, int rows, 
     const int mp = m == 1 ? 1 : (m == 2 ? 2 : (m <= 4 ? 4 : 8));
     const int tiles = (cols + 127) / 128;
     const size_t smem = (size_t)mp * cols * 2 + (size_t)mp * tiles * 4 + 16;
-    if (smem > 200 * 1024) CN_FAIL(CN_ERR_LIMIT, "cn_fp8_gemv: %d rows of %d activations need %zu B of shared memory", m, cols, smem);
+    if (smem > 200 * 1024) {
+        // the staged activations of all m rows do not fit one CTA: two calls over half the rows each
+        if (m == 1) CN_FAIL(CN_ERR_LIMIT, "cn_fp8_gemv: %d activations need %zu B of shared memory", cols, smem);
+        const int m0 = m / 2;
+        const size_t es = XT == 1 ? 2 : 4;
+        if (int rc = launch<XT>(w, scale, x, y, rows, cols, m0, ldy, st)) return rc;
+        return launch<XT>(w, scale, (const char*)x + (size_t)m0 * cols * es, (char*)y + (size_t)m0 * ldy * es, rows, cols, m - m0, ldy, st);
+    }
     int grid = (rows + WARPS - 1) / WARPS;
     if (grid > 148 * 8) grid = 148 * 8;
 #define CN_FP8_CASE(MPV)                                                                                                  \

@@ -147,7 +147,7 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
     // routed down: eo[c] = down_e h[c]
     GemvCall d = {};
     d.gs0 = gs_dn, d.x = p->h, d.y = p->eo, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
-    d.x_f16_ok = 1, d.ids = ids, d.order = p->order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
+    d.x_f16_ok = 0, d.ids = ids, d.order = p->order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
     if (int rc = cn_gemv_launch(d, stream, "cn_moe_nvfp4_run (down)")) return rc;
     // shared expert on every token, up to 8 rows per pass
     const float* shared = nullptr;
@@ -162,7 +162,7 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
             if (int rc = cn_gemv_launch(g, stream, "cn_moe_nvfp4_run (shared gate/up)")) return rc;
             GemvCall s = {};
             s.w0 = shared_down, s.gs0 = shared_gs + 2, s.x = p->hs + (size_t)t0 * p->shared_inter, s.y = p->ys + (size_t)t0 * p->hidden;
-            s.rows = p->hidden, s.k = p->shared_inter, s.m = m, s.ldy = p->hidden, s.dtype = CN_F32, s.out_f32 = 1, s.x_f16_ok = 1;
+            s.rows = p->hidden, s.k = p->shared_inter, s.m = m, s.ldy = p->hidden, s.dtype = CN_F32, s.out_f32 = 1, s.x_f16_ok = 0;
             if (int rc = cn_gemv_launch(s, stream, "cn_moe_nvfp4_run (shared down)")) return rc;
         }
         shared = p->ys;

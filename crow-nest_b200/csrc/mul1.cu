@@ -58,11 +58,26 @@ __device__ __forceinline__ float block_scale(float amax, float& inv) {
     return __uint_as_float((268u - e) << 23);
 }
 
-// xh16[slot][t][k] = f16(H128(x * suh) * mul), xinv[slot][t][k/128] = 1/mul.
+// Four scaled values as two f16 planes: hi = f16(v * mul), lo = f16((v * mul - hi) * 2^11). hi + lo * 2^-11
+// carries 22 significand bits, so the f16 x f16 products lose nothing that an f32 activation would keep.
+__device__ __forceinline__ void store_hi_lo(uint16_t* xh, size_t plane, size_t at, const float v[4], float mul) {
+    uint16_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float s = v[j] * mul;
+        const __half h = __float2half_rn(s);
+        hi[j] = __half_as_ushort(h);
+        lo[j] = __half_as_ushort(__float2half_rn((s - __half2float(h)) * 2048.0f));
+    }
+    *(uint2*)(xh + at) = make_uint2(hi[0] | ((uint32_t)hi[1] << 16), hi[2] | ((uint32_t)hi[3] << 16));
+    *(uint2*)(xh + plane + at) = make_uint2(lo[0] | ((uint32_t)lo[1] << 16), lo[2] | ((uint32_t)lo[3] << 16));
+}
+
+// xh16[slot][t][k] = the hi / lo planes of H128(x * suh) * mul, xinv[slot][t][k/128] = 1/mul.
 // grid (k/128, T, slots), block 32. XT: 0 f32, 1 bf16 input. x row of slot: x + (slot / x_div) * T * k.
 template <int XT>
 __global__ void mul1_had_in_kernel(const unsigned long long* __restrict__ ptrs, const void* __restrict__ x, uint16_t* __restrict__ xh,
-                                   float* __restrict__ xinv, int k, int T, long long suh_off, int x_div) {
+                                   float* __restrict__ xinv, int k, int T, long long suh_off, int x_div, size_t plane) {
     const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
     if (ptrs[slot] == 0ull) return;  // a null record: nothing to read or write
     const uint16_t* suh = (const uint16_t*)(ptrs[slot] + (unsigned long long)suh_off);
@@ -80,8 +95,7 @@ __global__ void mul1_had_in_kernel(const unsigned long long* __restrict__ ptrs, 
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     float inv;
     const float mul = block_scale(amax, inv);
-    const __half2 h0 = __floats2half2_rn(v[0] * mul, v[1] * mul), h1 = __floats2half2_rn(v[2] * mul, v[3] * mul);
-    *(uint2*)(xh + row + c0) = make_uint2(*(const uint32_t*)&h0, *(const uint32_t*)&h1);
+    store_hi_lo(xh, plane, row + c0, v, mul);
     if (lane == 0) xinv[((size_t)slot * T + t) * (k / 128) + blk] = inv;
 }
 
@@ -125,7 +139,8 @@ __device__ __forceinline__ void lane_states(const uint32_t* tile, int n32, const
 // part[slot][sp][t][n]; xh16 [slot][T][k] f16, xinv [slot][T][k/128].
 template <bool K3>
 __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long* __restrict__ ptrs, const uint16_t* __restrict__ xh,
-                                                        const float* __restrict__ xinv, float* __restrict__ part, Mul1Spec sp_, int S, int T) {
+                                                        const float* __restrict__ xinv, float* __restrict__ part, Mul1Spec sp_, int S, int T,
+                                                        size_t plane) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int slot = blockIdx.z, sp = blockIdx.y;
     const unsigned long long rec = ptrs[slot];
@@ -138,8 +153,8 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + RING;
     uint32_t* ring = (uint32_t*)(smem + 128);                                   // [RING][UROWS][8][n32]
-    uint16_t* xs = (uint16_t*)(smem + 128 + (size_t)RING * UROWS * run_bytes);  // [T][rows] f16
-    float* xi = (float*)(xs + (size_t)T * rows + ((T * rows) & 1));             // [T][rows/128]
+    uint16_t* xs = (uint16_t*)(smem + 128 + (size_t)RING * UROWS * run_bytes);  // [2][T][rows] f16: hi plane, lo plane
+    float* xi = (float*)(xs + (size_t)2 * T * rows);                            // [T][rows/128]
     if (threadIdx.x == 0) {
         for (int s = 0; s < RING; s++) {
             mbar_init(&full[s], 1);
@@ -177,7 +192,9 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
     // the activation rows of this k-split, and their block scales
     for (int i = threadIdx.x; i < T * rows / 2; i += 256) {
         const int t = i / (rows / 2), r = i - t * (rows / 2);
-        ((uint32_t*)xs)[i] = ((const uint32_t*)(xh + ((size_t)slot * T + t) * k + (size_t)kb0 * 16))[r];
+        const size_t at = ((size_t)slot * T + t) * k + (size_t)kb0 * 16;
+        ((uint32_t*)xs)[i] = ((const uint32_t*)(xh + at))[r];
+        ((uint32_t*)(xs + (size_t)T * rows))[i] = ((const uint32_t*)(xh + plane + at))[r];
     }
     const int nblk = rows / 128;
     for (int i = threadIdx.x; i < T * nblk; i += 256) {
@@ -199,9 +216,10 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
     float tot0[MUL1_MAXT], tot1[MUL1_MAXT];
 #pragma unroll
     for (int t = 0; t < MUL1_MAXT; t++) tot0[t] = tot1[t] = 0.0f;
-    float a0e[MUL1_MAXT], a0o[MUL1_MAXT], a1e[MUL1_MAXT], a1o[MUL1_MAXT];
+    float a0e[MUL1_MAXT], a0o[MUL1_MAXT], a1e[MUL1_MAXT], a1o[MUL1_MAXT];  // hi plane, even / odd chains
+    float l0e[MUL1_MAXT], l0o[MUL1_MAXT], l1e[MUL1_MAXT], l1o[MUL1_MAXT];  // lo plane
 #pragma unroll
-    for (int t = 0; t < MUL1_MAXT; t++) a0e[t] = a0o[t] = a1e[t] = a1o[t] = 0.0f;
+    for (int t = 0; t < MUL1_MAXT; t++) a0e[t] = a0o[t] = a1e[t] = a1o[t] = l0e[t] = l0o[t] = l1e[t] = l1o[t] = 0.0f;
     for (int c = 0; c < nst; c++) {
         const int s = c % RING;
         if (!mbar_wait(&full[s], (c / RING) & 1)) {
@@ -225,6 +243,12 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
                     fma2_f16_f32(a0e[t], a0o[t], w23, x89);
                     fma2_f16_f32(a1e[t], a1o[t], w45, x01);
                     fma2_f16_f32(a1e[t], a1o[t], w67, x89);
+                    const uint32_t* xl = xr + (size_t)T * rows / 2;
+                    const uint32_t y01 = xl[0], y89 = xl[4];
+                    fma2_f16_f32(l0e[t], l0o[t], w01, y01);
+                    fma2_f16_f32(l0e[t], l0o[t], w23, y89);
+                    fma2_f16_f32(l1e[t], l1o[t], w45, y01);
+                    fma2_f16_f32(l1e[t], l1o[t], w67, y89);
                 }
             }
             if ((kt & 7) == 7) {
@@ -233,9 +257,9 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
                 for (int t = 0; t < MUL1_MAXT; t++) {
                     if (t < T) {
                         const float inv = xi[t * nblk + (kt >> 3)];
-                        tot0[t] = fmaf(a0e[t] + a0o[t], inv, tot0[t]);
-                        tot1[t] = fmaf(a1e[t] + a1o[t], inv, tot1[t]);
-                        a0e[t] = a0o[t] = a1e[t] = a1o[t] = 0.0f;
+                        tot0[t] = fmaf(fmaf(l0e[t] + l0o[t], 4.8828125e-4f, a0e[t] + a0o[t]), inv, tot0[t]);
+                        tot1[t] = fmaf(fmaf(l1e[t] + l1o[t], 4.8828125e-4f, a1e[t] + a1o[t]), inv, tot1[t]);
+                        a0e[t] = a0o[t] = a1e[t] = a1o[t] = l0e[t] = l0o[t] = l1e[t] = l1o[t] = 0.0f;
                     }
                 }
             }
@@ -298,7 +322,7 @@ __global__ void mul1_had_out_kernel(const unsigned long long* __restrict__ ptrs,
 // grid (inter/128, T, slots), block 32.
 __global__ void mul1_act_had_in_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part_g,
                                        const float* __restrict__ part_u, uint16_t* __restrict__ xh_d, float* __restrict__ xinv_d, int inter, int S,
-                                       int T, long long svh_g, long long svh_u, long long suh_d, float limit) {
+                                       int T, long long svh_g, long long svh_u, long long suh_d, float limit, size_t plane) {
     const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
     if (ptrs[slot] == 0ull) return;
     float g[4], u[4], v[4];
@@ -322,9 +346,8 @@ __global__ void mul1_act_had_in_kernel(const unsigned long long* __restrict__ pt
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     float inv;
     const float mul = block_scale(amax, inv);
-    const __half2 h0 = __floats2half2_rn(v[0] * mul, v[1] * mul), h1 = __floats2half2_rn(v[2] * mul, v[3] * mul);
     const size_t row = ((size_t)slot * T + t) * inter;
-    *(uint2*)(xh_d + row + c0) = make_uint2(*(const uint32_t*)&h0, *(const uint32_t*)&h1);
+    store_hi_lo(xh_d, plane, row + c0, v, mul);
     if (lane == 0) xinv_d[((size_t)slot * T + t) * (inter / 128) + blk] = inv;
 }
 
@@ -357,7 +380,8 @@ namespace {
 struct Mul1Plan {
     int hidden, inter, bits, half, n32, max_slots, max_t;
     size_t kmax;
-    uint16_t *xh_a, *xh_b;  // [slots][T][kmax] f16
+    uint16_t *xh_a, *xh_b;  // [2 planes][slots][T][kmax] f16
+    size_t plane;           // elements of one plane
     float *xinv_a, *xinv_b;  // [slots][T][kmax/128]
     float *part_a, *part_b;  // [slots][16][T][kmax]
     unsigned long long* ptrs;  // [slots] gathered record addresses (MoE form)
@@ -385,20 +409,20 @@ Mul1Spec spec_of(const Mul1Plan* p, int which) {
 }
 
 int launch_had_in(const unsigned long long* ptrs, const void* x, uint16_t* xh, float* xinv, const Mul1Spec& s, int slots, int T, int x_div,
-                  int dtype, cudaStream_t st) {
+                  int dtype, size_t plane, cudaStream_t st) {
     dim3 grid(s.k / 128, T, slots);
     if (dtype == CN_BF16)
-        mul1_had_in_kernel<1><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div);
+        mul1_had_in_kernel<1><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane);
     else
-        mul1_had_in_kernel<0><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div);
+        mul1_had_in_kernel<0><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane);
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
 
 int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float* xinv, float* part, const Mul1Spec& s, int slots, int T,
-                cudaStream_t st) {
+                size_t plane, cudaStream_t st) {
     const int S = ksplit(s.k), tps = (s.k / 16) / S, rows = tps * 16;
-    const size_t smem = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)T * rows * 2 + 8 + (size_t)T * (rows / 128) * 4;
+    const size_t smem = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * rows * 2 + 8 + (size_t)T * (rows / 128) * 4;
     dim3 grid(s.n / 128, S, slots);
     static bool attr = false;
     if (!attr) {
@@ -408,9 +432,9 @@ int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float*
     }
     if (smem > 160 * 1024) CN_FAIL(CN_ERR_LIMIT, "mul1 gemv: %zu B of shared memory per block", smem);
     if (s.bits == 3 && !s.half)
-        mul1_gemv_kernel<true><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T);
+        mul1_gemv_kernel<true><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T, plane);
     else
-        mul1_gemv_kernel<false><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T);
+        mul1_gemv_kernel<false><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T, plane);
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
@@ -438,8 +462,9 @@ extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int b
     p->hidden = hidden, p->inter = inter, p->bits = bits, p->half = half, p->n32 = 8 * bits + (half ? 4 : 0), p->max_slots = max_slots, p->max_t = max_t;
     p->kmax = hidden > inter ? hidden : inter;
     const size_t rows = (size_t)max_slots * max_t;
-    CN_CUDA(cudaMalloc(&p->xh_a, rows * p->kmax * 2));
-    CN_CUDA(cudaMalloc(&p->xh_b, rows * p->kmax * 2));
+    p->plane = rows * p->kmax;
+    CN_CUDA(cudaMalloc(&p->xh_a, 2 * p->plane * 2));
+    CN_CUDA(cudaMalloc(&p->xh_b, 2 * p->plane * 2));
     CN_CUDA(cudaMalloc(&p->xinv_a, rows * (p->kmax / 128) * 4));
     CN_CUDA(cudaMalloc(&p->xinv_b, rows * (p->kmax / 128) * 4));
     CN_CUDA(cudaMalloc(&p->part_a, rows * 16 * p->kmax * 4));
@@ -466,8 +491,8 @@ extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptr
     if (which < 0 || which > 2 || x_div < 1) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv: matrix %d (0 gate, 1 up, 2 down), x_div %d", which, x_div);
     cudaStream_t st = (cudaStream_t)stream;
     const Mul1Spec s = spec_of(p, which);
-    if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, s, slots, t, x_div, dtype, st)) return rc;
-    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, s, slots, t, st)) return rc;
+    if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, s, slots, t, x_div, dtype, p->plane, st)) return rc;
+    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, s, slots, t, p->plane, st)) return rc;
     dim3 grid(s.n / 128, t, slots);
     if (dtype == CN_BF16)
         mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off);
@@ -481,14 +506,14 @@ extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptr
 static int mul1_ffn(Mul1Plan* p, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, float limit, int dtype,
                     int out_f32, cudaStream_t st) {
     const Mul1Spec g = spec_of(p, 0), u = spec_of(p, 1), d = spec_of(p, 2);
-    if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, st)) return rc;
-    if (int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, st)) return rc;
-    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, st)) return rc;
-    if (int rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, st)) return rc;
+    if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, p->plane, st)) return rc;
+    if (int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, p->plane, st)) return rc;
+    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, p->plane, st)) return rc;
+    if (int rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, p->plane, st)) return rc;
     mul1_act_had_in_kernel<<<dim3(p->inter / 128, t, slots), 32, 0, st>>>(ptrs, p->part_a, p->part_b, p->xh_a, p->xinv_a, p->inter, ksplit(p->hidden), t,
-                                                                         g.svh_off, u.svh_off, d.suh_off, limit);
+                                                                         g.svh_off, u.svh_off, d.suh_off, limit, p->plane);
     CN_CUDA(cudaGetLastError());
-    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, d, slots, t, st)) return rc;
+    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, d, slots, t, p->plane, st)) return rc;
     dim3 grid(d.n / 128, t, slots);
     if (dtype == CN_BF16 && !out_f32)
         mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off);

@@ -94,7 +94,7 @@ def test_moe_step_matches_the_cpu_reference(tokens):
     rids, rw = oracle.route_softmax_topk(logits, k)
     assert np.array_equal(ids, rids)
     ref = cpu_moe(xf, rids, rw, gu, dn, hidden, inter, gs_gu, gs_dn, shared, sgs)
-    check_close(from_dev_bf16(y), ref, f"moe tokens={tokens}")
+    check_close(from_dev_bf16(y), ref, f"moe tokens={tokens}", ulp_floor=1.0 / 64)
     # run to run: same bits
     y2 = plan.run(w, dev(logits), to_dev_bf16(xb))
     assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
