@@ -51,6 +51,7 @@ _SIGS = {
     "cn_mul1_gemv": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cn_mul1_ffn": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "cn_moe_mul1_run": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp],
+    "cn_mul1_gemv_noalloc": [_i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cn_mul1_reconstruct": [_vp, _vp, _i, _i, _i, _i, _vp],
     "cn_fp8_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cn_device_status": [C.POINTER(C.c_int)],

@@ -554,3 +554,80 @@ extern "C" int cn_mul1_reconstruct(const void* trellis, void* w_out, int k, int 
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
+
+// ---------------------------------------------------------------- allocation-free MUL1 GEMV
+// For callers that may not allocate device memory at the point of the call - an engine thread that
+// already runs inside a latency-critical decode loop, a plugin host that forbids cudaMalloc after
+// start-up because an allocation synchronises the whole device, or code that holds a memory budget
+// it has fully handed out. The scratch of the GEMV (the transformed activations and the k-split
+// partial sums) lives in a fixed array inside the library image instead of a plan.
+//
+// Limits: slots * t <= CN_MUL1_STATIC_ROWS (8) activation rows per call, hidden and inter <=
+// CN_MUL1_STATIC_DIM (4096). The array is about 2.2 MB and every GPU that loads the library holds
+// it until the process exits.
+namespace {
+
+constexpr size_t NA_ROWS = 8, NA_DIM = 4096, NA_SPLITS = 16;
+constexpr size_t NA_XH_BYTES = 2 * NA_ROWS * NA_DIM * 2;             // hi and lo f16 planes
+constexpr size_t NA_XINV_BYTES = NA_ROWS * (NA_DIM / 128) * 4;       // one f32 per 128-block
+constexpr size_t NA_PART_BYTES = NA_ROWS * NA_SPLITS * NA_DIM * 4;   // f32 partial sums of the k-split
+constexpr size_t NA_BYTES = NA_XH_BYTES + NA_XINV_BYTES + NA_PART_BYTES;
+
+// File-scope device array: in host code this name is only a handle for the runtime, never an
+// address a kernel may be given; the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_mul1_static_scratch[NA_BYTES];
+
+constexpr int NA_MAX_DEVICES = 64;
+unsigned char* g_static_ptr[NA_MAX_DEVICES] = {};
+
+// The device address of the scratch array on the current device, looked up once per device.
+int static_scratch(unsigned char** out) {
+    int dev = -1;
+    CN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NA_MAX_DEVICES) CN_FAIL(CN_ERR_LIMIT, "cn_mul1_gemv_noalloc: device ordinal %d beyond %d", dev, NA_MAX_DEVICES);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_mul1_static_scratch);
+        if (e != cudaSuccess || !p) CN_FAIL(CN_ERR_CUDA, "cn_mul1_gemv_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_static_ptr[dev] = (unsigned char*)p;
+    }
+    *out = g_static_ptr[dev];
+    return CN_OK;
+}
+
+}  // namespace
+
+extern "C" int cn_mul1_gemv_noalloc(int which, int hidden, int inter, int bits, int half, const unsigned long long* ptrs, const void* x, void* y,
+                                    int slots, int t, int x_div, int dtype, cn_stream_t stream) {
+    if (hidden <= 0 || inter <= 0 || hidden % 128 || inter % 128)
+        CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv_noalloc: [%d, %d] is not a positive multiple of 128 on both sides", hidden, inter);
+    if (bits < 1 || bits > 8 || (half && bits > 3)) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv_noalloc: unsupported bitrate %d%s", bits, half ? ".5" : "");
+    if (which < 0 || which > 2 || x_div < 1) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv_noalloc: matrix %d (0 gate, 1 up, 2 down), x_div %d", which, x_div);
+    if (slots < 1 || t < 1 || t > MUL1_MAXT || (size_t)slots * t > NA_ROWS)
+        CN_FAIL(CN_ERR_LIMIT, "cn_mul1_gemv_noalloc: %d slots x %d rows; the fixed scratch holds %zu rows in all (use a plan for more)", slots, t, NA_ROWS);
+    if ((size_t)hidden > NA_DIM || (size_t)inter > NA_DIM)
+        CN_FAIL(CN_ERR_LIMIT, "cn_mul1_gemv_noalloc: hidden %d / inter %d beyond the fixed scratch's %zu (use a plan for more)", hidden, inter, NA_DIM);
+    unsigned char* base = nullptr;
+    if (int rc = static_scratch(&base)) return rc;
+    Mul1Plan view = {};
+    view.hidden = hidden, view.inter = inter, view.bits = bits, view.half = half, view.n32 = 8 * bits + (half ? 4 : 0);
+    const Mul1Spec s = spec_of(&view, which);
+    uint16_t* xh = (uint16_t*)base;
+    float* xinv = (float*)(base + NA_XH_BYTES);
+    float* part = (float*)(base + NA_XH_BYTES + NA_XINV_BYTES);
+    const size_t plane = NA_ROWS * NA_DIM;  // the lo plane starts one full plane after the hi plane
+    cudaStream_t st = (cudaStream_t)stream;
+    // every region is written before it is read within one call (had_in fills xh / xinv of the live
+    // slots, the GEMV fills every partial that had_out sums), so nothing has to start at zero
+    if (int rc = launch_had_in(ptrs, x, xh, xinv, s, slots, t, x_div, dtype, plane, st)) return rc;
+    if (int rc = launch_gemv(ptrs, xh, xinv, part, s, slots, t, plane, st)) return rc;
+    dim3 grid(s.n / 128, t, slots);
+    if (dtype == CN_BF16)
+        mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off);
+    else if (dtype == CN_F32)
+        mul1_had_out_kernel<0><<<grid, 32, 0, st>>>(ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off);
+    else
+        CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv_noalloc: dtype %d is neither CN_F32 nor CN_BF16", dtype);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}

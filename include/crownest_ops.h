@@ -160,6 +160,24 @@ int cn_mul1_ffn(void* plan, const unsigned long long* ptrs, const void* x, void*
 int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared,
                     const void* x, void* y, int tokens, int topk, float limit, int dtype, cn_stream_t stream);
 
+/* The MUL1 GEMV of cn_mul1_gemv without a plan and without any allocation: for a caller that cannot
+ * allocate device memory where it makes the call (a decode loop that must not hit the device-wide
+ * synchronisation an allocation implies, a host that hands out all device memory at start-up, a
+ * plugin sandbox that forbids it). Its scratch is a fixed array of about 2.2 MB inside the library
+ * image, which every GPU that loads the library keeps until the process exits.
+ * This entry point has no counterpart in the reference (there every plan allocates its scratch,
+ * engine/src/kernels.rs:6664).
+ * Limits, refused with CN_ERR_LIMIT beyond them: slots * t <= CN_MUL1_STATIC_ROWS activation rows,
+ * hidden and inter <= CN_MUL1_STATIC_DIM. Same arguments and results as cn_mul1_gemv (bit for bit).
+ * The first call on each device looks up the array's device address (with that device current); make
+ * that first call outside any stream capture. All calls on a device share the one array, which keeps
+ * the previous call's contents (each call overwrites what it reads, nothing needs clearing): two calls
+ * whose kernels can overlap on the GPU - different streams without ordering - race on it. */
+#define CN_MUL1_STATIC_ROWS 8
+#define CN_MUL1_STATIC_DIM 4096
+int cn_mul1_gemv_noalloc(int which, int hidden, int inter, int bits, int half, const unsigned long long* ptrs, const void* x, void* y,
+                         int slots, int t, int x_div, int dtype, cn_stream_t stream);
+
 /* W_hat [k][n] as fp16 bits from a trellis (the codec self-check; converter/src/mul1.rs:177-195
  * `reconstruct`, GPU test mul1_gpu_weight_equals_codec engine/src/kernels.rs:7076). */
 int cn_mul1_reconstruct(const void* trellis, void* w_out, int k, int n, int bits, int half, cn_stream_t stream);
