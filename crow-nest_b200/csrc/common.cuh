@@ -99,7 +99,9 @@ __device__ __forceinline__ float ue4m3_f32(uint32_t b, bool rule) {
 // every E2M1 value is exact in f16
 __device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
     uint32_t r;
-    asm("{\n\t.reg .b8 t;\n\tcvt.u8.u32 t, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, t;\n\t}" : "=r"(r) : "r"(byte));
+    // the byte is taken with a vector mov: feeding cvt through cvt.u8.u32 gave wrong values when the source
+    // register came straight from a byte load
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b0;\n\t}" : "=r"(r) : "r"(byte));
     return r;
 }
 // d = a * b + c with a, b f16 (exact product), c, d f32: one rounding

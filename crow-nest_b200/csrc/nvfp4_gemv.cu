@@ -34,41 +34,8 @@ constexpr int NTHREADS = (NW + 1) * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int XB_F16 = 144;  // bytes of one k-block's 64 activations as f16, padded: conflict-free 16-byte loads
 constexpr int XB_F32 = 272;  // the same as f32
-constexpr int HDR_BYTES = 128 + 2048;  // barriers, two scale tables
-
-struct GemvParams {
-    const uint8_t* w0;  // plain: the matrix; gate/up: gate
-    const uint8_t* w1;  // gate/up: up (else null)
-    const float* gs0;
-    const float* gs1;
-    const void* x;
-    void* y;
-    int rows;  // output rows (gate/up: inter)
-    int k;
-    int m;  // live activation rows (<= MP)
-    int ldy;
-    float limit;
-    int tx;      // lanes across K per row: 16, 8 or 4
-    int stages;  // ring depth
-    int out_f32;  // store f32 whatever the activation type (MoE intermediates)
-    // routed-expert form (ids != null): blockIdx.y walks the combos, combo c = t * topk + j reads the
-    // matrix of expert ids[c] from a device pointer table (a null entry skips the combo), activation
-    // row c / x_div, output row c
-    const int32_t* ids;
-    const int32_t* order;           // combos sorted by expert (null: identity)
-    const unsigned long long* tab0;  // [experts] plain matrix or gate (or the fused gate|up slab)
-    const unsigned long long* tab1;  // [experts] up (null with a fused slab or a plain matrix)
-    int fused_up_rows;               // > 0: up = gate + fused_up_rows rows of the same slab
-    int x_div;
-};
-
-__device__ __forceinline__ float act_gu(float g, float u, float limit) {
-    if (limit > 0.0f) {
-        g = g > limit ? limit : g;
-        u = u > limit ? limit : (u < -limit ? -limit : u);
-    }
-    return (g / (1.0f + expf(-g))) * u;
-}
+constexpr int XB_SWZ = 128;  // bf16 rows staged by TMA, converted in place: 16-byte chunks XOR-swizzled instead of padded
+constexpr int HDR_BYTES = 256 + 2048;  // barriers, two scale tables
 
 // one load group of eight activation values: raw words in flight, widened exactly to f32 on use
 template <int XT>
@@ -103,9 +70,10 @@ __device__ __forceinline__ void widen_x8(const XRaw<XT>& r, float v[8]) {
 // XT: 0 = f32 activations/outputs, 1 = bf16. MP: activation rows compiled in (1, 2, 4, 8).
 // RT: rows per consumer thread. MODE: 0 = f32 FMA, 1 = f16 x f16 + f32 mixed FMA (bf16 input only).
 template <int XT, int MP, int RT, int MODE>
-__global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(NTHREADS, (MP <= 2 ? 4 : 1)) nvfp4_gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int XB = MODE == 1 ? XB_F16 : XB_F32;
+    constexpr bool SWZ = XT == 1 && MODE == 1;
+    constexpr int XB = SWZ ? XB_SWZ : (MODE == 1 ? XB_F16 : XB_F32);
     const int TX = p.tx;
     const int G = NW * (32 / TX);  // row groups per CTA
     const int ROWS = G * RT;       // row slots per stage
@@ -132,7 +100,8 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
 
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + MAX_STAGES;
-    float* lut = (float*)(smem + 128);  // [2][256]
+    uint64_t* xbar = empty + MAX_STAGES;  // the activation rows have landed
+    float* lut = (float*)(smem + 256);    // [2][256]
     uint8_t* xs0 = smem + HDR_BYTES;                              // [MP][bpr][XB] staged activations
     float* xinv0 = (float*)(xs0 + (size_t)MP * bpr * XB);         // [MP][bpr] inverse block scales
     uint8_t* stage0 = (uint8_t*)(xinv0 + ((MP * bpr + 3) & ~3));  // the weight ring
@@ -148,6 +117,7 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
             mbar_init(&full[s], 1);  // the producer's expect_tx arrive; the copies count bytes
             mbar_init(&empty[s], NW);
         }
+        mbar_init(xbar, 1);
         mbar_fence_init();
     }
     // scale tables: ue4m3(rule(byte)) * gs, the product the reference tabulates (cpu_nvfp4.rs:98)
@@ -207,7 +177,60 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
     // the weight ring. Groups of 8 values; lane & 7 = position in the 64-value block, so the 8
     // lanes of a block sit side by side. All loads of a batch are in flight before the first
     // conversion (one L2 round trip per batch, not per group).
-    {
+    if (SWZ) {
+        // bf16 rows: one bulk copy per row into shared memory, then an in-place conversion to f16 with a
+        // power-of-two scale per 64-value block. A thread owns whole 128-byte blocks (no exchange) and
+        // writes the eight 16-byte chunks of block b at chunk index i ^ (b & 7): conflict-free 16-byte
+        // loads for eight lanes reading eight consecutive blocks, without padding.
+        if (tid == 0) {
+            pdl_wait();  // activations may come from the previous kernel of the stream
+            mbar_expect_tx(xbar, (uint32_t)p.m * (uint32_t)p.k * 2u);
+            mbar_arrive(xbar);
+            for (int m = 0; m < p.m; m++) bulk_g2s(xs0 + (size_t)m * bpr * XB, xbase + (size_t)m * p.k * 2, (uint32_t)p.k * 2u, xbar);
+        }
+        if (!mbar_wait(xbar, 0)) {
+            cn_dev_fail(CN_DEV_WAIT_FULL);
+            return;
+        }
+        for (int b = tid; b < MP * bpr; b += NW * 32) {
+            const int m = b / bpr;
+            uint4* blkp = (uint4*)(xs0 + (size_t)b * XB);
+            uint4 raw[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) raw[i] = m < p.m ? blkp[i] : make_uint4(0, 0, 0, 0);
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t u[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    amax = fmaxf(amax, fabsf(__uint_as_float(u[q] << 16)));
+                    amax = fmaxf(amax, fabsf(__uint_as_float(u[q] & 0xffff0000u)));
+                }
+            }
+            uint32_t e = (__float_as_uint(amax) >> 23) & 0xFF;
+            float mul = 1.0f, inv = 1.0f;
+            if (amax > 0.0f && e < 255) {
+                e = e < 15 ? 15 : e;
+                mul = __uint_as_float((268u - e) << 23);
+                inv = __uint_as_float((e - 14u) << 23);
+            }
+            const int sw = (b % bpr) & 7;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t u[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+                uint32_t h[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const __half2 hh = __floats2half2_rn(__uint_as_float(u[q] << 16) * mul, __uint_as_float(u[q] & 0xffff0000u) * mul);
+                    h[q] = *(const uint32_t*)&hh;
+                }
+                blkp[i ^ sw] = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+            xinv0[b] = inv;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+    } else {
         pdl_wait();  // activations may come from the previous kernel of the stream
         constexpr int BATCH = 4;
         const int groups = MP * bpr * 8;
@@ -297,9 +320,15 @@ __global__ void __launch_bounds__(NTHREADS) nvfp4_gemv_kernel(const GemvParams p
                 uint4 xa[MP], xb[MP];
 #pragma unroll
                 for (int m = 0; m < MP; m++) {
-                    const uint4* xp = (const uint4*)(xs + (size_t)m * bpr * XB + sb * 32);
-                    xa[m] = xp[0];
-                    xb[m] = xp[1];
+                    const uint4* xp = (const uint4*)(xs + (size_t)m * bpr * XB);
+                    if (SWZ) {
+                        const int sw = (c * TX + txi) & 7;
+                        xa[m] = xp[(2 * sb) ^ sw];
+                        xb[m] = xp[(2 * sb + 1) ^ sw];
+                    } else {
+                        xa[m] = xp[2 * sb];
+                        xb[m] = xp[2 * sb + 1];
+                    }
                 }
 #pragma unroll
                 for (int r = 0; r < RT; r++) {
@@ -433,7 +462,7 @@ __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ w, const float*
     }
 }
 
-int g_tune_mode = 0, g_tune_rt = 0, g_tune_stages = 0, g_tune_pdl = 1;
+int g_tune_mode = 0, g_tune_rt = 0, g_tune_stages = 0, g_tune_pdl = 1, g_tune_engine = 0;
 
 template <int XT, int MP, int RT, int MODE>
 int launch_one(const GemvParams& p, int grid, int gy, size_t smem, cudaStream_t stream) {
@@ -477,6 +506,8 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     if (a.dtype != CN_F32 && a.dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "%s: dtype %d is neither CN_F32 nor CN_BF16", who, a.dtype);
     if (((uintptr_t)a.w0 & 15) || ((uintptr_t)a.w1 & 15) || ((uintptr_t)a.x & 15))
         CN_FAIL(CN_ERR_SHAPE, "%s: weight and activation pointers must be 16-byte aligned", who);
+    // bf16 activations: the tensor-core inner loop (engine 0 = default); engine 1 forces the CUDA-core kernel
+    if (a.dtype == CN_BF16 && g_tune_engine != 1 && g_tune_mode != 1 && a.k % 512 == 0 && (a.m >= 2 || g_tune_engine == 2)) return cn_gemv_mma_launch(a, stream, who);
     const bool routed = a.ids != nullptr;
     if (routed && (m != 1 || a.combos < 1 || a.x_div < 1)) CN_FAIL(CN_ERR_SHAPE, "%s: the routed form takes one row per combo", who);
     const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;
@@ -494,13 +525,19 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     const int ROWS = G * rt;
     const int per_cta = gu ? ROWS / 2 : ROWS;
     const int grid = (rows + per_cta - 1) / per_cta;
-    const int xb = mode == 1 ? XB_F16 : XB_F32;
+    const int xb = (mode == 1 && a.dtype == CN_BF16) ? XB_SWZ : (mode == 1 ? XB_F16 : XB_F32);
     const size_t stage_bytes = (size_t)ROWS * tx * 36;
     const size_t xbytes = (size_t)mp * bpr * xb + (size_t)((mp * bpr + 3) & ~3) * 4;
     const int nchunks = bpr / tx;
-    // ring depth: aim at four resident CTAs per SM (about 52 KB each), at least two stages
-    long long room = 52 * 1024 - (long long)HDR_BYTES - (long long)xbytes;
-    int stages = (int)(room / (long long)stage_bytes);
+    // ring depth: enough bytes in flight per SM to cover the HBM latency (about 96 KB), shared between
+    // the CTAs that will be resident together (at most four, fewer when the grid is small)
+    const long long total_ctas = (long long)grid * (routed ? a.combos : 1);
+    int resident = (int)((total_ctas + 147) / 148);
+    resident = resident < 1 ? 1 : (resident > 4 ? 4 : resident);
+    long long want = (96 * 1024) / resident;                                         // in-flight bytes per CTA
+    long long cap = (208 * 1024) / resident - (long long)HDR_BYTES - (long long)xbytes;  // what fits beside the activations
+    if (want > cap) want = cap;
+    int stages = (int)((want + (long long)stage_bytes - 1) / (long long)stage_bytes);
     if (g_tune_stages > 0) stages = g_tune_stages;
     stages = stages < 2 ? 2 : (stages > MAX_STAGES ? MAX_STAGES : stages);
     if (stages > nchunks) stages = nchunks < 1 ? 1 : nchunks;
@@ -559,4 +596,6 @@ extern "C" void cn_set_tuning(int key, int value) {
     if (key == CN_TUNE_GEMV_RT) g_tune_rt = value;
     if (key == CN_TUNE_GEMV_STAGES) g_tune_stages = value;
     if (key == 4) g_tune_pdl = value;
+    if (key == 5) g_tune_engine = value;
+    if (key == 6) cn_gemv_mma_set_stages(value);
 }

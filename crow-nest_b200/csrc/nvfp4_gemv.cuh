@@ -24,3 +24,43 @@ struct GemvCall {
 };
 
 int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who);
+
+// Kernel-side parameters shared by the CUDA-core and the tensor-core GEMV kernels.
+struct GemvParams {
+    const uint8_t* w0;  // plain: the matrix; gate/up: gate
+    const uint8_t* w1;  // gate/up: up (else null)
+    const float* gs0;
+    const float* gs1;
+    const void* x;
+    void* y;
+    int rows;  // output rows (gate/up: inter)
+    int k;
+    int m;  // live activation rows (<= MP)
+    int ldy;
+    float limit;
+    int tx;      // lanes across K per row: 16, 8 or 4
+    int stages;  // ring depth
+    int out_f32;  // store f32 whatever the activation type (MoE intermediates)
+    // routed-expert form (ids != null): blockIdx.y walks the combos, combo c = t * topk + j reads the
+    // matrix of expert ids[c] from a device pointer table (a null entry skips the combo), activation
+    // row c / x_div, output row c
+    const int32_t* ids;
+    const int32_t* order;           // combos sorted by expert (null: identity)
+    const unsigned long long* tab0;  // [experts] plain matrix or gate (or the fused gate|up slab)
+    const unsigned long long* tab1;  // [experts] up (null with a fused slab or a plain matrix)
+    int fused_up_rows;               // > 0: up = gate + fused_up_rows rows of the same slab
+    int x_div;
+};
+
+__device__ __forceinline__ float act_gu(float g, float u, float limit) {
+    if (limit > 0.0f) {
+        g = g > limit ? limit : g;
+        u = u > limit ? limit : (u < -limit ? -limit : u);
+    }
+    return (g / (1.0f + expf(-g))) * u;
+}
+
+
+// the tensor-core (mma.sync) form of the same GEMV for bf16 activations (nvfp4_gemv_mma.cu)
+int cn_gemv_mma_launch(const GemvCall& a, cudaStream_t stream, const char* who);
+void cn_gemv_mma_set_stages(int s);
