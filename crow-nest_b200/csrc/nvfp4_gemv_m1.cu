@@ -1,0 +1,367 @@
+// NVFP4 GEMV for one bf16 activation row (decode, and every combo of the routed-expert step):
+// persistent CTAs, tensor-core inner loop in "word" form.
+//
+// A CTA owns a list of 16-row tiles (tile = blockIdx.x + i * gridDim.x). The activation row is staged
+// once per CTA (f16 with a power-of-two scale per 64-value block: exact for bf16), the producer warp
+// streams the tiles' weight bytes through one mbarrier ring without draining it between tiles, and
+// eight consumer warps split the K range of every stage between them.
+//
+// Inner loop. mma.sync.m16n8k16 (f16 x f16 -> f32) takes the f16x2 registers that
+// cvt.rn.f16x2.e2m1x2 makes: A = 16 weight rows x 16 codes, B = the matching activations. The order
+// of k inside an MMA is free as long as A and B agree, so it is chosen to make the loads wide:
+// a "group" is two 36-byte blocks (eight 16-code sub-blocks), a "pair" is two sub-blocks = 16 code
+// bytes of a row, and thread t of a quad takes word t of the pair: ONE 32-bit shared-memory load per
+// row feeds four cvt and two MMAs (bytes 0,1 -> first MMA, bytes 2,3 -> second). Column j of the C
+// tile collects sub-block j of the group: in pair q only columns 2q and 2q+1 have non-zero B, and
+// since B's column index is the lane's quad number, a lane has activations for exactly one pair and
+// reads a 16-byte zero chunk for the other three (one select + one 128-bit load per pair). After the
+// eight MMAs of a group the C tile holds eight sub-block sums per row, and the UE4M3 scale x tensor
+// scale x inverse activation scale is applied once per sub-block and row.
+// Products are exact, accumulation is the tensor core's f32 and f32 FMAs in a fixed order.
+#include "common.cuh"
+#include "nvfp4_gemv.cuh"
+
+namespace {
+
+constexpr int NW = 8;  // consumer warps
+constexpr int NTHREADS = (NW + 1) * 32;
+constexpr int MAX_STAGES = 8;
+constexpr int RED_DEPTH = 10;  // tile sums in flight: a warp runs at most MAX_STAGES chunks ahead of warp 0
+constexpr int XB = 128;        // one 64-value block of f16 activations, 16-byte chunks XOR-swizzled
+// header: mbarriers (full, empty, tile, x), two 16-byte zero chunks 2048 B apart (the second group of a chunk
+// reads everything 2048 B further on), scale table, tile sums
+constexpr int TBAR_OFF = 128, XBAR_OFF = 208, ZERO_OFF = 224;
+constexpr int ZERO2_OFF = ZERO_OFF + 2048;
+constexpr int LUT_OFF = 2304;
+constexpr int RED_OFF = LUT_OFF + 2048;  // [RED_DEPTH][NW][16] f32
+constexpr int HDR = RED_OFF + RED_DEPTH * NW * 16 * 4;
+static_assert(ZERO2_OFF + 16 <= LUT_OFF && TBAR_OFF + RED_DEPTH * 8 <= XBAR_OFF, "header regions overlap");
+constexpr int ROWS = 16;
+// not volatile: a pure function of its operands, free to be scheduled between the shared-memory loads
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// TX: 36-byte blocks per row and stage (32, 16 or 8); the last chunk of a row may be shorter
+// CPS: CTAs per SM the register allocation must allow (2, 3 or 4)
+template <int TX, int CPS>
+__global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int pstride = TX * 36 + 16;  // padded: the eight rows of a quad column hit distinct banks
+    constexpr int stage_bytes = ROWS * pstride;
+    constexpr int GPW = TX / 2 / NW > 0 ? TX / 2 / NW : 1;  // groups per warp and full chunk
+    const int bpr = p.k >> 6;
+    const size_t row_bytes = (size_t)bpr * 36;
+    const int nch = (bpr + TX - 1) / TX;
+    const int S = p.stages;
+    const uint8_t* w0 = p.w0;
+    const uint8_t* w1 = p.w1;
+    const char* xbase = (const char*)p.x;
+    char* ybase = (char*)p.y;
+    if (p.ids) {
+        const int c = p.order ? p.order[blockIdx.y] : (int)blockIdx.y;
+        const int e = p.ids[c];
+        if (e < 0) return;  // uniform over the CTA, before any barrier
+        w0 = (const uint8_t*)p.tab0[e];
+        if (!w0) return;
+        w1 = p.tab1 ? (const uint8_t*)p.tab1[e] : (p.fused_up_rows > 0 ? w0 + (size_t)p.fused_up_rows * row_bytes : nullptr);
+        xbase += (size_t)(c / p.x_div) * p.k * 2;
+        ybase += (size_t)c * p.ldy * (p.out_f32 ? 4 : 2);
+    }
+    const bool gu = w1 != nullptr;
+
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = full + MAX_STAGES;
+    uint64_t* tbar = (uint64_t*)(smem + TBAR_OFF);  // [RED_DEPTH] one per tile-sum buffer
+    uint64_t* xbar = (uint64_t*)(smem + XBAR_OFF);
+    float* lut = (float*)(smem + LUT_OFF);  // [2][256] ue4m3 * gs
+    float* red = (float*)(smem + RED_OFF);  // [RED_DEPTH][NW][16] partial sums of a tile
+    uint8_t* xs0 = smem + HDR;              // [bpr][128] f16 activations
+    float* xinv0 = (float*)(xs0 + (size_t)bpr * XB);
+    uint8_t* stage0 = (uint8_t*)(xinv0 + ((bpr + 3) & ~3));
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int per_cta = gu ? ROWS / 2 : ROWS;  // gate/up: 8 indices, row slots 0-7 gate, 8-15 up
+    const int ntiles = (p.rows + per_cta - 1) / per_cta;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NW);
+        }
+        for (int i = 0; i < RED_DEPTH; i++) mbar_init(&tbar[i], NW);
+        mbar_init(xbar, 1);
+        mbar_fence_init();
+    }
+    if (tid < 4) ((uint32_t*)(smem + ZERO_OFF))[tid] = 0u;
+    if (tid >= 4 && tid < 8) ((uint32_t*)(smem + ZERO2_OFF))[tid - 4] = 0u;
+    {
+        const float g0 = p.gs0[0], g1 = gu ? p.gs1[0] : g0;
+        for (int b = tid; b < 256; b += NTHREADS) {
+            const float u = ue4m3_f32((uint32_t)b, true);
+            lut[b] = u * g0;
+            lut[256 + b] = u * g1;
+        }
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == NW) {
+        // ------------------------------------------------------------ weight producer warp
+        const uint64_t pol = l2_policy_evict_first();
+        int s = 0;
+        uint32_t par = 0;  // parity of the current use of stage s
+        bool first_round = true;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            const int row0 = tile * per_cta;
+            const int row = gu ? row0 + (lane & 7) : row0 + lane;
+            const uint8_t* base = (gu && ((lane >> 3) & 1)) ? w1 : w0;
+            const uint8_t* src = (lane < ROWS && row < p.rows) ? base + (size_t)row * row_bytes : nullptr;
+            const uint32_t nvalid = (uint32_t)__popc(__ballot_sync(0xffffffffu, src != nullptr));
+            for (int c = 0; c < nch; c++) {
+                const int nblk = min(TX, bpr - c * TX);
+                const uint32_t piece = (uint32_t)nblk * 36u;
+                if (!first_round && !mbar_wait(&empty[s], par ^ 1u)) {
+                    cn_dev_fail(CN_DEV_WAIT_EMPTY);
+                    return;
+                }
+                uint8_t* st = stage0 + (size_t)s * stage_bytes;
+                if (lane == 0) {
+                    mbar_expect_tx(&full[s], nvalid * piece);
+                    mbar_arrive(&full[s]);
+                }
+                __syncwarp();
+                if (src) bulk_g2s_stream(st + (size_t)lane * pstride, src + (size_t)c * TX * 36, piece, &full[s], pol);
+                if (++s == S) {
+                    s = 0;
+                    par ^= 1u;
+                    first_round = false;
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumer warps: the activation row first
+    if (tid == 0) {
+        pdl_wait();  // the activations may come from the previous kernel of the stream
+        mbar_expect_tx(xbar, (uint32_t)p.k * 2u);
+        mbar_arrive(xbar);
+        bulk_g2s(xs0, xbase, (uint32_t)p.k * 2u, xbar);
+    }
+    bool ok = mbar_wait(xbar, 0);
+    if (!ok) cn_dev_fail(CN_DEV_WAIT_FULL);
+    // in place bf16 -> f16 * 2^e per 64-value block, chunk i of block b stored at chunk i ^ (b & 7). Eight
+    // lanes per block, one 16-byte chunk each (k % 256 == 0 makes every warp wholly in or out of range).
+    for (int task = tid; ok && task < bpr * 8; task += NW * 32) {
+        const int b = task >> 3, i = task & 7;
+        uint4* blkp = (uint4*)(xs0 + (size_t)b * XB);
+        const uint4 raw = blkp[i];
+        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+        float amax = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            amax = fmaxf(amax, fabsf(__uint_as_float(u[q] << 16)));
+            amax = fmaxf(amax, fabsf(__uint_as_float(u[q] & 0xffff0000u)));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));  // every lane of the block has loaded its chunk by now
+        uint32_t e = (__float_as_uint(amax) >> 23) & 0xFF;
+        float mul = 1.0f, inv = 1.0f;
+        if (amax > 0.0f && e < 255) {
+            e = e < 15 ? 15 : e;
+            mul = __uint_as_float((268u - e) << 23);
+            inv = __uint_as_float((e - 14u) << 23);
+        }
+        uint32_t h[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const __half2 hh = __floats2half2_rn(__uint_as_float(u[q] << 16) * mul, __uint_as_float(u[q] & 0xffff0000u) * mul);
+            h[q] = *(const uint32_t*)&hh;
+        }
+        blkp[i ^ (b & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
+        if (i == 0) xinv0[b] = inv;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+
+    // ---------------------------------------------------------------- main loop
+    const int g = lane >> 2, t = lane & 3;
+    // the one pair of a group whose B columns this lane fills (column g = sub-block g of the group, and the
+    // k slots of thread t belong to sub-block 2q + (t >> 1) of pair q): -1 = none
+    const int myq = ((g & 1) == (t >> 1)) ? (g >> 1) : -1;
+    // byte offset (from smem) of this lane's 16 activations in the first group of a chunk: block 2 warp + (g >> 2),
+    // chunk 2 (g & 3) + (t & 1), swizzled by the block index mod 8, which chunk and group number do not change
+    const int xb0 = 2 * warp + (g >> 2);
+    const uint32_t xoff_lane = (uint32_t)(HDR + xb0 * XB + (((2 * (g & 3) + (t & 1)) ^ (xb0 & 7)) << 4));
+    const uint32_t aoff = (uint32_t)(g * pstride + 4 * t + warp * 72);
+    const int sdelta = -4 * t + (t >> 1) * 36 + 2 * (t & 1);  // from a row's code word to its two scale bytes
+    const float* xinv_lane = xinv0 + 2 * warp + (t >> 1);
+    const float* lut_b = lut + (gu ? 256 : 0);  // gate/up: rows 8-15 are up rows
+
+    int s = 0, rslot = 0;
+    uint32_t par = 0, rpar = 0;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g + 8 of the tile, this lane's two columns
+        for (int c = 0; c < nch; c++) {
+            const int ng = min(TX, bpr - c * TX) >> 1;  // groups of two blocks in this chunk
+            if (!mbar_wait(&full[s], par)) {
+                cn_dev_fail(CN_DEV_WAIT_FULL);
+                ok = false;
+                break;
+            }
+            const uint8_t* pa0 = stage0 + (size_t)s * stage_bytes + aoff;
+            const uint32_t xoff = xoff_lane + (uint32_t)(c * TX * XB);
+            uint32_t bq[4];  // where this lane's B registers of pair q come from: its activations or the zero chunk
+#pragma unroll
+            for (int q = 0; q < 4; q++) bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
+            const float* xip = xinv_lane + c * TX;
+#pragma unroll
+            for (int j = 0; j < GPW; j++) {
+                if (warp + NW * j < ng) {
+                    const uint8_t* pa = pa0 + j * (NW * 72);
+                    const uint8_t* pb = pa + 8 * pstride;
+                    float cc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const uint4 xv = *(const uint4*)(smem + bq[q] + j * 2048);
+                        const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
+                        uint32_t ha[4], hb[4];
+                        e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
+                        e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
+                        mma16816(cc, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+                        mma16816(cc, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+                    }
+                    // columns 2t, 2t + 1 of C = sub-blocks 2t, 2t + 1 of the group: block t >> 1, scale bytes 2 (t & 1), + 1
+                    const uint8_t* sc = pa + sdelta;
+                    const float s0 = lut[sc[0]], s1 = lut[sc[1]], s2 = lut_b[sc[8 * pstride]], s3 = lut_b[sc[8 * pstride + 1]];
+                    const float xi = xip[16 * j];
+                    acc0 = fmaf(fmaf(cc[1], s1, cc[0] * s0), xi, acc0);
+                    acc1 = fmaf(fmaf(cc[3], s3, cc[2] * s2), xi, acc1);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (++s == S) {
+                s = 0;
+                par ^= 1u;
+            }
+        }
+        if (!ok) break;
+        // the four lanes of a quad hold two columns each; then the eight warps' K ranges meet in shared memory:
+        // every warp posts its 16 sums and arrives on the slot's barrier, warp 0 alone waits for all eight
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+        float* rb = red + rslot * (NW * 16);
+        if (t == 0) {
+            rb[warp * 16 + g] = acc0;
+            rb[warp * 16 + g + 8] = acc1;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tbar[rslot]);
+        if (warp == 0) {
+            if (!mbar_wait(&tbar[rslot], rpar)) {
+                cn_dev_fail(CN_DEV_WAIT_FULL);
+                ok = false;
+            } else if (lane < per_cta) {
+                float v0 = rb[lane], v1 = gu ? rb[lane + 8] : 0.0f;
+                for (int w = 1; w < NW; w++) {  // warps in order: deterministic
+                    v0 += rb[w * 16 + lane];
+                    if (gu) v1 += rb[w * 16 + lane + 8];
+                }
+                const int row = tile * per_cta + lane;
+                if (row < p.rows) {
+                    const float v = gu ? act_gu(v0, v1, p.limit) : v0;
+                    if (p.out_f32)
+                        ((float*)ybase)[row] = v;
+                    else
+                        ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+        if (++rslot == RED_DEPTH) {
+            rslot = 0;
+            rpar ^= 1u;
+        }
+    }
+}
+
+int g_m1_stages = 0, g_m1_cps = 0, g_m1_tx = 0;
+
+template <int TX, int CPS>
+int launch_m1(const cudaLaunchConfig_t& cfg, const GemvParams& p) {
+    static bool attr = false;
+    if (!attr) {
+        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemv_m1_kernel<TX, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        attr = true;
+    }
+    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS>, p));
+    return CN_OK;
+}
+
+}  // namespace
+
+void cn_gemv_m1_set(int key, int value) {
+    if (key == 0) g_m1_stages = value;
+    if (key == 1) g_m1_cps = value;
+    if (key == 2) g_m1_tx = value;
+}
+
+int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
+    const int rows = a.rows, k = a.k;
+    const bool routed = a.ids != nullptr;
+    const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;
+    const int bpr = k / 64;
+    int tx = bpr >= 32 ? 32 : (bpr >= 16 ? 16 : 8);
+    if (g_m1_tx == 32 || g_m1_tx == 16 || g_m1_tx == 8) tx = g_m1_tx;
+    const int pstride = tx * 36 + 16;
+    const size_t stage_bytes = (size_t)ROWS * pstride;
+    const size_t xbytes = (size_t)bpr * XB + (size_t)((bpr + 3) & ~3) * 4;
+    const int per_cta = gu ? ROWS / 2 : ROWS;
+    const int ntiles = (rows + per_cta - 1) / per_cta;
+    const int nch = (bpr + tx - 1) / tx;
+    // CTAs per SM: as many as leave every CTA a ring of at least three stages
+    int cps = 2;
+    for (int c = 4; c > 2; c--)
+        if ((227 * 1024) / c - 1024 - (long long)HDR - (long long)xbytes >= 3 * (long long)stage_bytes) {
+            cps = c;
+            break;
+        }
+    if (g_m1_cps >= 2 && g_m1_cps <= 4) cps = g_m1_cps;
+    // persistent CTAs, each walking its share of the tiles (the routed form keeps one tile per CTA)
+    int grid = ntiles;
+    if (!routed && grid > 148 * cps) grid = 148 * cps;
+    const long long budget = (227 * 1024) / cps - 1024 - (long long)HDR - (long long)xbytes;
+    int stages = (int)(budget / (long long)stage_bytes);
+    if (g_m1_stages > 0) stages = g_m1_stages;
+    stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+    const int total_chunks = nch * ((ntiles + grid - 1) / grid);
+    if (stages > total_chunks) stages = total_chunks;
+    if (stages < 1) stages = 1;
+    const size_t smem = HDR + xbytes + stages * stage_bytes;
+    if (smem > 226 * 1024) CN_FAIL(CN_ERR_LIMIT, "%s: k = %d needs %zu B of shared memory per block", who, k, smem);
+    GemvParams p;
+    p.w0 = (const uint8_t*)a.w0, p.w1 = (const uint8_t*)a.w1, p.gs0 = a.gs0, p.gs1 = a.gs1 ? a.gs1 : a.gs0, p.x = a.x, p.y = a.y;
+    p.rows = rows, p.k = k, p.m = 1, p.ldy = a.ldy, p.limit = a.limit, p.tx = tx, p.stages = stages, p.out_f32 = a.out_f32;
+    p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, (unsigned)(routed ? a.combos : 1));
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+#define CN_M1_CASE(TXV, CPSV) \
+    if (tx == TXV && cps == CPSV) return launch_m1<TXV, CPSV>(cfg, p);
+    CN_M1_CASE(32, 2) CN_M1_CASE(32, 3) CN_M1_CASE(32, 4) CN_M1_CASE(16, 2) CN_M1_CASE(16, 3) CN_M1_CASE(16, 4)
+    CN_M1_CASE(8, 2) CN_M1_CASE(8, 3) CN_M1_CASE(8, 4)
+#undef CN_M1_CASE
+    CN_FAIL(CN_ERR_SHAPE, "%s: no kernel for %d blocks per stage, %d CTAs per SM", who, tx, cps);
+}
