@@ -21,6 +21,9 @@ sys.path.insert(0, ROOT)
 
 METRIC = "nvfp4_gemv_hbm_gbs"
 UNIT = "GB/s"
+# DRAM bytes moved per algorithmic byte by the M = 1 kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
+# captured gate/up launch (103.4 MB) over its algorithmic bytes (100.3 MB); the capture is summarised under profiles/
+TRAFFIC_RATIO = 1.031
 
 
 def measured_peak():
@@ -31,7 +34,7 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons sampled every 100 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -40,7 +43,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -134,8 +137,8 @@ def reference_arm(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 decode, 4 = MTP verify)")
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--impl", default="crownest")
@@ -162,9 +165,9 @@ def main():
     x_host = torch.randn((m, stack.hidden), generator=gen).to(torch.bfloat16).pin_memory()
     y_host = torch.empty((m, stack.hidden), dtype=torch.bfloat16).pin_memory()
     stack.x[:m].copy_(x_host)
-    use_graph = world == 1
-    if use_graph:
-        stack.capture(m)
+    # the whole step (256 launches, with their all-gathers when tensor parallel) replays as one CUDA graph
+    stack.capture(m)
+    use_graph = True
     step = (lambda: stack.graph.replay()) if use_graph else (lambda: stack.run_layers(m))
 
     def barrier():
@@ -215,8 +218,9 @@ def main():
                            "activations": "bf16 in/out, f32 accumulate", "parallelism": f"tp{world} row split + all-gather" if world > 1 else "none",
                            "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (bytes_step / 1e9),
                            "launch": "CUDA graph replay" if use_graph else "eager launches", "tokens_per_s": m / (ms_step * 1e-3)},
-                "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "traffic": None,
-                             "peak_kind": peak_kind, "kernel": "nvfp4_gemv_kernel", "bytes_per_launch": bytes_step / world / stack.launches_per_step,
+                "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "traffic": TRAFFIC_RATIO * bytes_step / world / stack.launches_per_step if m == 1 else None,
+                             "traffic_note": "dram read+write bytes of one ncu capture of the gate/up launch (profiles/), scaled to the average launch by bytes",
+                             "peak_kind": peak_kind, "kernel": "nvfp4_gemv_m1_kernel" if m == 1 else "nvfp4_gemv_mma_kernel", "bytes_per_launch": bytes_step / world / stack.launches_per_step,
                              "us_per_launch": ms_step * 1e3 / stack.launches_per_step},
                 "e2e": {"value": bytes_step / (e2e_s / args.steps) / 1e9, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
                         "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_s / args.steps * 1e3},

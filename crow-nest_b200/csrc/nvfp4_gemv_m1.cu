@@ -28,14 +28,14 @@ constexpr int NTHREADS = (NW + 1) * 32;
 constexpr int MAX_STAGES = 8;
 constexpr int RED_DEPTH = 10;  // tile sums in flight: a warp runs at most MAX_STAGES chunks ahead of warp 0
 constexpr int XB = 128;        // one 64-value block of f16 activations, 16-byte chunks XOR-swizzled
-// header: mbarriers (full, empty, tile, x), two 16-byte zero chunks 2048 B apart (the second group of a chunk
+// header: mbarriers (full, empty, tile), two 16-byte zero chunks 2048 B apart (the second group of a chunk
 // reads everything 2048 B further on), scale table, tile sums
-constexpr int TBAR_OFF = 128, XBAR_OFF = 208, ZERO_OFF = 224;
+constexpr int TBAR_OFF = 128, ZERO_OFF = 224;
 constexpr int ZERO2_OFF = ZERO_OFF + 2048;
 constexpr int LUT_OFF = 2304;
 constexpr int RED_OFF = LUT_OFF + 2048;  // [RED_DEPTH][NW][16] f32
 constexpr int HDR = RED_OFF + RED_DEPTH * NW * 16 * 4;
-static_assert(ZERO2_OFF + 16 <= LUT_OFF && TBAR_OFF + RED_DEPTH * 8 <= XBAR_OFF, "header regions overlap");
+static_assert(ZERO2_OFF + 16 <= LUT_OFF && TBAR_OFF + RED_DEPTH * 8 <= ZERO_OFF, "header regions overlap");
 constexpr int ROWS = 16;
 // not volatile: a pure function of its operands, free to be scheduled between the shared-memory loads
 __device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -75,7 +75,6 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + MAX_STAGES;
     uint64_t* tbar = (uint64_t*)(smem + TBAR_OFF);  // [RED_DEPTH] one per tile-sum buffer
-    uint64_t* xbar = (uint64_t*)(smem + XBAR_OFF);
     float* lut = (float*)(smem + LUT_OFF);  // [2][256] ue4m3 * gs
     float* red = (float*)(smem + RED_OFF);  // [RED_DEPTH][NW][16] partial sums of a tile
     uint8_t* xs0 = smem + HDR;              // [bpr][128] f16 activations
@@ -86,27 +85,21 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     const int per_cta = gu ? ROWS / 2 : ROWS;  // gate/up: 8 indices, row slots 0-7 gate, 8-15 up
     const int ntiles = (p.rows + per_cta - 1) / per_cta;
 
-    if (tid == 0) {
-        for (int s = 0; s < S; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], NW);
+    // The producer warp sets up the ring's barriers itself and starts streaming at once (the weights do not
+    // depend on the previous kernel); the consumers meet it on named barrier 2 before their first wait.
+    if (warp == NW) {
+        if (lane == 0) {
+            for (int s = 0; s < S; s++) {
+                mbar_init(&full[s], 1);
+                mbar_init(&empty[s], NW);
+            }
+            for (int i = 0; i < RED_DEPTH; i++) mbar_init(&tbar[i], NW);
+            mbar_fence_init();
         }
-        for (int i = 0; i < RED_DEPTH; i++) mbar_init(&tbar[i], NW);
-        mbar_init(xbar, 1);
-        mbar_fence_init();
+        __syncwarp();
+        asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
+        pdl_launch_dependents();
     }
-    if (tid < 4) ((uint32_t*)(smem + ZERO_OFF))[tid] = 0u;
-    if (tid >= 4 && tid < 8) ((uint32_t*)(smem + ZERO2_OFF))[tid - 4] = 0u;
-    {
-        const float g0 = p.gs0[0], g1 = gu ? p.gs1[0] : g0;
-        for (int b = tid; b < 256; b += NTHREADS) {
-            const float u = ue4m3_f32((uint32_t)b, true);
-            lut[b] = u * g0;
-            lut[256 + b] = u * g1;
-        }
-    }
-    __syncthreads();
-    pdl_launch_dependents();
 
     if (warp == NW) {
         // ------------------------------------------------------------ weight producer warp
@@ -144,21 +137,25 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         return;
     }
 
-    // ---------------------------------------------------------------- consumer warps: the activation row first
-    if (tid == 0) {
-        pdl_wait();  // the activations may come from the previous kernel of the stream
-        mbar_expect_tx(xbar, (uint32_t)p.k * 2u);
-        mbar_arrive(xbar);
-        bulk_g2s(xs0, xbase, (uint32_t)p.k * 2u, xbar);
+    // ---------------------------------------------------------------- consumer warps: scale table, then the activation row
+    if (tid < 4) ((uint32_t*)(smem + ZERO_OFF))[tid] = 0u;
+    if (tid >= 4 && tid < 8) ((uint32_t*)(smem + ZERO2_OFF))[tid - 4] = 0u;
+    {
+        const float g0 = p.gs0[0], g1 = gu ? p.gs1[0] : g0;
+        for (int b = tid; b < 256; b += NW * 32) {
+            const float u = ue4m3_f32((uint32_t)b, true);
+            lut[b] = u * g0;
+            lut[256 + b] = u * g1;
+        }
     }
-    bool ok = mbar_wait(xbar, 0);
-    if (!ok) cn_dev_fail(CN_DEV_WAIT_FULL);
-    // in place bf16 -> f16 * 2^e per 64-value block, chunk i of block b stored at chunk i ^ (b & 7). Eight
-    // lanes per block, one 16-byte chunk each (k % 256 == 0 makes every warp wholly in or out of range).
-    for (int task = tid; ok && task < bpr * 8; task += NW * 32) {
+    pdl_launch_dependents();
+    pdl_wait();  // the activations may come from the previous kernel of the stream
+    bool ok = true;
+    // bf16 -> f16 * 2^e per 64-value block, chunk i of block b stored at chunk i ^ (b & 7). Eight lanes per block,
+    // one 16-byte chunk each, straight from global memory (k % 256 == 0 makes every warp wholly in or out of range).
+    for (int task = tid; task < bpr * 8; task += NW * 32) {
         const int b = task >> 3, i = task & 7;
-        uint4* blkp = (uint4*)(xs0 + (size_t)b * XB);
-        const uint4 raw = blkp[i];
+        const uint4 raw = __ldcg((const uint4*)xbase + task);
         const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
         float amax = 0.0f;
 #pragma unroll
@@ -168,7 +165,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         }
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));  // every lane of the block has loaded its chunk by now
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
         uint32_t e = (__float_as_uint(amax) >> 23) & 0xFF;
         float mul = 1.0f, inv = 1.0f;
         if (amax > 0.0f && e < 255) {
@@ -182,10 +179,10 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             const __half2 hh = __floats2half2_rn(__uint_as_float(u[q] << 16) * mul, __uint_as_float(u[q] & 0xffff0000u) * mul);
             h[q] = *(const uint32_t*)&hh;
         }
-        blkp[i ^ (b & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
+        ((uint4*)(xs0 + (size_t)b * XB))[i ^ (b & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
         if (i == 0) xinv0[b] = inv;
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+    asm volatile("bar.sync 2, %0;" ::"n"(NTHREADS) : "memory");  // staging done, and the ring's barriers are initialised
 
     // ---------------------------------------------------------------- main loop
     const int g = lane >> 2, t = lane & 3;
