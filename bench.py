@@ -134,6 +134,87 @@ def reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def moe_arm(args, rank, world, local):
+    """`--workload moe` / `mul1`: the routed-expert decode step (BASELINE configs 2 and 3), `--tokens` rows per rank,
+    experts placed expert-parallel over the ranks (weak scaling: the global batch grows with the ranks)."""
+    import torch
+    import torch.distributed as dist
+    from crownest_b200 import _lib, workloads
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _lib.lib()
+    cls = workloads.MoeDecode if args.workload == "moe" else workloads.Mul1MoeDecode
+    wl = cls(args.tokens, device=f"cuda:{local}", rank=rank, world=world, group=None)
+    x_host = wl.x.cpu().pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        wl.step()
+        st.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            wl.step()
+    torch.cuda.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        wl.x.copy_(x_host, non_blocking=True)
+        graph.replay()
+        y_host.copy_(wl.y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    nbytes, distinct = wl.bytes_per_step()
+    t = torch.tensor([ms, e2e_s, float(nbytes), float(distinct)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(mx[0]), float(mx[1])
+    if rank == 0:
+        ms_step = ms / args.steps
+        toks = args.tokens * world
+        peak, peak_kind = measured_peak()
+        gbs = nbytes / (ms_step * 1e-3) / 1e9
+        shape = ("hidden 2048, 512 experts, inter 512, shared expert 512, softmax top-10, NVFP4" if args.workload == "moe" else
+                 "hidden 4096, 64 experts, inter 1536, top-4, EXL3 MUL1 K=3")
+        line = {"metric": "moe_decode_tok_s", "value": toks / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"routed-expert decode step ({shape}), {args.tokens} tokens per rank", "parallelism": f"ep{world}" if world > 1 else "none",
+                           "l2": "the expert set changes with the routing; weights of one step (%.0f MB on rank 0) fit L2, so the working set is flushed "
+                                 "only by its own size at larger batches" % (nbytes / 1e6), "launch": "CUDA graph replay",
+                           "distinct_experts_rank0_tokens": distinct},
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                             "kernel": "nvfp4_gemv_m1_kernel (routed form)" if args.workload == "moe" else "mul1_gemv_kernel",
+                             "note": "algorithmic bytes = distinct experts of rank 0's tokens x expert bytes + shared expert + activations"},
+                "e2e": {"value": toks / (e2e_s / args.steps), "unit": "tok/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+                "gpu_launches": args.steps * getattr(wl, "launches_per_step", 8), "clocks": clocks, "device_status": _lib.device_status()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -143,12 +224,16 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--impl", default="crownest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mul1"], help="dense = the headline (config 1); moe / mul1 = configs 2 / 3")
+    ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         return reference_arm(args, rank)
     args.warmup = max(args.warmup, 3)
+    if args.workload != "dense":
+        return moe_arm(args, rank, world, local)
 
     import torch
     import torch.distributed as dist

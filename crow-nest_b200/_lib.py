@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 SO_PATH = os.path.join(_HERE, "libcrownest_b200.so")
 CSRC = os.path.join(_HERE, "csrc")
 
-CN_F32, CN_BF16 = 0, 1
+CN_F32, CN_BF16, CN_BF16_IN_F32_OUT = 0, 1, 2
 CN_MAX_M = 8
 
 

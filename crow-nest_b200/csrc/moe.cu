@@ -136,6 +136,9 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!p) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_run: null plan");
     if (tokens < 1 || tokens > p->max_tokens) CN_FAIL(CN_ERR_LIMIT, "cn_moe_nvfp4_run: %d tokens, the plan holds %d", tokens, p->max_tokens);
+    if (dtype != CN_F32 && dtype != CN_BF16 && dtype != CN_BF16_IN_F32_OUT) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_run: dtype %d", dtype);
+    const int ydtype = dtype == CN_BF16 ? CN_BF16 : CN_F32;  // expert-parallel partial sums leave in f32
+    if (dtype == CN_BF16_IN_F32_OUT) dtype = CN_BF16;
     const int combos = tokens * p->topk;
     if (int rc = cn_moe_sort(ids, p->order, combos, p->experts, stream_)) return rc;
     // routed gate|up + activation: h[c] = act(gate_e x_t, up_e x_t), c = t * topk + j
@@ -167,5 +170,5 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
         }
         shared = p->ys;
     }
-    return cn_moe_combine(p->eo, wts, ids, table_dn, shared, sgate, y, tokens, p->hidden, p->topk, dtype, stream_);
+    return cn_moe_combine(p->eo, wts, ids, table_dn, shared, sgate, y, tokens, p->hidden, p->topk, ydtype, stream_);
 }

@@ -30,6 +30,26 @@ def _rand_nvfp4_device(rows, cols, gen, device, scale_sigma=0.05):
     return w.reshape(-1)
 
 
+def tp_rows(n, rank, world):
+    """Output rows [lo, hi) of an [n][k] matrix held by `rank`: contiguous, equal ranges."""
+    if n % world:
+        raise CrownestError(f"tensor parallel: {n} output rows do not split over {world} ranks")
+    return rank * (n // world), (rank + 1) * (n // world)
+
+
+def gather_rows(part, full, m, world, group=None):
+    """All-gather the ranks' output slices part [m][n / world] into full [m][n] (rank r's columns at
+    tp_rows(n, r, world)); works on any backend (NCCL on the device, gloo on the host)."""
+    import torch.distributed as dist
+    if m == 1:
+        dist.all_gather_into_tensor(full[:1].view(-1), part.reshape(-1), group=group)
+    else:
+        # [world][m][n / world] -> [m][n]: gather into a staging buffer, then interleave
+        tmp = torch.empty((world, m, part.shape[1]), dtype=part.dtype, device=part.device)
+        dist.all_gather_into_tensor(tmp.view(-1), part.reshape(-1), group=group)
+        full[:m].copy_(tmp.permute(1, 0, 2).reshape(m, -1))
+
+
 class DenseStack:
     def __init__(self, cfg=None, layers=None, device="cuda", seed=0, rank=0, world=1, group=None, max_m=1, dtype=torch.bfloat16):
         cfg = dict(cfg or synth.DENSE_27B)
@@ -76,15 +96,7 @@ class DenseStack:
         return sum(t.w.numel() for mats in self.w for t in mats.values())
 
     def _gather(self, name, full, m):
-        import torch.distributed as dist
-        # [world][m][n/world] -> [m][n]: gather into a staging view, then interleave
-        part = self.part[name][:m]
-        if m == 1:
-            dist.all_gather_into_tensor(full[:1].view(-1), part.reshape(-1), group=self.group)
-        else:
-            tmp = torch.empty((self.world, m, part.shape[1]), dtype=part.dtype, device=part.device)
-            dist.all_gather_into_tensor(tmp.view(-1), part.reshape(-1), group=self.group)
-            full[:m].copy_(tmp.permute(1, 0, 2).reshape(m, -1))
+        gather_rows(self.part[name][:m], full, m, self.world, self.group)
 
     def _proj(self, w, x, name, full, m, gu=None):
         out = full[:m] if self.world == 1 else self.part[name][:m]

@@ -11,7 +11,7 @@ import numpy as np
 import torch
 
 from . import ops
-from ._lib import CN_BF16, CN_F32, CrownestError, check, lib
+from ._lib import CN_BF16, CN_BF16_IN_F32_OUT, CN_F32, CrownestError, check, lib
 
 
 def _stream():
@@ -74,12 +74,17 @@ class GpuMoePlan:
 
     new = classmethod(lambda cls, *a, **k: cls(*a, **k))
 
-    def experts_run(self, w: GpuMoeWeights, ids, wts, x, y=None, limit=0.0, sgate=None):
-        """`experts`: everything after the routing - routed experts, shared expert, combine."""
+    def experts_run(self, w: GpuMoeWeights, ids, wts, x, y=None, limit=0.0, sgate=None, partial=False):
+        """`experts`: everything after the routing - routed experts, shared expert, combine.
+        ``partial``: bf16 x in, f32 y out - the partial sums of a rank that holds part of the experts."""
         tokens = x.shape[0]
         if y is None:
-            y = torch.empty_like(x)
+            y = torch.empty(x.shape, dtype=torch.float32, device=x.device) if partial else torch.empty_like(x)
         dt = CN_BF16 if x.dtype == torch.bfloat16 else CN_F32
+        if partial:
+            if x.dtype != torch.bfloat16 or y.dtype != torch.float32:
+                raise CrownestError("moe partial sums: x must be bf16 and y f32")
+            dt = CN_BF16_IN_F32_OUT
         sh = w.shared or (None, None, None)
         check(lib().cn_moe_nvfp4_run(self.handle, _ptr(w.table_gu), _ptr(w.table_up), _ptr(w.table_dn), _ptr(w.gs_gu), _ptr(w.gs_up),
                                      _ptr(w.gs_dn), _ptr(sh[0]), _ptr(sh[1]), _ptr(sh[2]), _ptr(w.shared_gs), _ptr(sgate),

@@ -33,6 +33,7 @@ extern "C" {
 /* activation / output element type of a call */
 #define CN_F32 0  /* the reference's own dtype (f32 in, f32 out) */
 #define CN_BF16 1 /* bf16 in, bf16 out, f32 accumulation */
+#define CN_BF16_IN_F32_OUT 2 /* cn_moe_nvfp4_run only: bf16 in, f32 out (partial sums of an expert-parallel rank) */
 
 /* status codes */
 #define CN_OK 0
@@ -121,7 +122,9 @@ int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const 
  * gs_gu / gs_up / gs_dn: device f32 tensor scales shared by all experts (gs_up may be null = gs_gu).
  * shared_*: the shared expert's matrices (null = none) with shared_gs a device f32[3] (gate, up,
  * down); sgate: optional device f32 [tokens] gate logits of the shared expert (engine/src/kernels.rs:1593).
- * ids, wts [tokens][topk] from a router above; x, y [tokens][hidden] in `dtype`. */
+ * ids, wts [tokens][topk] from a router above; x, y [tokens][hidden] in `dtype`; CN_BF16_IN_F32_OUT
+ * reads bf16 x and writes f32 y, for a rank that holds part of the experts (the other table entries
+ * null) and hands its partial sums to a reduction across ranks. */
 int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, int shared_inter, int experts, int topk, int max_tokens);
 int cn_moe_nvfp4_plan_destroy(void* plan);
 int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, const unsigned long long* table_up,
