@@ -211,11 +211,37 @@ def moe_arm(args, rank, world, local):
                 "e2e": {"value": toks / (e2e_s / args.steps), "unit": "tok/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
                 "gpu_launches": args.steps * getattr(wl, "launches_per_step", 8), "clocks": clocks, "device_status": _lib.device_status()}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    leave(world, graph)
+
+
+def leave(world, *holders):
+    """End of a multi-rank run. A captured graph that holds NCCL kernels keeps the communicator busy:
+    destroy_process_group() then waits for ever, so the ranks meet once more and exit without tearing it down."""
+    if world <= 1:
+        return
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
+def trace(msg):
+    """Progress lines on stderr when CN_BENCH_TRACE is set (to see where a multi-rank run stops)."""
+    if os.environ.get("CN_BENCH_TRACE"):
+        print(f"[bench rank {os.environ.get('RANK', 0)} +{time.perf_counter() - T0:.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
+T0 = time.perf_counter()
 
 
 def main():
+    if os.environ.get("CN_BENCH_TRACE"):
+        import faulthandler
+        faulthandler.dump_traceback_later(int(os.environ["CN_BENCH_TRACE"]), exit=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -224,6 +250,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--impl", default="crownest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
     ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mul1"], help="dense = the headline (config 1); moe / mul1 = configs 2 / 3")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
     args = ap.parse_args()
@@ -243,6 +270,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _lib.lib()  # fail loudly when the CUDA library is missing: there is no fallback
+    trace("process group up")
 
     stack = dense.DenseStack(layers=args.layers, device=f"cuda:{local}", seed=0, rank=rank, world=world, group=group, max_m=args.m)
     m = args.m
@@ -251,8 +279,9 @@ def main():
     y_host = torch.empty((m, stack.hidden), dtype=torch.bfloat16).pin_memory()
     stack.x[:m].copy_(x_host)
     # the whole step (256 launches, with their all-gathers when tensor parallel) replays as one CUDA graph
-    stack.capture(m)
-    use_graph = True
+    use_graph = not args.eager
+    if use_graph:
+        stack.capture(m)
     step = (lambda: stack.graph.replay()) if use_graph else (lambda: stack.run_layers(m))
 
     def barrier():
@@ -261,9 +290,11 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    trace("captured" if use_graph else "eager")
     for _ in range(args.warmup):
         step()
     barrier()
+    trace("warm")
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -318,8 +349,7 @@ def main():
                                     "sample": f"{passes} passes over whole layers ({host_layers and sum(w.size for w, _, _ in host_layers[0].values())} B each), "
                                               f"{len(host_layers)} distinct layers rotated, AVX2 arm"}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    leave(world, stack)
 
 
 if __name__ == "__main__":

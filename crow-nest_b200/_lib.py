@@ -46,6 +46,8 @@ _SIGS = {
     "cn_moe_nvfp4_plan_create": [C.POINTER(C.c_void_p), _i, _i, _i, _i, _i, _i],
     "cn_moe_nvfp4_plan_destroy": [_vp],
     "cn_moe_nvfp4_run": [_vp] * 16 + [_i, _f, _i, _vp],
+    "cn_nvfp4_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
+    "cn_nvfp4_gemm_workspace_bytes": [_i, _i],
     "cn_mul1_plan_create": [C.POINTER(C.c_void_p), _i, _i, _i, _i, _i, _i],
     "cn_mul1_plan_destroy": [_vp],
     "cn_mul1_gemv": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -67,6 +69,9 @@ def exported_symbols():
     return sorted(_SIGS)
 
 
+_RESTYPES_INIT = {"cn_nvfp4_gemm_workspace_bytes": C.c_size_t}
+
+
 def register(name, argtypes, restype=C.c_int):
     """Other modules of the package add their entry points here before the first load."""
     _SIGS[name] = argtypes
@@ -84,7 +89,7 @@ def lib():
         for name, args in _SIGS.items():
             fn = getattr(L, name)
             fn.argtypes = args
-            fn.restype = _RESTYPES.get(name, C.c_int)
+            fn.restype = _RESTYPES.get(name, _RESTYPES_INIT.get(name, C.c_int))
         _lib = L
     return _lib
 

@@ -122,7 +122,7 @@ class DenseStack:
         engine/src/gen.rs:6100-6225)."""
         st = torch.cuda.Stream()
         with torch.cuda.stream(st):
-            self.run_layers(m)
+            self.run_layers(m)  # warm-up outside the capture: first-use set-up of every kernel and communicator
             st.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=st):

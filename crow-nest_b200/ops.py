@@ -62,6 +62,26 @@ def launch_gemv(w: Fp4, x, y=None, ldy=None):
     return y
 
 
+def launch_gemm(w: Fp4, x, y=None, workspace=None):
+    """Y[t][n] = gs * sum_k X[t][k] W[n][k] for any number of rows t - the prompt GEMM (launch_mma_d,
+    engine/src/gen.rs:2491; glm5_gemm_fp4_tc, engine/src/kernels_glm5_moe.cu:349) on tcgen05 tensor cores.
+    ``workspace``: a uint8 device tensor of at least ``gemm_workspace_bytes(w.cols, t)`` bytes (allocated when absent)."""
+    x2 = x.reshape(-1, w.cols)
+    m = x2.shape[0]
+    if y is None:
+        y = torch.empty((m, w.rows), dtype=x.dtype, device=x.device)
+    need = gemm_workspace_bytes(w.cols, m)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib().cn_nvfp4_gemm(w.w.data_ptr(), w.gs.data_ptr(), x2.data_ptr(), y.data_ptr(), w.rows, w.cols, m, y.stride(0), _dtype_code(x),
+                              workspace.data_ptr(), workspace.numel(), _stream()))
+    return y
+
+
+def gemm_workspace_bytes(k, m):
+    return int(lib().cn_nvfp4_gemm_workspace_bytes(k, m))
+
+
 dense_proj = launch_gemv  # Engine::dense_proj (engine/src/gen.rs:3915): same operator at t == 1 and t <= 4
 
 

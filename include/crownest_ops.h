@@ -133,6 +133,19 @@ int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, const unsig
                      const float* sgate, const int32_t* ids, const float* wts, const void* x, void* y, int tokens, float limit,
                      int dtype, cn_stream_t stream);
 
+/* ---------------------------------------------------------------- NVFP4 GEMM (prefill / batched rows)
+ * Y[t][n] = gs * sum_k X[t][k] * W[n][k] for any m >= 1 activation rows (meant for m > 8; up to 8 rows
+ * cn_nvfp4_gemv streams the weights once and is faster), on tcgen05 tensor cores with the accumulator in
+ * tensor memory. Replaces gemm_fp4_dense (engine/src/kernels.rs:533, launched by launch_mma_d,
+ * engine/src/gen.rs:2491) and glm5_gemm_fp4_tc (engine/src/kernels_glm5_moe.cu:349), with the latter's
+ * arithmetic: weights widened losslessly to f16 (code x block scale), activations as f16 x 2^k per row,
+ * exact products, f32 accumulation. w is the container layout, unchanged. The call allocates nothing:
+ * `workspace` (device, 256-byte aligned) holds the widened activations and must be at least
+ * cn_nvfp4_gemm_workspace_bytes(k, m) bytes; it may be reused by the next call on the same stream. */
+size_t cn_nvfp4_gemm_workspace_bytes(int k, int m);
+int cn_nvfp4_gemm(const void* w, const float* gs, const void* x, void* y, int rows, int k, int m, int ldy, int dtype, void* workspace,
+                  size_t workspace_bytes, cn_stream_t stream);
+
 /* ---------------------------------------------------------------- EXL3 "MUL1" trellis experts
  * A record holds one expert (converter/src/mul1.rs:30-34, engine/src/cpu_mul1.rs:7-12):
  * [gate.trellis][up.trellis][down.trellis][gate.suh][gate.svh][up.suh][up.svh][down.suh][down.svh],
