@@ -214,6 +214,97 @@ def moe_arm(args, rank, world, local):
     leave(world, graph)
 
 
+def gemm_arm(args, rank, world, local):
+    """`--workload gemm`: the batched NVFP4 GEMM (BASELINE config 4): W [17408 x 5120] then [5120 x 17408], --m rows,
+    output columns split over the ranks with an all-gather (tensor parallel). A step = both GEMMs once."""
+    import torch
+    import torch.distributed as dist
+    from crownest_b200 import _lib, dense, ops
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _lib.lib()
+    dev = f"cuda:{local}"
+    m, hidden, inter = args.m, 5120, 17408
+    gen = torch.Generator(device=dev)
+    one = torch.ones(1, device=dev)
+    ncopy = 3  # distinct weight copies rotated step by step: 3 x 100 MB per rank, beyond L2 together with the activations
+    ups, downs = [], []
+    for c in range(ncopy):
+        gen.manual_seed(100 * c + rank)
+        ups.append(ops.Fp4(dense._rand_nvfp4_device(inter // world, hidden, gen, dev), one, inter // world, hidden))
+        downs.append(ops.Fp4(dense._rand_nvfp4_device(hidden // world, inter, gen, dev), one, hidden // world, inter))
+    gen.manual_seed(7)
+    x_host = torch.randn((m, hidden), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+    h = torch.empty((m, inter), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((m, hidden), dtype=torch.bfloat16, device=dev)
+    hp = torch.empty((m, inter // world), dtype=torch.bfloat16, device=dev) if world > 1 else h
+    yp = torch.empty((m, hidden // world), dtype=torch.bfloat16, device=dev) if world > 1 else y
+    y_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
+    ws = torch.empty(ops.gemm_workspace_bytes(inter, m), dtype=torch.uint8, device=dev)
+
+    def step(i):
+        ops.launch_gemm(ups[i % ncopy], x, hp, workspace=ws)
+        if world > 1:
+            dense.gather_rows(hp, h, m, world)
+        ops.launch_gemm(downs[i % ncopy], h, yp, workspace=ws)
+        if world > 1:
+            dense.gather_rows(yp, y, m, world)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        x.copy_(x_host, non_blocking=True)
+        step(i)
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+    if rank == 0:
+        flops = 2.0 * m * hidden * inter * 2
+        ms_step = ms / args.steps
+        tf = flops / (ms_step * 1e-3) / 1e12
+        try:
+            peak, kind = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]), "measured (bf16 GEMM, burst)"
+        except Exception:
+            peak, kind = 1590.0, "fallback"
+        line = {"metric": "nvfp4_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 x f16 -> f32", "data": "synthetic",
+                "config": {"workload": f"nvfp4 GEMM pair [17408 x 5120] and [5120 x 17408], M={m}", "parallelism": f"tp{world} column split + all-gather" if world > 1 else "none",
+                           "l2": "three weight copies rotated (300 MB per rank) plus the activations: larger than L2", "launch": "plain launches"},
+                "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s", "frac": tf / world / peak, "traffic": None, "peak_kind": kind,
+                             "kernel": "nvfp4_gemm_tc5_kernel", "flops_per_launch": flops / 2 / world, "us_per_launch": ms_step * 1e3 / 2,
+                             "hbm_gbs": (2 * hidden * inter // 64 * 36 / world + 2.0 * m * (hidden + inter) * 2) / (ms_step * 1e-3) / 1e9},
+                "e2e": {"value": flops / (e2e_s / args.steps) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+                "gpu_launches": args.steps * 4, "clocks": clocks, "device_status": _lib.device_status()}
+        print(json.dumps(line), flush=True)
+    leave(world)
+
+
 def leave(world, *holders):
     """End of a multi-rank run. A captured graph that holds NCCL kernels keeps the communicator busy:
     destroy_process_group() then waits for ever, so the ranks meet once more and exit without tearing it down."""
@@ -251,7 +342,7 @@ def main():
     ap.add_argument("--impl", default="crownest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mul1"], help="dense = the headline (config 1); moe / mul1 = configs 2 / 3")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mul1", "gemm"], help="dense = the headline (config 1); moe / mul1 = configs 2 / 3")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -259,6 +350,8 @@ def main():
     if args.impl == "reference":
         return reference_arm(args, rank)
     args.warmup = max(args.warmup, 3)
+    if args.workload == "gemm":
+        return gemm_arm(args, rank, world, local)
     if args.workload != "dense":
         return moe_arm(args, rank, world, local)
 

@@ -12,28 +12,40 @@
 // maximum. Products are exact in the tensor core, accumulation is f32 in tensor memory, the epilogue
 // multiplies by gs * 2^-k once.
 //
-// One CTA = 128 weight rows x 128 activation rows, K walked 64 at a time through a 3-stage ring:
-//   warps 0-3  A producers: thread r owns weight row r - 36 container bytes per step (prefetched one
-//              step ahead), cvt.rn.f16x2.e2m1x2 + one HMUL2 per pair, eight 16-byte stores into the
-//              canonical K-major 128-byte-swizzle tile (row r at r * 128, chunk c at c ^ (r & 7));
-//   warps 4-7  B producers: thread j owns activation row j - 128 bytes of f16 per step, same tile form;
-//   warp 8     one lane issues four tcgen05.mma (M 128, N 128, K 16) per stage and commits the stage's
-//              "empty" mbarrier; after the last step it commits the accumulator barrier;
-//   warps 0-3  then read the accumulator (tcgen05.ld 32x32b: lane = weight row, 32 activation rows per
-//              load), scale, and store y[t][n] (for one t the 32 lanes write 32 consecutive n).
-// Every wait is bounded; tensor memory (128 columns) is allocated by warp 8 and freed by it after the
-// CTA has met again, whatever happened in between.
+// One CTA = 128 weight rows x TN activation rows (128, or 256 when more than 128 rows are given), K walked
+// 64 at a time through a 3- or 4-stage ring:
+//   warps 0-7   A producers: thread (r, h) owns half of weight row r's 36-byte block per step (prefetched three
+//               steps ahead), cvt.rn.f16x2.e2m1x2 + one HMUL2 per pair, four 16-byte stores into the canonical
+//               K-major 128-byte-swizzle tile (row r at r * 128, chunk c at c ^ (r & 7));
+//   warps 8-11  B producers: cp.async of the activation rows' 128 bytes per step into the same tile form, the
+//               stage's mbarrier counting the copies as they land, so the threads run ahead of the data;
+//   warp 12     one lane issues four tcgen05.mma (M 128, N TN, K 16) per stage and commits the stage's "empty"
+//               mbarrier; after the last step it commits the accumulator barrier;
+//   warps 0-7   then read the accumulator (tcgen05.ld 32x32b: lane = weight row, 32 activation rows per load),
+//               scale, and store y[t][n] (for one t the 32 lanes write 32 consecutive n).
+// Every wait is bounded; tensor memory (TN columns) is allocated by warp 12 and freed by it after the CTA has
+// met again, whatever happened in between.
 #include "common.cuh"
 
 namespace {
 
-constexpr int TM = 128, TN = 128, TK = 64;
-constexpr int STAGES = 3;
-constexpr int A_BYTES = TM * 128, B_BYTES = TN * 128;
-constexpr int GEMM_THREADS = 9 * 32;
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 1024;  // header + ring + slack for the 1024-byte alignment
+constexpr int TM = 128, TK = 64;
+constexpr int A_BYTES = TM * 128;
+constexpr int A_WARPS = 8, B_WARPS = 4;  // producers; one more warp issues the MMAs
+constexpr int GEMM_THREADS = (A_WARPS + B_WARPS + 1) * 32;
+// TN activation rows per CTA: 128 (3 stages, two CTAs per SM) or 256 (4 stages, one CTA per SM, half the weight
+// decoding per MMA)
+__host__ __device__ constexpr int stages_of(int tn) { return tn == 256 ? 4 : 3; }
+__host__ __device__ constexpr int smem_of(int tn) { return 1024 + stages_of(tn) * (A_BYTES + tn * 128) + 1024; }  // header + ring + alignment slack
 // instruction descriptor, kind::f16: D f32 (bit 4), A and B f16 K-major (0), N >> 3 at bit 17, M >> 4 at bit 24
-constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_of(int tn) { return (1u << 4) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(TM >> 4) << 24); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// this thread's arrival on the barrier, made when its earlier cp.async copies have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 
 // shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: start address >> 4, leading byte
 // offset 1 (unused by swizzled K-major tiles), stride byte offset = 8 rows * 128 B, descriptor version 1, layout 2
@@ -103,7 +115,10 @@ struct GemmParams {
     int rows, k, m, ldy, out_bf16;
 };
 
-__global__ void __launch_bounds__(GEMM_THREADS, 2) nvfp4_gemm_tc5_kernel(const GemmParams p) {
+template <int TN>
+__global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc5_kernel(const GemmParams p) {
+    constexpr int STAGES = stages_of(TN), B_BYTES = TN * 128;
+    constexpr uint32_t IDESC = idesc_of(TN);
     extern __shared__ uint8_t smem_raw[];
     // header in the first 1024 bytes as the runtime gives them; the ring starts at the next 1024-byte boundary
     uint64_t* full = (uint64_t*)smem_raw;
@@ -121,15 +136,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) nvfp4_gemm_tc5_kernel(const G
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 256);
+            mbar_init(&full[s], (A_WARPS + B_WARPS) * 32);
             mbar_init(&empty[s], 1);
         }
         mbar_init(accbar, 1);
         mbar_fence_init();
         *failed = 0;
     }
-    if (warp == 8) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u) : "memory");
+    if (warp == A_WARPS + B_WARPS) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -137,73 +152,99 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) nvfp4_gemm_tc5_kernel(const G
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp < 4) {
-        // ------------------------------------------------------------ A producers: weight row r of the tile
-        const int r = tid, row = row0 + r;
-        const bool live = row < p.rows;
-        const uint32_t* src = (const uint32_t*)(p.w + (size_t)(live ? row : 0) * row_bytes);
-        uint32_t cur[9], nxt[9];
+    if (warp < A_WARPS) {
+        // ------------------------------------------------------------ A producers: unit (row, chunk c) = one code word = eight
+        // weights -> one 16-byte chunk of the tile. Eight consecutive lanes take the eight words of one row's block, so a
+        // warp's load touches four rows' 36 contiguous bytes, and its store fills four whole 128-byte tile rows.
+        constexpr int UNITS = TM * 8 / (A_WARPS * 32);  // 4 per thread and stage
+        constexpr int PF = 3;                           // stages of container words in flight per thread
+        const int c = tid & 7;
+        const uint32_t* src[UNITS];
+        bool live[UNITS];
 #pragma unroll
-        for (int i = 0; i < 9; i++) cur[i] = live ? __ldg(src + i) : 0u;
+        for (int u = 0; u < UNITS; u++) {
+            const int r = (u * (A_WARPS * 32) + tid) >> 3;
+            live[u] = row0 + r < p.rows;
+            src[u] = (const uint32_t*)(p.w + (size_t)(live[u] ? row0 + r : 0) * row_bytes);
+        }
+        uint32_t code[PF][UNITS], scl[PF][UNITS];
+        auto fetch = [&](int d, int kb) {
+#pragma unroll
+            for (int u = 0; u < UNITS; u++) {
+                scl[d][u] = live[u] ? __ldg(src[u] + (size_t)kb * 9) : 0u;
+                code[d][u] = live[u] ? __ldg(src[u] + (size_t)kb * 9 + 1 + c) : 0u;
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < PF; d++) {
+            if (d < bpr) {
+                fetch(d, d);
+            } else {
+#pragma unroll
+                for (int u = 0; u < UNITS; u++) scl[d][u] = code[d][u] = 0u;
+            }
+        }
         bool ok = true;
-        for (int kb = 0; kb < bpr && ok; kb++) {
-            const int s = kb % STAGES;
-            if (kb + 1 < bpr) {
+        for (int kb0 = 0; kb0 < bpr && ok; kb0 += PF) {
 #pragma unroll
-                for (int i = 0; i < 9; i++) nxt[i] = live ? __ldg(src + (size_t)(kb + 1) * 9 + i) : 0u;
-            }
-            if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) {
-                cn_dev_fail(CN_DEV_WAIT_EMPTY);
-                *failed = 1;
-                ok = false;
-                break;
-            }
-            uint8_t* dst = ring + (size_t)s * (A_BYTES + B_BYTES) + (size_t)r * 128;
+            for (int d = 0; d < PF; d++) {
+                const int kb = kb0 + d;
+                if (kb >= bpr || !ok) break;
+                const int s = kb % STAGES;
+                uint32_t cw[UNITS], sw[UNITS];
 #pragma unroll
-            for (int sb = 0; sb < 4; sb++) {
-                // scale of sub-block sb as f16x2 (both halves); the word pair 1 + 2 sb, 2 + 2 sb holds its 16 codes
-                const __half sh = __float2half_rn(ue4m3_f32((cur[0] >> (8 * sb)) & 0xFFu, true));
-                const __half2 s2 = __half2half2(sh);
+                for (int u = 0; u < UNITS; u++) cw[u] = code[d][u], sw[u] = scl[d][u];
+                if (kb + PF < bpr) fetch(d, kb + PF);
+                if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) {
+                    cn_dev_fail(CN_DEV_WAIT_EMPTY);
+                    *failed = 1;
+                    ok = false;
+                    break;
+                }
+                uint8_t* tile = ring + (size_t)s * (A_BYTES + B_BYTES);
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
+                for (int u = 0; u < UNITS; u++) {
+                    const int r = (u * (A_WARPS * 32) + tid) >> 3;
+                    // the chunk's sub-block is c >> 1: its scale in both halves of an f16x2
+                    const __half2 s2 = __half2half2(__float2half_rn(ue4m3_f32((sw[u] >> (8 * (c >> 1))) & 0xFFu, true)));
                     uint32_t f[4];
-                    e2m1x8_to_f16x2(cur[1 + 2 * sb + h], f);
+                    e2m1x8_to_f16x2(cw[u], f);
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         const __half2 v = __hmul2(*(const __half2*)&f[q], s2);
                         f[q] = *(const uint32_t*)&v;
                     }
-                    const int c = 2 * sb + h;
-                    *(uint4*)(dst + ((c ^ (r & 7)) << 4)) = make_uint4(f[0], f[1], f[2], f[3]);
+                    *(uint4*)(tile + (size_t)r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(f[0], f[1], f[2], f[3]);
                 }
+                fence_proxy_async();
+                mbar_arrive(&full[s]);
             }
-            fence_proxy_async();
-            mbar_arrive(&full[s]);
-#pragma unroll
-            for (int i = 0; i < 9; i++) cur[i] = nxt[i];
         }
-    } else if (warp < 8) {
-        // ------------------------------------------------------------ B producers: activation row j of the tile
-        const int j = tid - 128, tok = tok0 + j;
-        const bool live = tok < p.m;
-        const uint4* src = (const uint4*)(p.xh + (size_t)(live ? tok : 0) * p.k);
+    } else if (warp < A_WARPS + B_WARPS) {
+        // ------------------------------------------------------------ B producers: activation rows j, j + 128 .. of the tile,
+        // copied asynchronously (cp.async) so that this thread runs as far ahead as the ring has free stages
+        const int j = tid - A_WARPS * 32;
         bool ok = true;
         for (int kb = 0; kb < bpr && ok; kb++) {
             const int s = kb % STAGES;
-            uint4 v[8];
-#pragma unroll
-            for (int c = 0; c < 8; c++) v[c] = live ? __ldg(src + (size_t)kb * 8 + c) : make_uint4(0u, 0u, 0u, 0u);
             if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) {
                 cn_dev_fail(CN_DEV_WAIT_EMPTY);
                 *failed = 1;
                 ok = false;
                 break;
             }
-            uint8_t* dst = ring + (size_t)s * (A_BYTES + B_BYTES) + A_BYTES + (size_t)j * 128;
+            // eight consecutive lanes copy the eight 16-byte chunks of one activation row: whole 128-byte lines per request
 #pragma unroll
-            for (int c = 0; c < 8; c++) *(uint4*)(dst + ((c ^ (j & 7)) << 4)) = v[c];
-            fence_proxy_async();
-            mbar_arrive(&full[s]);
+            for (int it = 0; it < TN * 8 / (B_WARPS * 32); it++) {
+                const int idx = it * (B_WARPS * 32) + j, jr = idx >> 3, c = idx & 7, tok = tok0 + jr;
+                uint8_t* dst = ring + (size_t)s * (A_BYTES + B_BYTES) + A_BYTES + (size_t)jr * 128 + ((c ^ (jr & 7)) << 4);
+                if (tok < p.m)
+                    cp_async16(smem_u32(dst), (const uint4*)(p.xh + (size_t)tok * p.k) + (size_t)kb * 8 + c);
+                else
+                    *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async();       // the plain zero stores, if any
+            cp_async_arrive(&full[s]);  // counts as this thread's arrival once its copies have landed
         }
     } else if (lane == 0) {
         // ------------------------------------------------------------ MMA issuer
@@ -216,6 +257,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) nvfp4_gemm_tc5_kernel(const G
                 ok = false;
                 break;
             }
+            fence_proxy_async();  // the producers' shared-memory writes (plain stores and cp.async), before the tensor core reads them
             tc_fence_after();
             const uint32_t a_addr = ring_addr + (uint32_t)s * (A_BYTES + B_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
@@ -226,8 +268,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) nvfp4_gemm_tc5_kernel(const G
         if (ok) umma_commit(accbar);
     }
 
-    if (warp < 4) {
-        // ------------------------------------------------------------ epilogue: lane = weight row, 32 activation rows per load
+    if (warp < A_WARPS) {
+        // ------------------------------------------------------------ epilogue: lane = weight row (the warp's quarter of the
+        // accumulator's 128 lanes is warp % 4), 32 activation rows per load; warps 4-7 take the upper half of the columns
         bool ok = !*failed;
         if (ok && !mbar_wait(accbar, 0)) {
             cn_dev_fail(CN_DEV_WAIT_FULL);
@@ -235,12 +278,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) nvfp4_gemm_tc5_kernel(const G
         }
         if (ok) {
             tc_fence_after();
-            const int row = row0 + 32 * warp + lane;
+            const int q = warp & 3, half = warp >> 2;
+            const int row = row0 + 32 * q + lane;
             const float gs = p.gs[0];
-            for (int c0 = 0; c0 < TN; c0 += 32) {
+            for (int c0 = half * (TN / 2); c0 < (half + 1) * (TN / 2); c0 += 32) {
                 if (tok0 + c0 >= p.m) break;  // uniform
                 uint32_t v[32];
-                tmem_ld32(tmem + ((uint32_t)(32 * warp) << 16) + (uint32_t)c0, v);
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, v);
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     const int tok = tok0 + c0 + i;
@@ -257,7 +301,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) nvfp4_gemm_tc5_kernel(const G
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    if (warp == A_WARPS + B_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TN) : "memory");
 }
 
 }  // namespace
@@ -287,13 +331,19 @@ extern "C" int cn_nvfp4_gemm(const void* w, const float* gs, const void* x, void
     CN_CUDA(cudaGetLastError());
     static bool attr = false;
     if (!attr) {
-        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemm_tc5_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(128)));
+        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemm_tc5_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(256)));
         attr = true;
     }
     GemmParams p;
     p.w = (const uint8_t*)w, p.gs = gs, p.xh = xh, p.rs = rs, p.y = y, p.rows = rows, p.k = k, p.m = m, p.ldy = ldy, p.out_bf16 = dtype == CN_BF16;
-    dim3 grid((unsigned)((rows + TM - 1) / TM), (unsigned)((m + TN - 1) / TN));
-    nvfp4_gemm_tc5_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(p);
+    if (m > 128) {
+        dim3 grid((unsigned)((rows + TM - 1) / TM), (unsigned)((m + 255) / 256));
+        nvfp4_gemm_tc5_kernel<256><<<grid, GEMM_THREADS, smem_of(256), stream>>>(p);
+    } else {
+        dim3 grid((unsigned)((rows + TM - 1) / TM), 1);
+        nvfp4_gemm_tc5_kernel<128><<<grid, GEMM_THREADS, smem_of(128), stream>>>(p);
+    }
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
