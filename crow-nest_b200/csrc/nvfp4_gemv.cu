@@ -510,7 +510,7 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     const bool routed = a.ids != nullptr;
     if (routed && (m != 1 || a.combos < 1 || a.x_div < 1)) CN_FAIL(CN_ERR_SHAPE, "%s: the routed form takes one row per combo", who);
     if (a.dtype == CN_BF16 && g_tune_engine != 1 && g_tune_mode != 1) {
-        if (m == 1 && g_tune_engine != 2) return cn_gemv_m1_launch(a, stream, who);
+        if (g_tune_engine != 2) return cn_gemv_m1_launch(a, stream, who);
         if (a.k % 512 == 0) return cn_gemv_mma_launch(a, stream, who);
     }
     const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;

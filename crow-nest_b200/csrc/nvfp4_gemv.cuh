@@ -50,6 +50,7 @@ struct GemvParams {
     const unsigned long long* tab1;  // [experts] up (null with a fused slab or a plain matrix)
     int fused_up_rows;               // > 0: up = gate + fused_up_rows rows of the same slab
     int x_div;
+    int red_depth;  // multi-row tensor-core kernel: tile-sum slots in flight
 };
 
 __device__ __forceinline__ float act_gu(float g, float u, float limit) {

@@ -34,7 +34,6 @@ constexpr int TBAR_OFF = 128, ZERO_OFF = 224;
 constexpr int ZERO2_OFF = ZERO_OFF + 2048;
 constexpr int LUT_OFF = 2304;
 constexpr int RED_OFF = LUT_OFF + 2048;  // [RED_DEPTH][NW][16] f32
-constexpr int HDR = RED_OFF + RED_DEPTH * NW * 16 * 4;
 static_assert(ZERO2_OFF + 16 <= LUT_OFF && TBAR_OFF + RED_DEPTH * 8 <= ZERO_OFF, "header regions overlap");
 constexpr int ROWS = 16;
 // not volatile: a pure function of its operands, free to be scheduled between the shared-memory loads
@@ -44,11 +43,12 @@ __device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, u
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// TX: 36-byte blocks per row and stage (32, 16 or 8); the last chunk of a row may be shorter
-// CPS: CTAs per SM the register allocation must allow (2, 3 or 4)
-template <int TX, int CPS>
+// TX: 36-byte blocks per row and stage (32 or 16); the last chunk of a row may be shorter
+// CPS: CTAs per SM the register allocation must allow; MT: activation rows (1, 2, 4 or 8; p.m of them live)
+template <int TX, int CPS, int MT>
 __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    const float gs0_early = __ldg(p.gs0), gs1_early = __ldg(p.gs1);  // tensor scales: asked for first, used late
     constexpr int pstride = TX * 36 + 16;  // padded: the eight rows of a quad column hit distinct banks
     constexpr int stage_bytes = ROWS * pstride;
     constexpr int GPW = TX / 2 / NW > 0 ? TX / 2 / NW : 1;  // groups per warp and full chunk
@@ -76,10 +76,13 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     uint64_t* empty = full + MAX_STAGES;
     uint64_t* tbar = (uint64_t*)(smem + TBAR_OFF);  // [RED_DEPTH] one per tile-sum buffer
     float* lut = (float*)(smem + LUT_OFF);  // [2][256] ue4m3 * gs
-    float* red = (float*)(smem + RED_OFF);  // [RED_DEPTH][NW][16] partial sums of a tile
-    uint8_t* xs0 = smem + HDR;              // [bpr][128] f16 activations
-    float* xinv0 = (float*)(xs0 + (size_t)bpr * XB);
-    uint8_t* stage0 = (uint8_t*)(xinv0 + ((bpr + 3) & ~3));
+    float* red = (float*)(smem + RED_OFF);  // [red_depth][NW][MT][16] partial sums of a tile
+    const int RD = p.red_depth;             // tile sums in flight (<= RED_DEPTH)
+    const uint32_t xs_off = (uint32_t)(RED_OFF + RD * NW * MT * 64);
+    uint8_t* xs0 = smem + xs_off;           // [MT][bpr][128] f16 activations
+    const uint32_t XS = (uint32_t)bpr * XB;  // bytes of one activation row
+    float* xinv0 = (float*)(xs0 + (size_t)MT * XS);  // [MT][bpr]
+    uint8_t* stage0 = (uint8_t*)(xinv0 + ((MT * bpr + 3) & ~3));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int per_cta = gu ? ROWS / 2 : ROWS;  // gate/up: 8 indices, row slots 0-7 gate, 8-15 up
@@ -93,7 +96,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 mbar_init(&full[s], 1);
                 mbar_init(&empty[s], NW);
             }
-            for (int i = 0; i < RED_DEPTH; i++) mbar_init(&tbar[i], NW);
+            for (int i = 0; i < RD; i++) mbar_init(&tbar[i], NW);
             mbar_fence_init();
         }
         __syncwarp();
@@ -137,25 +140,34 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         return;
     }
 
-    // ---------------------------------------------------------------- consumer warps: scale table, then the activation row
+    // ---------------------------------------------------------------- consumer warps: the activation rows and the scale table.
+    // The first activation loads are issued right after the wait on the previous kernel and the table is built while they
+    // fly; each later load is issued before the previous chunk is converted.
+    pdl_launch_dependents();
+    pdl_wait();  // the activations may come from the previous kernel of the stream
+    const int ntask = MT * bpr * 8;
+    auto load_x = [&](int task) -> uint4 {
+        // task = (row * bpr + block) * 8 + chunk; rows beyond p.m read as zero
+        return (task < ntask && (MT == 1 || (task >> 3) < p.m * bpr)) ? __ldcg((const uint4*)xbase + task) : make_uint4(0u, 0u, 0u, 0u);
+    };
+    uint4 nxt = load_x(tid);
     if (tid < 4) ((uint32_t*)(smem + ZERO_OFF))[tid] = 0u;
     if (tid >= 4 && tid < 8) ((uint32_t*)(smem + ZERO2_OFF))[tid - 4] = 0u;
     {
-        const float g0 = p.gs0[0], g1 = gu ? p.gs1[0] : g0;
+        const float g1 = gu ? gs1_early : gs0_early;
         for (int b = tid; b < 256; b += NW * 32) {
             const float u = ue4m3_f32((uint32_t)b, true);
-            lut[b] = u * g0;
+            lut[b] = u * gs0_early;
             lut[256 + b] = u * g1;
         }
     }
-    pdl_launch_dependents();
-    pdl_wait();  // the activations may come from the previous kernel of the stream
     bool ok = true;
     // bf16 -> f16 * 2^e per 64-value block, chunk i of block b stored at chunk i ^ (b & 7). Eight lanes per block,
     // one 16-byte chunk each, straight from global memory (k % 256 == 0 makes every warp wholly in or out of range).
-    for (int task = tid; task < bpr * 8; task += NW * 32) {
+    for (int task = tid; task < ntask; task += NW * 32) {
         const int b = task >> 3, i = task & 7;
-        const uint4 raw = __ldcg((const uint4*)xbase + task);
+        const uint4 raw = nxt;
+        nxt = load_x(task + NW * 32);
         const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
         float amax = 0.0f;
 #pragma unroll
@@ -179,7 +191,8 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             const __half2 hh = __floats2half2_rn(__uint_as_float(u[q] << 16) * mul, __uint_as_float(u[q] & 0xffff0000u) * mul);
             h[q] = *(const uint32_t*)&hh;
         }
-        ((uint4*)(xs0 + (size_t)b * XB))[i ^ (b & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
+        const int blk = MT == 1 ? b : b % bpr;
+        ((uint4*)(xs0 + (size_t)b * XB))[i ^ (blk & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
         if (i == 0) xinv0[b] = inv;
     }
     asm volatile("bar.sync 2, %0;" ::"n"(NTHREADS) : "memory");  // staging done, and the ring's barriers are initialised
@@ -192,16 +205,18 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     // byte offset (from smem) of this lane's 16 activations in the first group of a chunk: block 2 warp + (g >> 2),
     // chunk 2 (g & 3) + (t & 1), swizzled by the block index mod 8, which chunk and group number do not change
     const int xb0 = 2 * warp + (g >> 2);
-    const uint32_t xoff_lane = (uint32_t)(HDR + xb0 * XB + (((2 * (g & 3) + (t & 1)) ^ (xb0 & 7)) << 4));
+    const uint32_t xoff_lane = xs_off + (uint32_t)(xb0 * XB + (((2 * (g & 3) + (t & 1)) ^ (xb0 & 7)) << 4));
     const uint32_t aoff = (uint32_t)(g * pstride + 4 * t + warp * 72);
     const int sdelta = -4 * t + (t >> 1) * 36 + 2 * (t & 1);  // from a row's code word to its two scale bytes
-    const float* xinv_lane = xinv0 + 2 * warp + (t >> 1);
+    const float* xinv_lane = xinv0 + 2 * warp + (t >> 1);  // row m: + m * bpr
     const float* lut_b = lut + (gu ? 256 : 0);  // gate/up: rows 8-15 are up rows
 
     int s = 0, rslot = 0;
     uint32_t par = 0, rpar = 0;
     for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g + 8 of the tile, this lane's two columns
+        float acc0[MT], acc1[MT];  // rows g and g + 8 of the tile, this lane's two columns, per activation row
+#pragma unroll
+        for (int m = 0; m < MT; m++) acc0[m] = acc1[m] = 0.0f;
         for (int c = 0; c < nch; c++) {
             const int ng = min(TX, bpr - c * TX) >> 1;  // groups of two blocks in this chunk
             if (!mbar_wait(&full[s], par)) {
@@ -211,32 +226,45 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             }
             const uint8_t* pa0 = stage0 + (size_t)s * stage_bytes + aoff;
             const uint32_t xoff = xoff_lane + (uint32_t)(c * TX * XB);
-            uint32_t bq[4];  // where this lane's B registers of pair q come from: its activations or the zero chunk
+            // where this lane's B registers of pair q come from: its activations (then row m is XS bytes further on) or
+            // the zero chunk (the same for every row)
+            uint32_t bq[4], bstep[4];
 #pragma unroll
-            for (int q = 0; q < 4; q++) bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
+            for (int q = 0; q < 4; q++) {
+                bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
+                bstep[q] = myq == q ? XS : 0u;
+            }
             const float* xip = xinv_lane + c * TX;
 #pragma unroll
             for (int j = 0; j < GPW; j++) {
                 if (warp + NW * j < ng) {
                     const uint8_t* pa = pa0 + j * (NW * 72);
                     const uint8_t* pb = pa + 8 * pstride;
-                    float cc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    float cc[MT][4];
+#pragma unroll
+                    for (int m = 0; m < MT; m++) cc[m][0] = cc[m][1] = cc[m][2] = cc[m][3] = 0.0f;
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        const uint4 xv = *(const uint4*)(smem + bq[q] + j * 2048);
                         const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
                         uint32_t ha[4], hb[4];
                         e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
                         e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
-                        mma16816(cc, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
-                        mma16816(cc, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+#pragma unroll
+                        for (int m = 0; m < MT; m++) {
+                            const uint4 xv = *(const uint4*)(smem + bq[q] + m * bstep[q] + j * 2048);
+                            mma16816(cc[m], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+                            mma16816(cc[m], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+                        }
                     }
                     // columns 2t, 2t + 1 of C = sub-blocks 2t, 2t + 1 of the group: block t >> 1, scale bytes 2 (t & 1), + 1
                     const uint8_t* sc = pa + sdelta;
                     const float s0 = lut[sc[0]], s1 = lut[sc[1]], s2 = lut_b[sc[8 * pstride]], s3 = lut_b[sc[8 * pstride + 1]];
-                    const float xi = xip[16 * j];
-                    acc0 = fmaf(fmaf(cc[1], s1, cc[0] * s0), xi, acc0);
-                    acc1 = fmaf(fmaf(cc[3], s3, cc[2] * s2), xi, acc1);
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        const float xi = xip[m * bpr + 16 * j];
+                        acc0[m] = fmaf(fmaf(cc[m][1], s1, cc[m][0] * s0), xi, acc0[m]);
+                        acc1[m] = fmaf(fmaf(cc[m][3], s3, cc[m][2] * s2), xi, acc1[m]);
+                    }
                 }
             }
             __syncwarp();
@@ -248,15 +276,19 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         }
         if (!ok) break;
         // the four lanes of a quad hold two columns each; then the eight warps' K ranges meet in shared memory:
-        // every warp posts its 16 sums and arrives on the slot's barrier, warp 0 alone waits for all eight
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
-        float* rb = red + rslot * (NW * 16);
-        if (t == 0) {
-            rb[warp * 16 + g] = acc0;
-            rb[warp * 16 + g + 8] = acc1;
+        // every warp posts its sums and arrives on the slot's barrier, warp 0 alone waits for all eight
+        float* rb = red + rslot * (NW * MT * 16);
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            float a = acc0[m], b = acc1[m];
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            b += __shfl_xor_sync(0xffffffffu, b, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            b += __shfl_xor_sync(0xffffffffu, b, 2);
+            if (t == 0) {
+                rb[(warp * MT + m) * 16 + g] = a;
+                rb[(warp * MT + m) * 16 + g + 8] = b;
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&tbar[rslot]);
@@ -265,22 +297,25 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 cn_dev_fail(CN_DEV_WAIT_FULL);
                 ok = false;
             } else if (lane < per_cta) {
-                float v0 = rb[lane], v1 = gu ? rb[lane + 8] : 0.0f;
-                for (int w = 1; w < NW; w++) {  // warps in order: deterministic
-                    v0 += rb[w * 16 + lane];
-                    if (gu) v1 += rb[w * 16 + lane + 8];
-                }
                 const int row = tile * per_cta + lane;
-                if (row < p.rows) {
-                    const float v = gu ? act_gu(v0, v1, p.limit) : v0;
-                    if (p.out_f32)
-                        ((float*)ybase)[row] = v;
-                    else
-                        ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(v);
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    float v0 = rb[m * 16 + lane], v1 = gu ? rb[m * 16 + lane + 8] : 0.0f;
+                    for (int w = 1; w < NW; w++) {  // warps in order: deterministic
+                        v0 += rb[(w * MT + m) * 16 + lane];
+                        if (gu) v1 += rb[(w * MT + m) * 16 + lane + 8];
+                    }
+                    if (row < p.rows && m < p.m) {
+                        const float v = gu ? act_gu(v0, v1, p.limit) : v0;
+                        if (p.out_f32)
+                            ((float*)ybase)[(size_t)m * p.ldy + row] = v;
+                        else
+                            ((__nv_bfloat16*)ybase)[(size_t)m * p.ldy + row] = __float2bfloat16_rn(v);
+                    }
                 }
             }
         }
-        if (++rslot == RED_DEPTH) {
+        if (++rslot == RD) {
             rslot = 0;
             rpar ^= 1u;
         }
@@ -289,14 +324,14 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
 
 int g_m1_stages = 0, g_m1_cps = 0, g_m1_tx = 0;
 
-template <int TX, int CPS>
+template <int TX, int CPS, int MT>
 int launch_m1(const cudaLaunchConfig_t& cfg, const GemvParams& p) {
     static bool attr = false;
     if (!attr) {
-        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemv_m1_kernel<TX, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemv_m1_kernel<TX, CPS, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         attr = true;
     }
-    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS>, p));
+    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS, MT>, p));
     return CN_OK;
 }
 
@@ -309,42 +344,62 @@ void cn_gemv_m1_set(int key, int value) {
 }
 
 int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
-    const int rows = a.rows, k = a.k;
+    const int rows = a.rows, k = a.k, m = a.m;
     const bool routed = a.ids != nullptr;
     const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;
     const int bpr = k / 64;
-    int tx = bpr >= 32 ? 32 : (bpr >= 16 ? 16 : 8);
-    if (g_m1_tx == 32 || g_m1_tx == 16 || g_m1_tx == 8) tx = g_m1_tx;
+    const int mt = m == 1 ? 1 : (m == 2 ? 2 : (m <= 4 ? 4 : 8));
+    // blocks per row and stage: the same rule for every row count, so that row i of an m-row call is summed in the
+    // order of a one-row call
+    int tx = bpr >= 32 ? 32 : 16;
+    if (g_m1_tx == 32 || g_m1_tx == 16) tx = g_m1_tx;
     const int pstride = tx * 36 + 16;
     const size_t stage_bytes = (size_t)ROWS * pstride;
-    const size_t xbytes = (size_t)bpr * XB + (size_t)((bpr + 3) & ~3) * 4;
+    const size_t xbytes = (size_t)mt * bpr * XB + (size_t)((mt * bpr + 3) & ~3) * 4;
     const int per_cta = gu ? ROWS / 2 : ROWS;
     const int ntiles = (rows + per_cta - 1) / per_cta;
     const int nch = (bpr + tx - 1) / tx;
-    // CTAs per SM: as many as leave every CTA a ring of at least three stages
-    int cps = 2;
-    for (int c = 4; c > 2; c--)
-        if ((227 * 1024) / c - 1024 - (long long)HDR - (long long)xbytes >= 3 * (long long)stage_bytes) {
+    // fixed part of a CTA's shared memory for a ring of `st` stages: header, tile-sum slots (a warp runs at most
+    // `st` chunks ahead of warp 0, i.e. st / nch + 1 tiles), activations
+    auto fixed = [&](int st) { return (long long)RED_OFF + (long long)((st + nch) / nch + 1) * NW * mt * 64 + (long long)xbytes; };
+    // CTAs per SM: as many (up to 4 for one row, 2 for more) as leave every CTA a ring of at least three stages
+    int cps = 1;
+    for (int c = mt == 1 ? 4 : 2; c > 1; c--)
+        if ((227 * 1024) / c - 1024 - fixed(3) >= 3 * (long long)stage_bytes) {
             cps = c;
             break;
         }
-    if (g_m1_cps >= 2 && g_m1_cps <= 4) cps = g_m1_cps;
+    if (mt == 1 && cps < 2) cps = 2;
+    if (g_m1_cps >= 1 && g_m1_cps <= 4 && (mt == 1 ? g_m1_cps >= 2 : g_m1_cps <= 2)) cps = g_m1_cps;
     // persistent CTAs, each walking its share of the tiles (the routed form keeps one tile per CTA)
     int grid = ntiles;
     if (!routed && grid > 148 * cps) grid = 148 * cps;
-    const long long budget = (227 * 1024) / cps - 1024 - (long long)HDR - (long long)xbytes;
-    int stages = (int)(budget / (long long)stage_bytes);
-    if (g_m1_stages > 0) stages = g_m1_stages;
-    stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+    int fit = MAX_STAGES;  // ring depth that fits beside the fixed part
+    while (fit > 1 && fixed(fit) + (long long)fit * (long long)stage_bytes > (227 * 1024) / cps - 1024) fit--;
+    int stages = fit;
+    if (g_m1_stages > 0 && g_m1_stages < stages) stages = g_m1_stages;
     const int total_chunks = nch * ((ntiles + grid - 1) / grid);
     if (stages > total_chunks) stages = total_chunks;
     if (stages < 1) stages = 1;
-    const size_t smem = HDR + xbytes + stages * stage_bytes;
-    if (smem > 226 * 1024) CN_FAIL(CN_ERR_LIMIT, "%s: k = %d needs %zu B of shared memory per block", who, k, smem);
+    int red_depth = (stages + nch) / nch + 1;
+    if (red_depth > RED_DEPTH) red_depth = RED_DEPTH;
+    const size_t smem = (size_t)RED_OFF + (size_t)red_depth * NW * mt * 64 + xbytes + stages * stage_bytes;
+    if (smem > 226 * 1024 || fit < 2) {
+        // the staged activations of all m rows do not fit beside a ring: two calls over half the rows each
+        if (m == 1) CN_FAIL(CN_ERR_LIMIT, "%s: k = %d needs %zu B of shared memory per block", who, k, smem);
+        GemvCall lo = a, hi = a;
+        const int m0 = m / 2;
+        lo.m = m0, hi.m = m - m0;
+        hi.x = (const char*)a.x + (size_t)m0 * k * 2;
+        hi.y = (char*)a.y + (size_t)m0 * a.ldy * (a.out_f32 ? 4 : 2);
+        int rc = cn_gemv_m1_launch(lo, stream, who);
+        return rc ? rc : cn_gemv_m1_launch(hi, stream, who);
+    }
     GemvParams p;
     p.w0 = (const uint8_t*)a.w0, p.w1 = (const uint8_t*)a.w1, p.gs0 = a.gs0, p.gs1 = a.gs1 ? a.gs1 : a.gs0, p.x = a.x, p.y = a.y;
-    p.rows = rows, p.k = k, p.m = 1, p.ldy = a.ldy, p.limit = a.limit, p.tx = tx, p.stages = stages, p.out_f32 = a.out_f32;
+    p.rows = rows, p.k = k, p.m = m, p.ldy = a.ldy, p.limit = a.limit, p.tx = tx, p.stages = stages, p.out_f32 = a.out_f32;
     p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
+    p.red_depth = red_depth;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, (unsigned)(routed ? a.combos : 1));
     cfg.blockDim = dim3(NTHREADS);
@@ -355,10 +410,12 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-#define CN_M1_CASE(TXV, CPSV) \
-    if (tx == TXV && cps == CPSV) return launch_m1<TXV, CPSV>(cfg, p);
-    CN_M1_CASE(32, 2) CN_M1_CASE(32, 3) CN_M1_CASE(32, 4) CN_M1_CASE(16, 2) CN_M1_CASE(16, 3) CN_M1_CASE(16, 4)
-    CN_M1_CASE(8, 2) CN_M1_CASE(8, 3) CN_M1_CASE(8, 4)
+#define CN_M1_CASE(TXV, CPSV, MTV) \
+    if (tx == TXV && cps == CPSV && mt == MTV) return launch_m1<TXV, CPSV, MTV>(cfg, p);
+    CN_M1_CASE(32, 2, 1) CN_M1_CASE(32, 3, 1) CN_M1_CASE(32, 4, 1) CN_M1_CASE(16, 2, 1) CN_M1_CASE(16, 3, 1) CN_M1_CASE(16, 4, 1)
+    CN_M1_CASE(32, 1, 2) CN_M1_CASE(32, 2, 2) CN_M1_CASE(16, 1, 2) CN_M1_CASE(16, 2, 2)
+    CN_M1_CASE(32, 1, 4) CN_M1_CASE(32, 2, 4) CN_M1_CASE(16, 1, 4) CN_M1_CASE(16, 2, 4)
+    CN_M1_CASE(32, 1, 8) CN_M1_CASE(32, 2, 8) CN_M1_CASE(16, 1, 8) CN_M1_CASE(16, 2, 8)
 #undef CN_M1_CASE
-    CN_FAIL(CN_ERR_SHAPE, "%s: no kernel for %d blocks per stage, %d CTAs per SM", who, tx, cps);
+    CN_FAIL(CN_ERR_SHAPE, "%s: no kernel for %d blocks per stage, %d CTAs per SM, %d rows", who, tx, cps, mt);
 }
