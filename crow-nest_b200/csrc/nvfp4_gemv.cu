@@ -506,13 +506,10 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     if (a.dtype != CN_F32 && a.dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "%s: dtype %d is neither CN_F32 nor CN_BF16", who, a.dtype);
     if (((uintptr_t)a.w0 & 15) || ((uintptr_t)a.w1 & 15) || ((uintptr_t)a.x & 15))
         CN_FAIL(CN_ERR_SHAPE, "%s: weight and activation pointers must be 16-byte aligned", who);
-    // bf16 activations: the tensor-core inner loop (engine 0 = default); engine 1 forces the CUDA-core kernel
     const bool routed = a.ids != nullptr;
     if (routed && (m != 1 || a.combos < 1 || a.x_div < 1)) CN_FAIL(CN_ERR_SHAPE, "%s: the routed form takes one row per combo", who);
-    if (a.dtype == CN_BF16 && g_tune_engine != 1 && g_tune_mode != 1) {
-        if (g_tune_engine != 2) return cn_gemv_m1_launch(a, stream, who);
-        if (a.k % 512 == 0) return cn_gemv_mma_launch(a, stream, who);
-    }
+    // bf16 activations: the tensor-core kernel (tuning key 5 = 1 keeps them on this file's CUDA-core kernel)
+    if (a.dtype == CN_BF16 && g_tune_engine != 1 && g_tune_mode != 1) return cn_gemv_m1_launch(a, stream, who);
     const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;
     const int bpr = k / 64;
     const int tx = bpr % 16 == 0 ? 16 : (bpr % 8 == 0 ? 8 : 4);
@@ -600,6 +597,5 @@ extern "C" void cn_set_tuning(int key, int value) {
     if (key == CN_TUNE_GEMV_STAGES) g_tune_stages = value;
     if (key == 4) g_tune_pdl = value;
     if (key == 5) g_tune_engine = value;
-    if (key == 6) cn_gemv_mma_set_stages(value);
     if (key >= 7 && key <= 9) cn_gemv_m1_set(key - 7, value);
 }

@@ -62,10 +62,6 @@ __device__ __forceinline__ float act_gu(float g, float u, float limit) {
 }
 
 
-// the tensor-core (mma.sync) form of the same GEMV for bf16 activations (nvfp4_gemv_mma.cu)
-int cn_gemv_mma_launch(const GemvCall& a, cudaStream_t stream, const char* who);
-void cn_gemv_mma_set_stages(int s);
-
-// one bf16 activation row: persistent CTAs, tensor-core inner loop in word form (nvfp4_gemv_m1.cu)
+// bf16 activation rows (1..8): persistent CTAs, tensor-core inner loop in word form (nvfp4_gemv_m1.cu)
 int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who);
 void cn_gemv_m1_set(int key, int value);  // 0 ring depth, 1 CTAs per SM, 2 blocks per row and stage (0 = automatic)

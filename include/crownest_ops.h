@@ -212,6 +212,8 @@ void cn_set_tuning(int key, int value);
 #define CN_TUNE_GEMV_MODE 1 /* 0 default, 1 force f32 FMA path, 2 force f16 mixed-FMA path */
 #define CN_TUNE_GEMV_RT 2   /* rows per thread: 0 heuristic, else 1, 2 or 4 */
 #define CN_TUNE_GEMV_STAGES 3
+/* 4: programmatic dependent launch on (1, default) / off (0); 5: 1 = send bf16 calls to the CUDA-core kernel too;
+ * 7, 8, 9: tensor-core GEMV ring depth, CTAs per SM, blocks per row and stage (0 = chosen by the library) */
 
 #ifdef __cplusplus
 }
