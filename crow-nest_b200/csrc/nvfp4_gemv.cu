@@ -597,5 +597,5 @@ extern "C" void cn_set_tuning(int key, int value) {
     if (key == CN_TUNE_GEMV_STAGES) g_tune_stages = value;
     if (key == 4) g_tune_pdl = value;
     if (key == 5) g_tune_engine = value;
-    if (key >= 7 && key <= 9) cn_gemv_m1_set(key - 7, value);
+    if (key >= 7 && key <= 10) cn_gemv_m1_set(key - 7, value);
 }

@@ -51,6 +51,7 @@ struct GemvParams {
     int fused_up_rows;               // > 0: up = gate + fused_up_rows rows of the same slab
     int x_div;
     int red_depth;  // multi-row tensor-core kernel: tile-sum slots in flight
+    int ksplit;     // 2: launched as two-CTA clusters, each CTA of a pair over half of K (one activation row only)
 };
 
 __device__ __forceinline__ float act_gu(float g, float u, float limit) {

@@ -43,22 +43,61 @@ __device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, u
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// ---- two-CTA cluster helpers (K range of a tile shared between the CTAs of a pair)
+constexpr int XCH_OFF = 256, XCH_SLOTS = 8, XBAR_OFF = XCH_OFF + XCH_SLOTS * 64;  // f32 [8][16] sums from the peer + a barrier per slot
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_addr(const void* local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_peer_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void arrive_peer(uint32_t bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+// bounded wait with cluster-scope acquire: the peer CTA's stores before its arrive are visible afterwards
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
+}
+
 // TX: 36-byte blocks per row and stage (32 or 16); the last chunk of a row may be shorter
 // CPS: CTAs per SM the register allocation must allow; MT: activation rows (1, 2, 4 or 8; p.m of them live)
-template <int TX, int CPS, int MT>
+// KS: 1, or 2 = launched as two-CTA clusters, the CTAs of a pair sharing every tile's K range (MT = 1 only)
+template <int TX, int CPS, int MT, int KS = 1>
 __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const float gs0_early = __ldg(p.gs0), gs1_early = __ldg(p.gs1);  // tensor scales: asked for first, used late
     constexpr int pstride = TX * 36 + 16;  // padded: the eight rows of a quad column hit distinct banks
     constexpr int stage_bytes = ROWS * pstride;
     constexpr int GPW = TX / 2 / NW > 0 ? TX / 2 / NW : 1;  // groups per warp and full chunk
-    const int bpr = p.k >> 6;
-    const size_t row_bytes = (size_t)bpr * 36;
+    // KS = 2 (one activation row only): the CTAs of a cluster pair walk the same tiles, each over half of K
+    static_assert(KS == 1 || MT == 1, "the K range is shared between CTAs for one activation row only");
+    const int crank = KS == 2 ? (int)(blockIdx.x & 1) : 0;
+    const int cid = KS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, ncl = KS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int bpr_all = p.k >> 6;
+    const int bpr = bpr_all / KS, b0 = crank * bpr;  // this CTA's blocks of every row: [b0, b0 + bpr)
+    const size_t row_bytes = (size_t)bpr_all * 36;
     const int nch = (bpr + TX - 1) / TX;
     const int S = p.stages;
-    const uint8_t* w0 = p.w0;
-    const uint8_t* w1 = p.w1;
-    const char* xbase = (const char*)p.x;
+    const uint8_t* w0 = p.w0 + (size_t)b0 * 36;
+    const uint8_t* w1 = p.w1 ? p.w1 + (size_t)b0 * 36 : nullptr;
+    const char* xbase = (const char*)p.x + (size_t)b0 * 128;
     char* ybase = (char*)p.y;
     if (p.ids) {
         const int c = p.order ? p.order[blockIdx.y] : (int)blockIdx.y;
@@ -97,20 +136,23 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 mbar_init(&empty[s], NW);
             }
             for (int i = 0; i < RD; i++) mbar_init(&tbar[i], NW);
+            if (KS == 2)
+                for (int i = 0; i < XCH_SLOTS; i++) mbar_init((uint64_t*)(smem + XBAR_OFF) + i, 1);
             mbar_fence_init();
         }
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
         pdl_launch_dependents();
     }
+    if (KS == 2) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
 
     if (warp == NW) {
         // ------------------------------------------------------------ weight producer warp
         const uint64_t pol = l2_policy_evict_first();
         int s = 0;
         uint32_t par = 0;  // parity of the current use of stage s
-        bool first_round = true;
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        bool first_round = true, pfail = false;
+        for (int tile = cid; tile < ntiles && !pfail; tile += ncl) {
             const int row0 = tile * per_cta;
             const int row = gu ? row0 + (lane & 7) : row0 + lane;
             const uint8_t* base = (gu && ((lane >> 3) & 1)) ? w1 : w0;
@@ -121,7 +163,8 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 const uint32_t piece = (uint32_t)nblk * 36u;
                 if (!first_round && !mbar_wait(&empty[s], par ^ 1u)) {
                     cn_dev_fail(CN_DEV_WAIT_EMPTY);
-                    return;
+                    pfail = true;
+                    break;
                 }
                 uint8_t* st = stage0 + (size_t)s * stage_bytes;
                 if (lane == 0) {
@@ -137,6 +180,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 }
             }
         }
+        if (KS == 2) cluster_sync_all();  // nobody leaves while the peer may still send or receive
         return;
     }
 
@@ -213,7 +257,8 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
 
     int s = 0, rslot = 0;
     uint32_t par = 0, rpar = 0;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+    int titer = 0;
+    for (int tile = cid; tile < ntiles && ok; tile += ncl, titer++) {
         float acc0[MT], acc1[MT];  // rows g and g + 8 of the tile, this lane's two columns, per activation row
 #pragma unroll
         for (int m = 0; m < MT; m++) acc0[m] = acc1[m] = 0.0f;
@@ -296,6 +341,37 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             if (!mbar_wait(&tbar[rslot], rpar)) {
                 cn_dev_fail(CN_DEV_WAIT_FULL);
                 ok = false;
+            } else if (MT == 1 && KS == 2) {
+                // lane l < 16: row slot l of the tile over this CTA's half of K, the eight warps in order
+                float v = 0.0f;
+                if (lane < 16) {
+                    v = rb[lane];
+                    for (int w = 1; w < NW; w++) v += rb[w * 16 + lane];
+                }
+                float* xch = (float*)(smem + XCH_OFF) + titer * 16;
+                uint64_t* xb = (uint64_t*)(smem + XBAR_OFF) + titer;
+                if (crank == 1) {
+                    // hand the sums to the pair's first CTA: into its slot, then one arrival on its barrier
+                    if (lane < 16) st_peer_f32(peer_addr(xch + lane, 0), v);
+                    __syncwarp();
+                    if (lane == 0) arrive_peer(peer_addr(xb, 0));
+                } else {
+                    if (!mbar_wait_cluster(xb, 0)) {
+                        cn_dev_fail(CN_DEV_WAIT_FULL);
+                        ok = false;
+                    } else {
+                        if (lane < 16) v += xch[lane];  // first half of K + second half: a fixed order
+                        const float up = __shfl_down_sync(0xffffffffu, v, 8);
+                        const int row = tile * per_cta + lane;
+                        if (lane < per_cta && row < p.rows) {
+                            const float r = gu ? act_gu(v, up, p.limit) : v;
+                            if (p.out_f32)
+                                ((float*)ybase)[row] = r;
+                            else
+                                ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(r);
+                        }
+                    }
+                }
             } else if (lane < per_cta) {
                 const int row = tile * per_cta + lane;
 #pragma unroll
@@ -320,18 +396,19 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             rpar ^= 1u;
         }
     }
+    if (KS == 2) cluster_sync_all();  // nobody leaves while the peer may still send or receive
 }
 
-int g_m1_stages = 0, g_m1_cps = 0, g_m1_tx = 0;
+int g_m1_stages = 0, g_m1_cps = 0, g_m1_tx = 0, g_m1_ksplit = 0;
 
-template <int TX, int CPS, int MT>
+template <int TX, int CPS, int MT, int KS = 1>
 int launch_m1(const cudaLaunchConfig_t& cfg, const GemvParams& p) {
     static bool attr = false;
     if (!attr) {
-        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemv_m1_kernel<TX, CPS, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemv_m1_kernel<TX, CPS, MT, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         attr = true;
     }
-    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS, MT>, p));
+    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS, MT, KS>, p));
     return CN_OK;
 }
 
@@ -341,6 +418,7 @@ void cn_gemv_m1_set(int key, int value) {
     if (key == 0) g_m1_stages = value;
     if (key == 1) g_m1_cps = value;
     if (key == 2) g_m1_tx = value;
+    if (key == 3) g_m1_ksplit = value;  // 0 automatic, 1 never, 2 whenever the shape allows
 }
 
 int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
@@ -358,7 +436,7 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     const size_t xbytes = (size_t)mt * bpr * XB + (size_t)((mt * bpr + 3) & ~3) * 4;
     const int per_cta = gu ? ROWS / 2 : ROWS;
     const int ntiles = (rows + per_cta - 1) / per_cta;
-    const int nch = (bpr + tx - 1) / tx;
+    int nch = (bpr + tx - 1) / tx;
     // fixed part of a CTA's shared memory for a ring of `st` stages: header, tile-sum slots (a warp runs at most
     // `st` chunks ahead of warp 0, i.e. st / nch + 1 tiles), activations
     auto fixed = [&](int st) { return (long long)RED_OFF + (long long)((st + nch) / nch + 1) * NW * mt * 64 + (long long)xbytes; };
@@ -374,16 +452,36 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     // persistent CTAs, each walking its share of the tiles (the routed form keeps one tile per CTA)
     int grid = ntiles;
     if (!routed && grid > 148 * cps) grid = 148 * cps;
+    // When the tiles do not fill the last wave, pairs of CTAs (a cluster of two) share every tile, each over half of
+    // K, and the pair's second CTA hands its 16 sums to the first through distributed shared memory: the wave
+    // quantum drops from a tile to half a tile. Taken when that shortens the longest CTA by a tenth or more.
+    int ksplit = 1;
+    if (!routed && mt == 1 && tx == 32 && cps <= 3 && bpr % 8 == 0 && g_m1_ksplit != 1) {
+        const int slots = 148 * cps, pairs = slots / 2;
+        const int waves1 = (ntiles + slots - 1) / slots, waves2 = (ntiles + pairs - 1) / pairs;  // tiles / CTA, half tiles / CTA
+        // worth it only when a CTA's share is long enough to hide the pair's hand-over (measured: 235 KB yes, 69 KB no)
+        const long long share = (long long)waves2 * ROWS * bpr * 36 / 2;
+        if (waves2 <= XCH_SLOTS && (g_m1_ksplit == 2 || (10 * waves2 <= 18 * waves1 && share >= 160 * 1024))) {
+            ksplit = 2;
+            grid = 2 * (ntiles < pairs ? ntiles : pairs);
+        }
+    }
+    size_t xbytes_l = xbytes;
+    if (ksplit == 2) {
+        nch = (bpr / 2 + tx - 1) / tx;
+        xbytes_l = (size_t)(bpr / 2) * XB + (size_t)((bpr / 2 + 3) & ~3) * 4;
+    }
+    auto fixed2 = [&](int st) { return (long long)RED_OFF + (long long)((st + nch) / nch + 1) * NW * mt * 64 + (long long)xbytes_l; };
     int fit = MAX_STAGES;  // ring depth that fits beside the fixed part
-    while (fit > 1 && fixed(fit) + (long long)fit * (long long)stage_bytes > (227 * 1024) / cps - 1024) fit--;
+    while (fit > 1 && fixed2(fit) + (long long)fit * (long long)stage_bytes > (227 * 1024) / cps - 1024) fit--;
     int stages = fit;
     if (g_m1_stages > 0 && g_m1_stages < stages) stages = g_m1_stages;
-    const int total_chunks = nch * ((ntiles + grid - 1) / grid);
+    const int total_chunks = nch * ((ntiles + grid / ksplit - 1) / (grid / ksplit));
     if (stages > total_chunks) stages = total_chunks;
     if (stages < 1) stages = 1;
     int red_depth = (stages + nch) / nch + 1;
     if (red_depth > RED_DEPTH) red_depth = RED_DEPTH;
-    const size_t smem = (size_t)RED_OFF + (size_t)red_depth * NW * mt * 64 + xbytes + stages * stage_bytes;
+    const size_t smem = (size_t)RED_OFF + (size_t)red_depth * NW * mt * 64 + xbytes_l + stages * stage_bytes;
     if (smem > 226 * 1024 || fit < 2) {
         // the staged activations of all m rows do not fit beside a ring: two calls over half the rows each
         if (m == 1) CN_FAIL(CN_ERR_LIMIT, "%s: k = %d needs %zu B of shared memory per block", who, k, smem);
@@ -400,16 +498,26 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.rows = rows, p.k = k, p.m = m, p.ldy = a.ldy, p.limit = a.limit, p.tx = tx, p.stages = stages, p.out_f32 = a.out_f32;
     p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
     p.red_depth = red_depth;
+    p.ksplit = ksplit;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, (unsigned)(routed ? a.combos : 1));
     cfg.blockDim = dim3(NTHREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
+    if (ksplit == 2) {
+        at[1].id = cudaLaunchAttributeClusterDimension;
+        at[1].val.clusterDim.x = 2, at[1].val.clusterDim.y = 1, at[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
+    if (ksplit == 2) {
+        if (cps == 2) return launch_m1<32, 2, 1, 2>(cfg, p);
+        return launch_m1<32, 3, 1, 2>(cfg, p);
+    }
 #define CN_M1_CASE(TXV, CPSV, MTV) \
     if (tx == TXV && cps == CPSV && mt == MTV) return launch_m1<TXV, CPSV, MTV>(cfg, p);
     CN_M1_CASE(32, 2, 1) CN_M1_CASE(32, 3, 1) CN_M1_CASE(32, 4, 1) CN_M1_CASE(16, 2, 1) CN_M1_CASE(16, 3, 1) CN_M1_CASE(16, 4, 1)
