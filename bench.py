@@ -341,6 +341,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--impl", default="crownest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="tensor parallel: slices pushed over peer memory, or NCCL all-gather")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
     ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mul1", "gemm"], help="dense = the headline (config 1); moe / mul1 = configs 2 / 3")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
@@ -365,7 +366,8 @@ def main():
     _lib.lib()  # fail loudly when the CUDA library is missing: there is no fallback
     trace("process group up")
 
-    stack = dense.DenseStack(layers=args.layers, device=f"cuda:{local}", seed=0, rank=rank, world=world, group=group, max_m=args.m)
+    stack = dense.DenseStack(layers=args.layers, device=f"cuda:{local}", seed=0, rank=rank, world=world, group=group, max_m=args.m,
+                             exchange=args.exchange)
     m = args.m
     gen = torch.Generator(device="cpu").manual_seed(1)
     x_host = torch.randn((m, stack.hidden), generator=gen).to(torch.bfloat16).pin_memory()
@@ -424,7 +426,7 @@ def main():
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic",
                 "config": {"workload": f"nvfp4 dense decode stack 27B-shaped (hidden 5120, qkv 7168, inter 17408, {stack.layers} layers), M={m}",
-                           "activations": "bf16 in/out, f32 accumulate", "parallelism": f"tp{world} row split + all-gather" if world > 1 else "none",
+                           "activations": "bf16 in/out, f32 accumulate", "parallelism": (f"tp{world} row split + " + ("peer-memory exchange" if stack.peer is not None else "NCCL all-gather")) if world > 1 else "none",
                            "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (bytes_step / 1e9),
                            "launch": "CUDA graph replay" if use_graph else "eager launches", "tokens_per_s": m / (ms_step * 1e-3)},
                 "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "traffic": TRAFFIC_RATIO * bytes_step / world / stack.launches_per_step if m == 1 else None,

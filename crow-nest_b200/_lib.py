@@ -48,6 +48,10 @@ _SIGS = {
     "cn_moe_nvfp4_run": [_vp] * 16 + [_i, _f, _i, _vp],
     "cn_nvfp4_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
     "cn_nvfp4_gemm_workspace_bytes": [_i, _i],
+    "cn_peer_export": [_vp, _vp, C.POINTER(C.c_size_t)],
+    "cn_peer_open": [_vp, C.c_size_t, C.POINTER(C.c_void_p)],
+    "cn_peer_close": [_vp, C.c_size_t],
+    "cn_tp_allgather": [C.POINTER(C.c_void_p), _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, _vp],
     "cn_mul1_plan_create": [C.POINTER(C.c_void_p), _i, _i, _i, _i, _i, _i],
     "cn_mul1_plan_destroy": [_vp],
     "cn_mul1_gemv": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],

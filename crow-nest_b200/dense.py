@@ -50,8 +50,58 @@ def gather_rows(part, full, m, world, group=None):
         full[:m].copy_(tmp.permute(1, 0, 2).reshape(m, -1))
 
 
+class PeerExchange:
+    """One buffer per rank, visible to every peer over NVLink (CUDA IPC), holding the replicated activation vectors
+    of the tensor-parallel stack, plus the arrival counters of each exchange point (`cn_tp_allgather`)."""
+
+    def __init__(self, vectors, rank, world, device, group=None):
+        """vectors: {name: elements}, bf16, one row; every vector's length divides by `world`."""
+        import ctypes as C
+        import torch.distributed as dist
+        from ._lib import check, lib
+        self.rank, self.world = rank, world
+        self.off, at = {}, 0
+        for name, n in vectors.items():
+            self.off[name] = (at, n * 2 // world)
+            at += (n * 2 + 255) // 256 * 256
+        self.flag_off = {}
+        for name in vectors:
+            self.flag_off[name] = at
+            at += 64
+        self.buf = torch.zeros(at, dtype=torch.uint8, device=device)
+        handle, offset = C.create_string_buffer(64), C.c_size_t(0)
+        check(lib().cn_peer_export(self.buf.data_ptr(), handle, C.byref(offset)))
+        mine = (bytes(handle.raw), int(offset.value))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine, group=group)
+        self.bases = (C.c_void_p * world)()
+        self.opened = []
+        for r, (h, o) in enumerate(everyone):
+            if r == rank:
+                self.bases[r] = self.buf.data_ptr()
+            else:
+                p = C.c_void_p()
+                check(lib().cn_peer_open(h, o, C.byref(p)))
+                self.bases[r] = p.value
+                self.opened.append((p.value, o))
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # every buffer is zeroed and open before the first exchange
+
+    def vector(self, name, n):
+        """The local copy of a vector as a [1][n] bf16 tensor."""
+        at, _ = self.off[name]
+        return self.buf[at:at + 2 * n].view(torch.bfloat16).view(1, n)
+
+    def exchange(self, name):
+        from ._lib import check, lib
+        at, slice_bytes = self.off[name]
+        check(lib().cn_tp_allgather(self.bases, self.rank, self.world, at, slice_bytes, self.flag_off[name],
+                                    torch.cuda.current_stream().cuda_stream))
+
+
 class DenseStack:
-    def __init__(self, cfg=None, layers=None, device="cuda", seed=0, rank=0, world=1, group=None, max_m=1, dtype=torch.bfloat16):
+    def __init__(self, cfg=None, layers=None, device="cuda", seed=0, rank=0, world=1, group=None, max_m=1, dtype=torch.bfloat16,
+                 exchange="nccl"):
         cfg = dict(cfg or synth.DENSE_27B)
         self.hidden, self.qkv, self.inter = cfg["hidden"], cfg["qkv"], cfg["inter"]
         self.layers = layers if layers is not None else cfg["layers"]
@@ -77,10 +127,16 @@ class DenseStack:
         self.o = torch.empty((m, self.hidden), dtype=dtype, device=device)
         self.h = torch.empty((m, self.inter), dtype=dtype, device=device)
         self.y = torch.empty((m, self.hidden), dtype=dtype, device=device)
+        self.peer = None
         if world > 1:
             # per-rank slices land here, then one all-gather per projection
             self.part = {n: torch.empty((m, r // world), dtype=dtype, device=device) for n, r in
                          (("q", self.qkv), ("o", self.hidden), ("h", self.inter), ("y", self.hidden))}
+            if exchange == "peer" and max_m == 1 and dtype == torch.bfloat16:
+                # one activation row: the slices are written straight into a peer-visible buffer and pushed to the peers
+                sizes = {"q": self.qkv, "o": self.hidden, "h": self.inter, "y": self.hidden}
+                self.peer = PeerExchange(sizes, rank, world, device, group)
+                self.q, self.o, self.h, self.y = (self.peer.vector(n, r) for n, r in sizes.items())
         self.launches_per_step = 4 * self.layers
         self.graph = None
 
@@ -99,12 +155,18 @@ class DenseStack:
         gather_rows(self.part[name][:m], full, m, self.world, self.group)
 
     def _proj(self, w, x, name, full, m, gu=None):
-        out = full[:m] if self.world == 1 else self.part[name][:m]
+        if self.peer is not None:
+            lo, hi = tp_rows(full.shape[1], self.rank, self.world)
+            out = full[:, lo:hi]  # this rank's slice of the replicated vector, in place
+        else:
+            out = full[:m] if self.world == 1 else self.part[name][:m]
         if gu is None:
             ops.launch_gemv(w, x, out)
         else:
             ops.launch_gemv_gu(w, gu, x, out)
-        if self.world > 1:
+        if self.peer is not None:
+            self.peer.exchange(name)
+        elif self.world > 1:
             self._gather(name, full, m)
 
     def run_layers(self, m=1):

@@ -207,6 +207,20 @@ int cn_mul1_reconstruct(const void* trellis, void* w_out, int k, int n, int bits
 int cn_fp8_gemv(const void* w, const float* scale, const void* x, void* y, int rows, int cols, int m, int ldy, int dtype,
                 cn_stream_t stream);
 
+/* ---------------------------------------------------------------- tensor-parallel exchange over peer memory
+ * No counterpart in the reference (it is single-GPU). Every rank holds one buffer of the same layout; a rank
+ * exports its buffer (cn_peer_export: a 64-byte CUDA IPC handle of the allocation and the buffer's offset in it),
+ * the others open it (cn_peer_open) and pass all base pointers, their own included, to cn_tp_allgather:
+ * the rank's slice [data_off + rank * slice_bytes, + slice_bytes) is stored into every peer's buffer at the same
+ * place, then the ranks meet on the arrival counters at flag_off (36 bytes, zero before the first use, one flag
+ * block per exchange point). One launch, graph-capturable; the wait is bounded. Offsets and sizes in multiples of
+ * 16 bytes; world <= 8. */
+int cn_peer_export(const void* ptr, void* handle64, size_t* offset);
+int cn_peer_open(const void* handle64, size_t offset, void** ptr);
+int cn_peer_close(void* ptr, size_t offset);
+int cn_tp_allgather(const void* const* peer_bases, int rank, int world, size_t data_off, size_t slice_bytes, size_t flag_off,
+                    cn_stream_t stream);
+
 /* diagnostics: select an inner-loop variant of the NVFP4 GEMV for A/B timing (0 = default) */
 void cn_set_tuning(int key, int value);
 #define CN_TUNE_GEMV_MODE 1 /* 0 default, 1 force f32 FMA path, 2 force f16 mixed-FMA path */
