@@ -137,16 +137,19 @@ __device__ __forceinline__ void lane_states(const uint32_t* tile, int n32, const
 
 // y' partials of one k-split. grid (n/128, S, slots), block 288 = 8 decode warps + 1 copy warp.
 // part[slot][sp][t][n]; xh16 [slot][T][k] f16, xinv [slot][T][k/128].
-template <bool K3>
-__global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long* __restrict__ ptrs, const uint16_t* __restrict__ xh,
+// MT: activation rows the register allocation is built for (1, 2, 4 or 8; T <= MT of them live)
+template <bool K3, int MT>
+__global__ void __launch_bounds__(288, MT == 1 ? 4 : (MT == 2 ? 3 : (MT == 4 ? 2 : 1))) mul1_gemv_kernel(const unsigned long long* __restrict__ ptrs, const uint16_t* __restrict__ xh,
                                                         const float* __restrict__ xinv, float* __restrict__ part, Mul1Spec sp_, int S, int T,
-                                                        size_t plane) {
+                                                        size_t plane, int SPC) {
+    // SPC consecutive k-splits per CTA (blockIdx.y walks groups of SPC): the splits keep their own partial sums, so
+    // the arithmetic does not depend on SPC; a CTA that takes several streams them through one ring without a drain
     extern __shared__ __align__(128) uint8_t smem[];
-    const int slot = blockIdx.z, sp = blockIdx.y;
+    const int slot = blockIdx.z, sp0 = blockIdx.y * SPC;
     const unsigned long long rec = ptrs[slot];
     if (rec == 0ull) return;  // uniform, before any barrier
     const int k = sp_.k, n = sp_.n, n32 = sp_.n32;
-    const int tiles_n = n >> 4, tps = (k >> 4) / S, kb0 = sp * tps, rows = tps * 16;
+    const int tiles_n = n >> 4, tps = (k >> 4) / S, kb0 = sp0 * tps, rows = SPC * tps * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb0 = blockIdx.x * 8;
     const int run_bytes = 32 * n32;  // 8 tiles of one tile row
@@ -163,7 +166,8 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
         mbar_fence_init();
     }
     __syncthreads();
-    const int nst = (tps + UROWS - 1) / UROWS;
+    const int nst1 = (tps + UROWS - 1) / UROWS;  // stages of one split
+    const int nst = SPC * nst1;
     if (warp == 8) {
         const uint8_t* base = (const uint8_t*)(rec + (unsigned long long)sp_.tr_off);
         if (((uintptr_t)base & 15) != 0) {
@@ -176,14 +180,15 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
                 cn_dev_fail(CN_DEV_WAIT_EMPTY);
                 return;
             }
-            const int live = min(UROWS, tps - c * UROWS);
+            const int spi = c / nst1, cs = c - spi * nst1;  // split within the CTA, stage within the split
+            const int live = min(UROWS, tps - cs * UROWS);
             if (lane == 0) {
                 mbar_expect_tx(&full[s], (uint32_t)(live * run_bytes));
                 mbar_arrive(&full[s]);
             }
             __syncwarp();
             if (lane < live) {
-                const size_t off = ((size_t)(kb0 + c * UROWS + lane) * tiles_n + nb0) * n32 * 4;
+                const size_t off = ((size_t)(kb0 + spi * tps + cs * UROWS + lane) * tiles_n + nb0) * n32 * 4;
                 bulk_g2s((uint8_t*)ring + ((size_t)s * UROWS + lane) * run_bytes, base + off, (uint32_t)run_bytes, &full[s]);
             }
         }
@@ -213,29 +218,30 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
     }
     const int wi0 = lo[0] >> 5, sh0 = lo[0] & 31;
     const int q2 = 2 * (lane & 3);
-    float tot0[MUL1_MAXT], tot1[MUL1_MAXT];
+    float tot0[MT], tot1[MT];
 #pragma unroll
-    for (int t = 0; t < MUL1_MAXT; t++) tot0[t] = tot1[t] = 0.0f;
-    float a0e[MUL1_MAXT], a0o[MUL1_MAXT], a1e[MUL1_MAXT], a1o[MUL1_MAXT];  // hi plane, even / odd chains
-    float l0e[MUL1_MAXT], l0o[MUL1_MAXT], l1e[MUL1_MAXT], l1o[MUL1_MAXT];  // lo plane
+    for (int t = 0; t < MT; t++) tot0[t] = tot1[t] = 0.0f;
+    float a0e[MT], a0o[MT], a1e[MT], a1o[MT];  // hi plane, even / odd chains
+    float l0e[MT], l0o[MT], l1e[MT], l1o[MT];  // lo plane
 #pragma unroll
-    for (int t = 0; t < MUL1_MAXT; t++) a0e[t] = a0o[t] = a1e[t] = a1o[t] = l0e[t] = l0o[t] = l1e[t] = l1o[t] = 0.0f;
+    for (int t = 0; t < MT; t++) a0e[t] = a0o[t] = a1e[t] = a1o[t] = l0e[t] = l0o[t] = l1e[t] = l1o[t] = 0.0f;
     for (int c = 0; c < nst; c++) {
         const int s = c % RING;
         if (!mbar_wait(&full[s], (c / RING) & 1)) {
             cn_dev_fail(CN_DEV_WAIT_FULL);
             return;
         }
-        const int live = min(UROWS, tps - c * UROWS);
+        const int spi = c / nst1, cs = c - spi * nst1;
+        const int live = min(UROWS, tps - cs * UROWS);
         for (int u = 0; u < live; u++) {
-            const int kt = c * UROWS + u;  // tile row within the split
+            const int kt = spi * tps + cs * UROWS + u;  // tile row within the CTA's splits
             const uint32_t* tile = ring + ((size_t)(s * UROWS + u) * 8 + warp) * n32;
             uint32_t st[8];
             lane_states<K3>(tile, n32, lo, wi0, sh0, st);
             const uint32_t w01 = mul1_pair(st[0], st[1]), w23 = mul1_pair(st[2], st[3]);
             const uint32_t w45 = mul1_pair(st[4], st[5]), w67 = mul1_pair(st[6], st[7]);
 #pragma unroll
-            for (int t = 0; t < MUL1_MAXT; t++) {
+            for (int t = 0; t < MT; t++) {
                 if (t < T) {
                     const uint32_t* xr = (const uint32_t*)(xs + (size_t)t * rows + kt * 16 + q2);
                     const uint32_t x01 = xr[0], x89 = xr[4];
@@ -254,7 +260,7 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
             if ((kt & 7) == 7) {
                 // end of a 128-row block: undo its activation scale
 #pragma unroll
-                for (int t = 0; t < MUL1_MAXT; t++) {
+                for (int t = 0; t < MT; t++) {
                     if (t < T) {
                         const float inv = xi[t * nblk + (kt >> 3)];
                         tot0[t] = fmaf(fmaf(l0e[t] + l0o[t], 4.8828125e-4f, a0e[t] + a0o[t]), inv, tot0[t]);
@@ -266,20 +272,23 @@ __global__ void __launch_bounds__(288) mul1_gemv_kernel(const unsigned long long
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-    }
-    // the four lanes of a column (g % 4): two xor-shuffle adds, then one store per column
+        if (cs == nst1 - 1) {
+            // end of a split: the four lanes of a column (g % 4) meet with two xor-shuffle adds, one store per column
 #pragma unroll
-    for (int t = 0; t < MUL1_MAXT; t++) {
-        if (t < T) {
-            float a = tot0[t], b = tot1[t];
-            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
-            b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 1));
-            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
-            b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 2));
-            if ((lane & 3) == 0) {
-                float* pp = part + (((size_t)slot * S + sp) * T + t) * n + (size_t)(nb0 + warp) * 16 + (lane >> 2);
-                pp[0] = a;
-                pp[8] = b;
+            for (int t = 0; t < MT; t++) {
+                if (t < T) {
+                    float a = tot0[t], b = tot1[t];
+                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+                    b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 1));
+                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+                    b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 2));
+                    if ((lane & 3) == 0) {
+                        float* pp = part + (((size_t)slot * S + sp0 + spi) * T + t) * n + (size_t)(nb0 + warp) * 16 + (lane >> 2);
+                        pp[0] = a;
+                        pp[8] = b;
+                    }
+                    tot0[t] = tot1[t] = 0.0f;
+                }
             }
         }
     }
@@ -421,20 +430,37 @@ int launch_had_in(const unsigned long long* ptrs, const void* x, uint16_t* xh, f
 
 int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float* xinv, float* part, const Mul1Spec& s, int slots, int T,
                 size_t plane, cudaStream_t st) {
-    const int S = ksplit(s.k), tps = (s.k / 16) / S, rows = tps * 16;
-    const size_t smem = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * rows * 2 + 8 + (size_t)T * (rows / 128) * 4;
-    dim3 grid(s.n / 128, S, slots);
-    static bool attr = false;
-    if (!attr) {
-        CN_CUDA(cudaFuncSetAttribute(mul1_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        CN_CUDA(cudaFuncSetAttribute(mul1_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        attr = true;
+    const int S = ksplit(s.k), tps = (s.k / 16) / S;
+    // k-splits per CTA: as many as still leave about four CTAs per SM (the splits keep separate partial sums, so
+    // this only moves work between CTAs) and fit the staged activations
+    int spc = 1;
+    for (int c = S; c > 1; c--) {
+        if (S % c) continue;
+        const long long ctas = (long long)(s.n / 128) * (S / c) * slots;
+        const size_t need = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * (c * tps * 16) * 2 + 8 + (size_t)T * (c * tps / 8) * 4;
+        if (ctas >= 592 && need <= 160 * 1024) {
+            spc = c;
+            break;
+        }
     }
+    const int rows = spc * tps * 16;
+    const size_t smem = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * rows * 2 + 8 + (size_t)T * (rows / 128) * 4;
+    dim3 grid(s.n / 128, S / spc, slots);
     if (smem > 160 * 1024) CN_FAIL(CN_ERR_LIMIT, "mul1 gemv: %zu B of shared memory per block", smem);
-    if (s.bits == 3 && !s.half)
-        mul1_gemv_kernel<true><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T, plane);
-    else
-        mul1_gemv_kernel<false><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T, plane);
+    const bool k3 = s.bits == 3 && !s.half;
+    const int mt = T == 1 ? 1 : (T == 2 ? 2 : (T <= 4 ? 4 : 8));
+#define CN_MUL1_CASE(K3V, MTV)                                                                                                      \
+    if (k3 == K3V && mt == MTV) {                                                                                                   \
+        static bool attr = false;                                                                                                   \
+        if (!attr) {                                                                                                                \
+            CN_CUDA(cudaFuncSetAttribute(mul1_gemv_kernel<K3V, MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));     \
+            attr = true;                                                                                                            \
+        }                                                                                                                           \
+        mul1_gemv_kernel<K3V, MTV><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T, plane, spc);                            \
+    }
+    CN_MUL1_CASE(true, 1) CN_MUL1_CASE(true, 2) CN_MUL1_CASE(true, 4) CN_MUL1_CASE(true, 8)
+    CN_MUL1_CASE(false, 1) CN_MUL1_CASE(false, 2) CN_MUL1_CASE(false, 4) CN_MUL1_CASE(false, 8)
+#undef CN_MUL1_CASE
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
