@@ -452,6 +452,12 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     // persistent CTAs, each walking its share of the tiles (the routed form keeps one tile per CTA)
     int grid = ntiles;
     if (!routed && grid > 148 * cps) grid = 148 * cps;
+    if (routed && (long long)ntiles * a.combos > 3LL * 148 * cps / 2) {
+        // many combos: a few persistent CTAs per combo (the activation row is staged once per CTA), about one wave in all
+        grid = 148 * cps / a.combos;
+        if (grid < 1) grid = 1;
+        grid = (ntiles + ((ntiles + grid - 1) / grid) - 1) / ((ntiles + grid - 1) / grid);  // the same tiles per CTA, fewer CTAs
+    }
     // When the tiles do not fill the last wave, pairs of CTAs (a cluster of two) share every tile, each over half of
     // K, and the pair's second CTA hands its 16 sums to the first through distributed shared memory: the wave
     // quantum drops from a tile to half a tile. Taken when that shortens the longest CTA by a tenth or more.
