@@ -36,7 +36,7 @@ constexpr int GEMM_THREADS = (A_WARPS + B_WARPS + 1) * 32;
 // TN activation rows per CTA: 128 (3 stages, two CTAs per SM) or 256 (4 stages, one CTA per SM, half the weight
 // decoding per MMA)
 __host__ __device__ constexpr int stages_of(int tn) { return tn == 256 ? 4 : 3; }
-__host__ __device__ constexpr int smem_of(int tn) { return 1024 + stages_of(tn) * (A_BYTES + tn * 128) + 1024; }  // header + ring + alignment slack
+__host__ __device__ constexpr int smem_of(int tn) { return 2048 + stages_of(tn) * (A_BYTES + tn * 128) + 1024; }  // header (barriers, scale table) + ring + alignment slack
 // instruction descriptor, kind::f16: D f32 (bit 4), A and B f16 K-major (0), N >> 3 at bit 17, M >> 4 at bit 24
 __host__ __device__ constexpr uint32_t idesc_of(int tn) { return (1u << 4) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(TM >> 4) << 24); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -113,6 +113,10 @@ struct GemmParams {
     const float* rs;
     void* y;
     int rows, k, m, ldy, out_bf16;
+    // K shared between `ksplits` CTAs of a tile (blockIdx.y, when m <= 128 and the row tiles alone do not fill the
+    // machine): each writes its raw f32 sums to part[split][m][rows], a second kernel adds them in split order
+    int ksplits;
+    float* part;
 };
 
 template <int TN>
@@ -126,13 +130,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc
     uint64_t* accbar = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accbar + 1);
     volatile int* failed = (volatile int*)(tmem_slot + 1);
-    const uint32_t ring_addr = (smem_u32(smem_raw) + 1024u + 1023u) & ~1023u;
+    uint32_t* slut = (uint32_t*)(smem_raw + 1024);  // [256] UE4M3 scale byte -> f16x2 (both halves), 0x7F read as 0x7E
+    const uint32_t ring_addr = (smem_u32(smem_raw) + 2048u + 1023u) & ~1023u;
     uint8_t* ring = smem_raw + (ring_addr - smem_u32(smem_raw));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row0 = blockIdx.x * TM, tok0 = blockIdx.y * TN;
-    const int bpr = p.k >> 6;
-    const size_t row_bytes = (size_t)bpr * 36;
+    const int KSP = p.ksplits, ksi = KSP > 1 ? (int)blockIdx.y : 0;
+    const int row0 = blockIdx.x * TM, tok0 = KSP > 1 ? 0 : (int)blockIdx.y * TN;
+    const int bpr_all = p.k >> 6;
+    const int kbeg = (int)((long long)bpr_all * ksi / KSP), bpr = (int)((long long)bpr_all * (ksi + 1) / KSP) - kbeg;  // this CTA's blocks
+    const size_t row_bytes = (size_t)bpr_all * 36;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -142,6 +149,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc
         mbar_init(accbar, 1);
         mbar_fence_init();
         *failed = 0;
+    }
+    if (tid < 256) {
+        const __half2 h2 = __half2half2(__float2half_rn(ue4m3_f32((uint32_t)tid, true)));
+        slut[tid] = *(const uint32_t*)&h2;
     }
     if (warp == A_WARPS + B_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TN) : "memory");
@@ -165,7 +176,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc
         for (int u = 0; u < UNITS; u++) {
             const int r = (u * (A_WARPS * 32) + tid) >> 3;
             live[u] = row0 + r < p.rows;
-            src[u] = (const uint32_t*)(p.w + (size_t)(live[u] ? row0 + r : 0) * row_bytes);
+            src[u] = (const uint32_t*)(p.w + (size_t)(live[u] ? row0 + r : 0) * row_bytes + (size_t)kbeg * 36);
         }
         uint32_t code[PF][UNITS], scl[PF][UNITS];
         auto fetch = [&](int d, int kb) {
@@ -206,7 +217,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc
                 for (int u = 0; u < UNITS; u++) {
                     const int r = (u * (A_WARPS * 32) + tid) >> 3;
                     // the chunk's sub-block is c >> 1: its scale in both halves of an f16x2
-                    const __half2 s2 = __half2half2(__float2half_rn(ue4m3_f32((sw[u] >> (8 * (c >> 1))) & 0xFFu, true)));
+                    const uint32_t sbits = slut[(sw[u] >> (8 * (c >> 1))) & 0xFFu];
+                    const __half2 s2 = *(const __half2*)&sbits;
                     uint32_t f[4];
                     e2m1x8_to_f16x2(cw[u], f);
 #pragma unroll
@@ -239,7 +251,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc
                 const int idx = it * (B_WARPS * 32) + j, jr = idx >> 3, c = idx & 7, tok = tok0 + jr;
                 uint8_t* dst = ring + (size_t)s * (A_BYTES + B_BYTES) + A_BYTES + (size_t)jr * 128 + ((c ^ (jr & 7)) << 4);
                 if (tok < p.m)
-                    cp_async16(smem_u32(dst), (const uint4*)(p.xh + (size_t)tok * p.k) + (size_t)kb * 8 + c);
+                    cp_async16(smem_u32(dst), (const uint4*)(p.xh + (size_t)tok * p.k) + (size_t)(kbeg + kb) * 8 + c);
                 else
                     *(uint4*)dst = make_uint4(0u, 0u, 0u, 0u);
             }
@@ -289,6 +301,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc
                 for (int i = 0; i < 32; i++) {
                     const int tok = tok0 + c0 + i;
                     if (tok < p.m && row < p.rows) {
+                        if (KSP > 1) {
+                            p.part[((size_t)ksi * p.m + tok) * p.rows + row] = __uint_as_float(v[i]);
+                            continue;
+                        }
                         const float r = __uint_as_float(v[i]) * (gs * p.rs[tok]);
                         if (p.out_bf16)
                             ((__nv_bfloat16*)p.y)[(size_t)tok * p.ldy + row] = __float2bfloat16_rn(r);
@@ -304,11 +320,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, TN == 256 ? 1 : 2) nvfp4_gemm_tc
     if (warp == A_WARPS + B_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TN) : "memory");
 }
 
+// y[t][n] = (sum over splits, in order, of part[s][t][n]) * gs * rs[t]
+__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ part, const float* __restrict__ gs, const float* __restrict__ rs,
+                                          void* __restrict__ y, int rows, int m, int ldy, int ksplits, int out_bf16) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (n >= rows) return;
+    float v = part[(size_t)t * rows + n];
+    for (int s = 1; s < ksplits; s++) v += part[((size_t)s * m + t) * rows + n];
+    v *= gs[0] * rs[t];
+    if (out_bf16)
+        ((__nv_bfloat16*)y)[(size_t)t * ldy + n] = __float2bfloat16_rn(v);
+    else
+        ((float*)y)[(size_t)t * ldy + n] = v;
+}
+
+constexpr int MAX_KSPLITS = 8;
+
+// K splits for m <= 128: enough CTAs for two per SM, at least eight 64-wide steps each
+int gemm_ksplits(int rows, int k, int m) {
+    if (m > 128) return 1;
+    const int tiles = (rows + TM - 1) / TM, bpr = k / 64;
+    int ks = (2 * 148 + tiles - 1) / tiles;
+    if (ks > MAX_KSPLITS) ks = MAX_KSPLITS;
+    if (ks > bpr / 8) ks = bpr / 8;
+    return ks < 1 ? 1 : ks;
+}
+
 }  // namespace
 
 extern "C" size_t cn_nvfp4_gemm_workspace_bytes(int k, int m) {
     if (k <= 0 || m <= 0) return 0;
-    return (size_t)m * k * 2 + (((size_t)m * 4 + 255) & ~(size_t)255) + 256;
+    // widened activations, row scales, and (m <= 128) room for the partial sums of up to 8 K splits of 2^15 rows
+    const size_t part = m <= 128 ? (size_t)MAX_KSPLITS * m * 32768 * 4 : 0;
+    return (size_t)m * k * 2 + (((size_t)m * 4 + 255) & ~(size_t)255) + 256 + part;
 }
 
 extern "C" int cn_nvfp4_gemm(const void* w, const float* gs, const void* x, void* y, int rows, int k, int m, int ldy, int dtype, void* workspace,
@@ -337,12 +381,22 @@ extern "C" int cn_nvfp4_gemm(const void* w, const float* gs, const void* x, void
     }
     GemmParams p;
     p.w = (const uint8_t*)w, p.gs = gs, p.xh = xh, p.rs = rs, p.y = y, p.rows = rows, p.k = k, p.m = m, p.ldy = ldy, p.out_bf16 = dtype == CN_BF16;
+    p.ksplits = 1, p.part = nullptr;
     if (m > 128) {
         dim3 grid((unsigned)((rows + TM - 1) / TM), (unsigned)((m + 255) / 256));
         nvfp4_gemm_tc5_kernel<256><<<grid, GEMM_THREADS, smem_of(256), stream>>>(p);
     } else {
-        dim3 grid((unsigned)((rows + TM - 1) / TM), 1);
+        int ks = gemm_ksplits(rows, k, m);
+        if (rows > 32768) ks = 1;  // the workspace holds partial sums for up to 2^15 rows
+        p.ksplits = ks;
+        p.part = (float*)((char*)workspace + (((size_t)m * k * 2 + 255) & ~(size_t)255) + (((size_t)m * 4 + 255) & ~(size_t)255));
+        dim3 grid((unsigned)((rows + TM - 1) / TM), (unsigned)ks);
         nvfp4_gemm_tc5_kernel<128><<<grid, GEMM_THREADS, smem_of(128), stream>>>(p);
+        if (ks > 1) {
+            CN_CUDA(cudaGetLastError());
+            gemm_splitk_reduce_kernel<<<dim3((unsigned)((rows + 255) / 256), (unsigned)m), 256, 0, stream>>>(p.part, gs, rs, y, rows, m, ldy, ks,
+                                                                                                         p.out_bf16);
+        }
     }
     CN_CUDA(cudaGetLastError());
     return CN_OK;
