@@ -164,3 +164,30 @@ def test_errors_are_named_not_fatal():
         ops.launch_gemv(dev, torch.zeros((9, 256), dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(CrownestError, match="needs"):
         ops.Fp4.from_host(np.zeros(10, np.uint8), 64, 256, 1.0)
+
+
+@pytest.mark.parametrize("rows,cols,gu", [(640, 4096, False), (5120, 17408, False), (512, 2048, True)])
+def test_k_shared_by_a_cta_pair_matches_the_cpu_reference(rows, cols, gu):
+    """Tuning key 10 = 2 forces the two-CTA-cluster form (each CTA of a pair over half of K, sums handed over through
+    distributed shared memory) wherever the shape allows; the library itself picks it for the down projection."""
+    from crownest_b200._lib import lib
+    rng, w, fw = make(rows, cols, rows + cols)
+    xb, xf = synth.activations(1, cols, rng)
+    lib().cn_set_tuning(10, 2)
+    try:
+        if gu:
+            w2 = synth.nvfp4_matrix(rows, cols, rng)
+            fw2 = ops.Fp4.from_host(w2, rows, cols, 1.0)
+            y = ops.launch_gemv_gu(fw, fw2, to_dev_bf16(xb))
+            g = oracle.nvfp4_gemv(w, rows, cols, np.float32(1.0), xf, threads=8, path=1)
+            u = oracle.nvfp4_gemv(w2, rows, cols, np.float32(1.0), xf, threads=8, path=1)
+            ref = np.vectorize(oracle.lib().cn_o_silu_mul)(g, u).astype(np.float32)
+        else:
+            y = ops.launch_gemv(fw, to_dev_bf16(xb))
+            ref = oracle.nvfp4_gemv(w, rows, cols, np.float32(1.0), xf, threads=8, path=1)
+        y2 = ops.launch_gemv_gu(fw, fw2, to_dev_bf16(xb)) if gu else ops.launch_gemv(fw, to_dev_bf16(xb))
+    finally:
+        lib().cn_set_tuning(10, 0)
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))  # run to run: the same bits
+    check_close(from_dev_bf16(y), ref, f"cluster pair {rows}x{cols} gu={gu}", ulp_floor=1.0 / 64 if gu else 0.0)
+    assert device_status() == 0
