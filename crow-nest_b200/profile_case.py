@@ -26,14 +26,13 @@ def main():
         w = torch.randint(0, 256, (nbytes // 36, 36), dtype=torch.uint8, device="cuda", generator=gen)
         w[:, :4] = torch.randint(0x20, 0x38, (nbytes // 36, 4), dtype=torch.uint8, device="cuda", generator=gen)
         ws.append(ops.Fp4(w.reshape(-1), torch.ones(1, device="cuda"), rows, args.k))
-    ws_w = ws
     x = torch.randn(args.m, args.k, device="cuda", generator=gen).to(torch.bfloat16)
     y = torch.empty(args.m, rows, device="cuda", dtype=torch.bfloat16)
     torch.cuda.synchronize()
-    ws = torch.empty(ops.gemm_workspace_bytes(args.k, args.m), dtype=torch.uint8, device="cuda") if args.op == "gemm" else None
+    scratch = torch.empty(ops.gemm_workspace_bytes(args.k, args.m), dtype=torch.uint8, device="cuda") if args.op == "gemm" else None
     for i in range(args.launches):
         if args.op == "gemm":
-            ops.launch_gemm(ws_w[i % args.copies], x, y, workspace=ws)
+            ops.launch_gemm(ws[i % args.copies], x, y, workspace=scratch)
         elif args.op == "gu":
             ops.launch_gemv_gu(ws[2 * (i % args.copies)], ws[2 * (i % args.copies) + 1], x, y)
         else:
