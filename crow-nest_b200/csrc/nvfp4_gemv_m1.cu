@@ -1,10 +1,17 @@
-// NVFP4 GEMV for one bf16 activation row (decode, and every combo of the routed-expert step):
-// persistent CTAs, tensor-core inner loop in "word" form.
+// NVFP4 GEMV for 1..8 bf16 activation rows (decode, MTP verify, and every combo of the routed-expert
+// step): persistent CTAs, tensor-core inner loop in "word" form. Supersedes gemv_nvfp4_w / _gu / _wm /
+// _gum (engine/src/kernels_p2.rs:355-530) and the routed record kernels gemv_fp4(_b), gemv_fp4_ptrb
+// (engine/src/kernels.rs:118-195) for bf16 activations.
 //
-// A CTA owns a list of 16-row tiles (tile = blockIdx.x + i * gridDim.x). The activation row is staged
+// A CTA owns a list of 16-row tiles (tile = blockIdx.x + i * gridDim.x). The activation rows are staged
 // once per CTA (f16 with a power-of-two scale per 64-value block: exact for bf16), the producer warp
 // streams the tiles' weight bytes through one mbarrier ring without draining it between tiles, and
-// eight consumer warps split the K range of every stage between them.
+// eight consumer warps split the K range of every stage between them; their 16 sums per tile meet in a
+// small shared-memory ring with one mbarrier per slot, so no CTA-wide barrier sits in the loop.
+// With more than one activation row the decoded weight fragments are used by every row (8 MMAs per
+// row and group); row i of an m-row call is summed in exactly the order of a one-row call.
+// When the tiles do not fill the last wave and a CTA's share is long enough (the down projection),
+// the launch is made of two-CTA clusters whose CTAs take half of K each (see the helpers below).
 //
 // Inner loop. mma.sync.m16n8k16 (f16 x f16 -> f32) takes the f16x2 registers that
 // cvt.rn.f16x2.e2m1x2 makes: A = 16 weight rows x 16 codes, B = the matching activations. The order
