@@ -100,6 +100,19 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Launch with programmatic dependent launch allowed: the grid may be scheduled while its predecessor in the stream
+// drains; the kernel calls pdl_wait() before it touches anything the predecessor wrote.
+template <typename... KArgs, typename... Args>
+inline cudaError_t cn_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------- device: NVFP4 decode
 // UE4M3 scale byte -> f32 with the engine's reading: bit 7 ignored, e == 0 subnormal m * 2^-9,
 // 0x7F -> 448 when `rule` (engine/src/cnq.rs:1287, engine/src/cpu_nvfp4.rs:88).

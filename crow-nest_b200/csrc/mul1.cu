@@ -78,6 +78,8 @@ __device__ __forceinline__ void store_hi_lo(uint16_t* xh, size_t plane, size_t a
 template <int XT>
 __global__ void mul1_had_in_kernel(const unsigned long long* __restrict__ ptrs, const void* __restrict__ x, uint16_t* __restrict__ xh,
                                    float* __restrict__ xinv, int k, int T, long long suh_off, int x_div, size_t plane) {
+    pdl_launch_dependents();
+    pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
     if (ptrs[slot] == 0ull) return;  // a null record: nothing to read or write
     const uint16_t* suh = (const uint16_t*)(ptrs[slot] + (unsigned long long)suh_off);
@@ -142,6 +144,8 @@ template <bool K3, int MT>
 __global__ void __launch_bounds__(288, MT == 1 ? 4 : (MT == 2 ? 3 : (MT == 4 ? 2 : 1))) mul1_gemv_kernel(const unsigned long long* __restrict__ ptrs, const uint16_t* __restrict__ xh,
                                                         const float* __restrict__ xinv, float* __restrict__ part, Mul1Spec sp_, int S, int T,
                                                         size_t plane, int SPC) {
+    pdl_launch_dependents();
+    pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     // SPC consecutive k-splits per CTA (blockIdx.y walks groups of SPC): the splits keep their own partial sums, so
     // the arithmetic does not depend on SPC; a CTA that takes several streams them through one ring without a drain
     extern __shared__ __align__(128) uint8_t smem[];
@@ -313,6 +317,8 @@ __device__ __forceinline__ void out_block(float v[4], const float* __restrict__ 
 template <int YT>
 __global__ void mul1_had_out_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part, void* __restrict__ y, int n,
                                     int S, int T, long long svh_off) {
+    pdl_launch_dependents();
+    pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
     if (ptrs[slot] == 0ull) return;
     float v[4];
@@ -332,6 +338,8 @@ __global__ void mul1_had_out_kernel(const unsigned long long* __restrict__ ptrs,
 __global__ void mul1_act_had_in_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part_g,
                                        const float* __restrict__ part_u, uint16_t* __restrict__ xh_d, float* __restrict__ xinv_d, int inter, int S,
                                        int T, long long svh_g, long long svh_u, long long suh_d, float limit, size_t plane) {
+    pdl_launch_dependents();
+    pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
     if (ptrs[slot] == 0ull) return;
     float g[4], u[4], v[4];
@@ -421,9 +429,9 @@ int launch_had_in(const unsigned long long* ptrs, const void* x, uint16_t* xh, f
                   int dtype, size_t plane, cudaStream_t st) {
     dim3 grid(s.k / 128, T, slots);
     if (dtype == CN_BF16)
-        mul1_had_in_kernel<1><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane);
+        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane));
     else
-        mul1_had_in_kernel<0><<<grid, 32, 0, st>>>(ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane);
+        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
@@ -456,7 +464,7 @@ int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float*
             CN_CUDA(cudaFuncSetAttribute(mul1_gemv_kernel<K3V, MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));     \
             attr = true;                                                                                                            \
         }                                                                                                                           \
-        mul1_gemv_kernel<K3V, MTV><<<grid, 288, smem, st>>>(ptrs, xh, xinv, part, s, S, T, plane, spc);                            \
+        CN_CUDA(cn_launch_pdl((mul1_gemv_kernel<K3V, MTV>), grid, dim3(288), smem, st, ptrs, xh, xinv, part, s, S, T, plane, spc));        \
     }
     CN_MUL1_CASE(true, 1) CN_MUL1_CASE(true, 2) CN_MUL1_CASE(true, 4) CN_MUL1_CASE(true, 8)
     CN_MUL1_CASE(false, 1) CN_MUL1_CASE(false, 2) CN_MUL1_CASE(false, 4) CN_MUL1_CASE(false, 8)
@@ -473,6 +481,8 @@ int check_run(const Mul1Plan* p, int slots, int T, const char* who) {
 }
 
 __global__ void mul1_gather_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ ids, unsigned long long* ptrs, int n) {
+    pdl_launch_dependents();
+    pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c < n) ptrs[c] = ids[c] < 0 ? 0ull : table[ids[c]];
 }
@@ -521,9 +531,9 @@ extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptr
     if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, s, slots, t, p->plane, st)) return rc;
     dim3 grid(s.n / 128, t, slots);
     if (dtype == CN_BF16)
-        mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off);
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off));
     else
-        mul1_had_out_kernel<0><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off);
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
@@ -536,15 +546,15 @@ static int mul1_ffn(Mul1Plan* p, const unsigned long long* ptrs, const void* x, 
     if (int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, p->plane, st)) return rc;
     if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, p->plane, st)) return rc;
     if (int rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, p->plane, st)) return rc;
-    mul1_act_had_in_kernel<<<dim3(p->inter / 128, t, slots), 32, 0, st>>>(ptrs, p->part_a, p->part_b, p->xh_a, p->xinv_a, p->inter, ksplit(p->hidden), t,
-                                                                         g.svh_off, u.svh_off, d.suh_off, limit, p->plane);
+    CN_CUDA(cn_launch_pdl(mul1_act_had_in_kernel, dim3(p->inter / 128, t, slots), dim3(32), 0, st, ptrs, p->part_a, p->part_b, p->xh_a, p->xinv_a, p->inter, ksplit(p->hidden), t,
+                                                                         g.svh_off, u.svh_off, d.suh_off, limit, p->plane));
     CN_CUDA(cudaGetLastError());
     if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, d, slots, t, p->plane, st)) return rc;
     dim3 grid(d.n / 128, t, slots);
     if (dtype == CN_BF16 && !out_f32)
-        mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off);
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off));
     else
-        mul1_had_out_kernel<0><<<grid, 32, 0, st>>>(ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off);
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
@@ -566,7 +576,7 @@ extern "C" int cn_moe_mul1_run(void* plan, const unsigned long long* table, cons
     const int combos = tokens * topk;
     if (int rc = check_run(p, combos, 1, "cn_moe_mul1_run")) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    mul1_gather_kernel<<<(combos + 127) / 128, 128, 0, st>>>(table, ids, p->ptrs, combos);
+    CN_CUDA(cn_launch_pdl(mul1_gather_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->ptrs, combos));
     CN_CUDA(cudaGetLastError());
     if (int rc = mul1_ffn(p, p->ptrs, x, p->eo, combos, 1, topk, limit, dtype, 1, st)) return rc;
     return cn_moe_combine(p->eo, wts, ids, table, shared, nullptr, y, tokens, p->hidden, topk, dtype, stream);
@@ -649,9 +659,9 @@ extern "C" int cn_mul1_gemv_noalloc(int which, int hidden, int inter, int bits, 
     if (int rc = launch_gemv(ptrs, xh, xinv, part, s, slots, t, plane, st)) return rc;
     dim3 grid(s.n / 128, t, slots);
     if (dtype == CN_BF16)
-        mul1_had_out_kernel<1><<<grid, 32, 0, st>>>(ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off);
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off));
     else if (dtype == CN_F32)
-        mul1_had_out_kernel<0><<<grid, 32, 0, st>>>(ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off);
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off));
     else
         CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv_noalloc: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     CN_CUDA(cudaGetLastError());
