@@ -69,23 +69,36 @@ class PeerExchange:
             self.flag_off[name] = at
             at += 64
         self.buf = torch.zeros(at, dtype=torch.uint8, device=device)
-        handle, offset = C.create_string_buffer(64), C.c_size_t(0)
-        check(lib().cn_peer_export(self.buf.data_ptr(), handle, C.byref(offset)))
-        mine = (bytes(handle.raw), int(offset.value))
+        # every step below is collective: a rank whose export or open fails still takes part, and all ranks raise together
+        handle, offset, err = C.create_string_buffer(64), C.c_size_t(0), None
+        try:
+            check(lib().cn_peer_export(self.buf.data_ptr(), handle, C.byref(offset)))
+        except CrownestError as e:
+            err = str(e)
         everyone = [None] * world
-        dist.all_gather_object(everyone, mine, group=group)
+        dist.all_gather_object(everyone, (bytes(handle.raw), int(offset.value), err), group=group)
         self.bases = (C.c_void_p * world)()
         self.opened = []
-        for r, (h, o) in enumerate(everyone):
-            if r == rank:
-                self.bases[r] = self.buf.data_ptr()
-            else:
+        if not any(e for _, _, e in everyone):
+            for r, (h, o, _) in enumerate(everyone):
+                if r == rank:
+                    self.bases[r] = self.buf.data_ptr()
+                    continue
                 p = C.c_void_p()
-                check(lib().cn_peer_open(h, o, C.byref(p)))
+                try:
+                    check(lib().cn_peer_open(h, o, C.byref(p)))
+                except CrownestError as e:
+                    err = str(e)
+                    break
                 self.bases[r] = p.value
                 self.opened.append((p.value, o))
+        errs = [None] * world
+        dist.all_gather_object(errs, err, group=group)
         torch.cuda.synchronize()
         dist.barrier(group=group)  # every buffer is zeroed and open before the first exchange
+        bad = [e for e in errs if e] + [e for _, _, e in everyone if e]
+        if bad:
+            raise CrownestError("peer exchange unavailable: " + bad[0])
 
     def vector(self, name, n):
         """The local copy of a vector as a [1][n] bf16 tensor."""
@@ -135,8 +148,11 @@ class DenseStack:
             if exchange == "peer" and max_m == 1 and dtype == torch.bfloat16:
                 # one activation row: the slices are written straight into a peer-visible buffer and pushed to the peers
                 sizes = {"q": self.qkv, "o": self.hidden, "h": self.inter, "y": self.hidden}
-                self.peer = PeerExchange(sizes, rank, world, device, group)
-                self.q, self.o, self.h, self.y = (self.peer.vector(n, r) for n, r in sizes.items())
+                try:
+                    self.peer = PeerExchange(sizes, rank, world, device, group)  # raises on every rank or on none
+                    self.q, self.o, self.h, self.y = (self.peer.vector(n, r) for n, r in sizes.items())
+                except CrownestError as e:  # no peer access between these GPUs: NCCL all-gather instead
+                    self.peer, self.peer_error = None, str(e)
         self.launches_per_step = 4 * self.layers
         self.graph = None
 
