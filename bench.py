@@ -337,7 +337,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--m", type=int, default=1, help="activation rows per step (1 decode, 4 = MTP verify)")
+    # "--act-rows": the spelling to use under torch.distributed.run, whose own parser takes "--m" for an abbreviation
+    ap.add_argument("--m", "--act-rows", dest="m", type=int, default=1, help="activation rows per step (1 decode, 4 = MTP verify)")
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--impl", default="crownest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
