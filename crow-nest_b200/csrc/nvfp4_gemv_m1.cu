@@ -8,8 +8,9 @@
 // streams the tiles' weight bytes through one mbarrier ring without draining it between tiles, and
 // eight consumer warps split the K range of every stage between them; their 16 sums per tile meet in a
 // small shared-memory ring with one mbarrier per slot, so no CTA-wide barrier sits in the loop.
-// With more than one activation row the decoded weight fragments are used by every row (8 MMAs per
-// row and group); row i of an m-row call is summed in exactly the order of a one-row call.
+// With more than one activation row the C columns are packed (four activation rows x the two sub-blocks
+// of a pair: 8 MMAs per group for up to four rows, 16 for eight); row i of an m-row call is summed in
+// exactly the order of a one-row call.
 // When the tiles do not fill the last wave and a CTA's share is long enough (the down projection),
 // the launch is made of two-CTA clusters whose CTAs take half of K each (see the helpers below).
 //
@@ -201,7 +202,11 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         // task = (row * bpr + block) * 8 + chunk; rows beyond p.m read as zero
         return (task < ntask && (MT == 1 || (task >> 3) < p.m * bpr)) ? __ldcg((const uint4*)xbase + task) : make_uint4(0u, 0u, 0u, 0u);
     };
-    uint4 nxt = load_x(tid);
+    // PF loads of every thread are in flight at any time: the staging loop costs about one trip to L2 per PF tasks
+    constexpr int PF = CPS >= 4 ? 2 : 4;
+    uint4 pre[PF];
+#pragma unroll
+    for (int i = 0; i < PF; i++) pre[i] = load_x(tid + i * (NW * 32));
     if (tid < 4) ((uint32_t*)(smem + ZERO_OFF))[tid] = 0u;
     if (tid >= 4 && tid < 8) ((uint32_t*)(smem + ZERO2_OFF))[tid - 4] = 0u;
     {
@@ -215,10 +220,14 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     bool ok = true;
     // bf16 -> f16 * 2^e per 64-value block, chunk i of block b stored at chunk i ^ (b & 7). Eight lanes per block,
     // one 16-byte chunk each, straight from global memory (k % 256 == 0 makes every warp wholly in or out of range).
-    for (int task = tid; task < ntask; task += NW * 32) {
+    for (int task0 = tid; task0 < ntask; task0 += PF * NW * 32) {
+#pragma unroll
+      for (int pf = 0; pf < PF; pf++) {
+        const int task = task0 + pf * (NW * 32);
+        const uint4 raw = pre[pf];
+        pre[pf] = load_x(task + PF * NW * 32);
+        if (task >= ntask) break;  // uniform over the warp
         const int b = task >> 3, i = task & 7;
-        const uint4 raw = nxt;
-        nxt = load_x(task + NW * 32);
         const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
         float amax = 0.0f;
 #pragma unroll
@@ -245,6 +254,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         const int blk = MT == 1 ? b : b % bpr;
         ((uint4*)(xs0 + (size_t)b * XB))[i ^ (blk & 7)] = make_uint4(h[0], h[1], h[2], h[3]);
         if (i == 0) xinv0[b] = inv;
+      }
     }
     asm volatile("bar.sync 2, %0;" ::"n"(NTHREADS) : "memory");  // staging done, and the ring's barriers are initialised
 
@@ -261,14 +271,36 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     const int sdelta = -4 * t + (t >> 1) * 36 + 2 * (t & 1);  // from a row's code word to its two scale bytes
     const float* xinv_lane = xinv0 + 2 * warp + (t >> 1);  // row m: + m * bpr
     const float* lut_b = lut + (gu ? 256 : 0);  // gate/up: rows 8-15 are up rows
+    // More than one activation row: "packed columns". Column g of the C tile = activation row (g >> 1) of a pass of
+    // four rows, sub-block (g & 1) of the pair in hand, so the two MMAs of a pair serve four rows at once and a lane
+    // (g, t) ends up with the sums of activation row t for weight rows g and g + 8. A lane fills column g where its
+    // k slots belong to that column's sub-block (t >> 1 == g & 1) and reads the zero chunk otherwise. A pair's C tile
+    // is scaled on its own (every lane looks up both rows' eight scales of a group), and the four pairs of a group keep
+    // separate running sums that are added as (p0 + p1) + (p2 + p3) at the end of the tile: the order in which the
+    // one-row form's quad shuffle adds them, which keeps row i of an m-row call bit-identical to a one-row call.
+    constexpr int NP = MT > 4 ? 2 : 1;  // passes of four activation rows
+    const bool live = MT > 1 && (t >> 1) == (g & 1) && (g >> 1) < MT;
+    uint32_t xq_lane[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int blk = 2 * warp + (q >> 1);
+        xq_lane[q] = live ? xs_off + (uint32_t)((g >> 1) * XS + blk * XB + (((4 * (q & 1) + t) ^ (blk & 7)) << 4)) : (uint32_t)ZERO_OFF;
+    }
+    const uint32_t cstep = live ? (uint32_t)(TX * XB) : 0u, pstep = live ? 4u * XS : 0u;
+    const int mrow = t < MT ? t : MT - 1;  // this lane's activation row of a pass (lanes without one compute a copy)
 
     int s = 0, rslot = 0;
     uint32_t par = 0, rpar = 0;
     int titer = 0;
     for (int tile = cid; tile < ntiles && ok; tile += ncl, titer++) {
-        float acc0[MT], acc1[MT];  // rows g and g + 8 of the tile, this lane's two columns, per activation row
+        float acc0[MT], acc1[MT];  // one row: rows g and g + 8 of the tile, this lane's two columns
+        float pk0[NP][4], pk1[NP][4];  // packed columns: rows g and g + 8, activation row t of each pass, per pair
 #pragma unroll
         for (int m = 0; m < MT; m++) acc0[m] = acc1[m] = 0.0f;
+#pragma unroll
+        for (int ps = 0; ps < NP; ps++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) pk0[ps][q] = pk1[ps][q] = 0.0f;
         for (int c = 0; c < nch; c++) {
             const int ng = min(TX, bpr - c * TX) >> 1;  // groups of two blocks in this chunk
             if (!mbar_wait(&full[s], par)) {
@@ -278,44 +310,82 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             }
             const uint8_t* pa0 = stage0 + (size_t)s * stage_bytes + aoff;
             const uint32_t xoff = xoff_lane + (uint32_t)(c * TX * XB);
-            // where this lane's B registers of pair q come from: its activations (then row m is XS bytes further on) or
-            // the zero chunk (the same for every row)
-            uint32_t bq[4], bstep[4];
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
-                bstep[q] = myq == q ? XS : 0u;
-            }
-            const float* xip = xinv_lane + c * TX;
-#pragma unroll
-            for (int j = 0; j < GPW; j++) {
-                if (warp + NW * j < ng) {
-                    const uint8_t* pa = pa0 + j * (NW * 72);
-                    const uint8_t* pb = pa + 8 * pstride;
-                    float cc[MT][4];
-#pragma unroll
-                    for (int m = 0; m < MT; m++) cc[m][0] = cc[m][1] = cc[m][2] = cc[m][3] = 0.0f;
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
-                        uint32_t ha[4], hb[4];
-                        e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
-                        e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
-#pragma unroll
+            if constexpr (MT == 1) {
+                // where this lane's B registers of pair q come from: its activations (then row m is XS bytes further on) or
+                // the zero chunk (the same for every row)
+                uint32_t bq[4], bstep[4];
+    #pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
+                    bstep[q] = myq == q ? XS : 0u;
+                }
+                const float* xip = xinv_lane + c * TX;
+    #pragma unroll
+                for (int j = 0; j < GPW; j++) {
+                    if (warp + NW * j < ng) {
+                        const uint8_t* pa = pa0 + j * (NW * 72);
+                        const uint8_t* pb = pa + 8 * pstride;
+                        float cc[MT][4];
+    #pragma unroll
+                        for (int m = 0; m < MT; m++) cc[m][0] = cc[m][1] = cc[m][2] = cc[m][3] = 0.0f;
+    #pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
+                            uint32_t ha[4], hb[4];
+                            e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
+                            e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
+    #pragma unroll
+                            for (int m = 0; m < MT; m++) {
+                                const uint4 xv = *(const uint4*)(smem + bq[q] + m * bstep[q] + j * 2048);
+                                mma16816(cc[m], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+                                mma16816(cc[m], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+                            }
+                        }
+                        // columns 2t, 2t + 1 of C = sub-blocks 2t, 2t + 1 of the group: block t >> 1, scale bytes 2 (t & 1), + 1
+                        const uint8_t* sc = pa + sdelta;
+                        const float s0 = lut[sc[0]], s1 = lut[sc[1]], s2 = lut_b[sc[8 * pstride]], s3 = lut_b[sc[8 * pstride + 1]];
+    #pragma unroll
                         for (int m = 0; m < MT; m++) {
-                            const uint4 xv = *(const uint4*)(smem + bq[q] + m * bstep[q] + j * 2048);
-                            mma16816(cc[m], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
-                            mma16816(cc[m], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+                            const float xi = xip[m * bpr + 16 * j];
+                            acc0[m] = fmaf(fmaf(cc[m][1], s1, cc[m][0] * s0), xi, acc0[m]);
+                            acc1[m] = fmaf(fmaf(cc[m][3], s3, cc[m][2] * s2), xi, acc1[m]);
                         }
                     }
-                    // columns 2t, 2t + 1 of C = sub-blocks 2t, 2t + 1 of the group: block t >> 1, scale bytes 2 (t & 1), + 1
-                    const uint8_t* sc = pa + sdelta;
-                    const float s0 = lut[sc[0]], s1 = lut[sc[1]], s2 = lut_b[sc[8 * pstride]], s3 = lut_b[sc[8 * pstride + 1]];
+                }
+            } else {
+                const float* xip = xinv0 + 2 * warp + c * TX;
 #pragma unroll
-                    for (int m = 0; m < MT; m++) {
-                        const float xi = xip[m * bpr + 16 * j];
-                        acc0[m] = fmaf(fmaf(cc[m][1], s1, cc[m][0] * s0), xi, acc0[m]);
-                        acc1[m] = fmaf(fmaf(cc[m][3], s3, cc[m][2] * s2), xi, acc1[m]);
+                for (int j = 0; j < GPW; j++) {
+                    if (warp + NW * j < ng) {
+                        const uint8_t* pa = pa0 + j * (NW * 72);
+                        const uint8_t* pb = pa + 8 * pstride;
+                        // the scale bytes of rows g and g + 8: one word per 64-value block
+                        const uint8_t* sr = pa - 4 * t;
+                        const uint32_t sw0[2] = {*(const uint32_t*)sr, *(const uint32_t*)(sr + 36)};
+                        const uint32_t sw1[2] = {*(const uint32_t*)(sr + 8 * pstride), *(const uint32_t*)(sr + 8 * pstride + 36)};
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
+                            uint32_t ha[4], hb[4];
+                            e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
+                            e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
+                            // table look-ups by byte offset: one shift and one mask per scale byte
+                            const uint32_t wa = sw0[q >> 1], wb = sw1[q >> 1];
+                            const uint32_t o0 = (q & 1) ? (wa >> 14) & 0x3fcu : (wa << 2) & 0x3fcu, o1 = (q & 1) ? (wa >> 22) & 0x3fcu : (wa >> 6) & 0x3fcu;
+                            const uint32_t o2 = (q & 1) ? (wb >> 14) & 0x3fcu : (wb << 2) & 0x3fcu, o3 = (q & 1) ? (wb >> 22) & 0x3fcu : (wb >> 6) & 0x3fcu;
+                            const float s0 = *(const float*)((const char*)lut + o0), s1 = *(const float*)((const char*)lut + o1);
+                            const float s2 = *(const float*)((const char*)lut_b + o2), s3 = *(const float*)((const char*)lut_b + o3);
+#pragma unroll
+                            for (int ps = 0; ps < NP; ps++) {
+                                const uint4 xv = *(const uint4*)(smem + xq_lane[q] + c * cstep + ps * pstep + j * 2048);
+                                float cc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                                mma16816(cc, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+                                mma16816(cc, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+                                const float xi = xip[(ps * 4 + mrow) * bpr + 16 * j + (q >> 1)];
+                                pk0[ps][q] = fmaf(fmaf(cc[1], s1, cc[0] * s0), xi, pk0[ps][q]);
+                                pk1[ps][q] = fmaf(fmaf(cc[3], s3, cc[2] * s2), xi, pk1[ps][q]);
+                            }
+                        }
                     }
                 }
             }
@@ -330,16 +400,24 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         // the four lanes of a quad hold two columns each; then the eight warps' K ranges meet in shared memory:
         // every warp posts its sums and arrives on the slot's barrier, warp 0 alone waits for all eight
         float* rb = red + rslot * (NW * MT * 16);
-#pragma unroll
-        for (int m = 0; m < MT; m++) {
-            float a = acc0[m], b = acc1[m];
+        if constexpr (MT == 1) {
+            float a = acc0[0], b = acc1[0];
             a += __shfl_xor_sync(0xffffffffu, a, 1);
             b += __shfl_xor_sync(0xffffffffu, b, 1);
             a += __shfl_xor_sync(0xffffffffu, a, 2);
             b += __shfl_xor_sync(0xffffffffu, b, 2);
             if (t == 0) {
-                rb[(warp * MT + m) * 16 + g] = a;
-                rb[(warp * MT + m) * 16 + g + 8] = b;
+                rb[warp * 16 + g] = a;
+                rb[warp * 16 + g + 8] = b;
+            }
+        } else {
+#pragma unroll
+            for (int ps = 0; ps < NP; ps++) {
+                const int m = ps * 4 + t;
+                if (m < MT) {
+                    rb[(warp * MT + m) * 16 + g] = (pk0[ps][0] + pk0[ps][1]) + (pk0[ps][2] + pk0[ps][3]);
+                    rb[(warp * MT + m) * 16 + g + 8] = (pk1[ps][0] + pk1[ps][1]) + (pk1[ps][2] + pk1[ps][3]);
+                }
             }
         }
         __syncwarp();
