@@ -311,82 +311,80 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             const uint8_t* pa0 = stage0 + (size_t)s * stage_bytes + aoff;
             const uint32_t xoff = xoff_lane + (uint32_t)(c * TX * XB);
             if constexpr (MT == 1) {
-                // where this lane's B registers of pair q come from: its activations (then row m is XS bytes further on) or
-                // the zero chunk (the same for every row)
-                uint32_t bq[4], bstep[4];
-    #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
-                    bstep[q] = myq == q ? XS : 0u;
-                }
+                // where this lane's B registers of pair q come from: its activations or the zero chunk
+                uint32_t bq[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
                 const float* xip = xinv_lane + c * TX;
-    #pragma unroll
-                for (int j = 0; j < GPW; j++) {
-                    if (warp + NW * j < ng) {
-                        const uint8_t* pa = pa0 + j * (NW * 72);
-                        const uint8_t* pb = pa + 8 * pstride;
-                        float cc[MT][4];
-    #pragma unroll
-                        for (int m = 0; m < MT; m++) cc[m][0] = cc[m][1] = cc[m][2] = cc[m][3] = 0.0f;
-    #pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
-                            uint32_t ha[4], hb[4];
-                            e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
-                            e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
-    #pragma unroll
-                            for (int m = 0; m < MT; m++) {
-                                const uint4 xv = *(const uint4*)(smem + bq[q] + m * bstep[q] + j * 2048);
-                                mma16816(cc[m], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
-                                mma16816(cc[m], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
-                            }
-                        }
-                        // columns 2t, 2t + 1 of C = sub-blocks 2t, 2t + 1 of the group: block t >> 1, scale bytes 2 (t & 1), + 1
-                        const uint8_t* sc = pa + sdelta;
-                        const float s0 = lut[sc[0]], s1 = lut[sc[1]], s2 = lut_b[sc[8 * pstride]], s3 = lut_b[sc[8 * pstride + 1]];
-    #pragma unroll
-                        for (int m = 0; m < MT; m++) {
-                            const float xi = xip[m * bpr + 16 * j];
-                            acc0[m] = fmaf(fmaf(cc[m][1], s1, cc[m][0] * s0), xi, acc0[m]);
-                            acc1[m] = fmaf(fmaf(cc[m][3], s3, cc[m][2] * s2), xi, acc1[m]);
-                        }
+                auto group = [&](int j) {
+                    const uint8_t* pa = pa0 + j * (NW * 72);
+                    const uint8_t* pb = pa + 8 * pstride;
+                    float cc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
+                        uint32_t ha[4], hb[4];
+                        e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
+                        e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
+                        const uint4 xv = *(const uint4*)(smem + bq[q] + j * 2048);
+                        mma16816(cc, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+                        mma16816(cc, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
                     }
+                    // columns 2t, 2t + 1 of C = sub-blocks 2t, 2t + 1 of the group: block t >> 1, scale bytes 2 (t & 1), + 1
+                    const uint8_t* sc = pa + sdelta;
+                    const float s0 = lut[sc[0]], s1 = lut[sc[1]], s2 = lut_b[sc[8 * pstride]], s3 = lut_b[sc[8 * pstride + 1]];
+                    const float xi = xip[16 * j];
+                    acc0[0] = fmaf(fmaf(cc[1], s1, cc[0] * s0), xi, acc0[0]);
+                    acc1[0] = fmaf(fmaf(cc[3], s3, cc[2] * s2), xi, acc1[0]);
+                };
+                if (ng == TX / 2) {  // a full chunk: every warp has all its groups, nothing to test between them
+#pragma unroll
+                    for (int j = 0; j < GPW; j++) group(j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < GPW; j++)
+                        if (warp + NW * j < ng) group(j);
                 }
             } else {
                 const float* xip = xinv0 + 2 * warp + c * TX;
+                auto group = [&](int j) {
+                    const uint8_t* pa = pa0 + j * (NW * 72);
+                    const uint8_t* pb = pa + 8 * pstride;
+                    // the scale bytes of rows g and g + 8: one word per 64-value block
+                    const uint8_t* sr = pa - 4 * t;
+                    const uint32_t sw0[2] = {*(const uint32_t*)sr, *(const uint32_t*)(sr + 36)};
+                    const uint32_t sw1[2] = {*(const uint32_t*)(sr + 8 * pstride), *(const uint32_t*)(sr + 8 * pstride + 36)};
 #pragma unroll
-                for (int j = 0; j < GPW; j++) {
-                    if (warp + NW * j < ng) {
-                        const uint8_t* pa = pa0 + j * (NW * 72);
-                        const uint8_t* pb = pa + 8 * pstride;
-                        // the scale bytes of rows g and g + 8: one word per 64-value block
-                        const uint8_t* sr = pa - 4 * t;
-                        const uint32_t sw0[2] = {*(const uint32_t*)sr, *(const uint32_t*)(sr + 36)};
-                        const uint32_t sw1[2] = {*(const uint32_t*)(sr + 8 * pstride), *(const uint32_t*)(sr + 8 * pstride + 36)};
+                    for (int q = 0; q < 4; q++) {
+                        const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
+                        uint32_t ha[4], hb[4];
+                        e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
+                        e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
+                        // table look-ups by byte offset: one shift and one mask per scale byte
+                        const uint32_t wa = sw0[q >> 1], wb = sw1[q >> 1];
+                        const uint32_t o0 = (q & 1) ? (wa >> 14) & 0x3fcu : (wa << 2) & 0x3fcu, o1 = (q & 1) ? (wa >> 22) & 0x3fcu : (wa >> 6) & 0x3fcu;
+                        const uint32_t o2 = (q & 1) ? (wb >> 14) & 0x3fcu : (wb << 2) & 0x3fcu, o3 = (q & 1) ? (wb >> 22) & 0x3fcu : (wb >> 6) & 0x3fcu;
+                        const float s0 = *(const float*)((const char*)lut + o0), s1 = *(const float*)((const char*)lut + o1);
+                        const float s2 = *(const float*)((const char*)lut_b + o2), s3 = *(const float*)((const char*)lut_b + o3);
 #pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            const int off = (q >> 1) * 36 + 4 + 16 * (q & 1);
-                            uint32_t ha[4], hb[4];
-                            e2m1x8_to_f16x2(*(const uint32_t*)(pa + off), ha);
-                            e2m1x8_to_f16x2(*(const uint32_t*)(pb + off), hb);
-                            // table look-ups by byte offset: one shift and one mask per scale byte
-                            const uint32_t wa = sw0[q >> 1], wb = sw1[q >> 1];
-                            const uint32_t o0 = (q & 1) ? (wa >> 14) & 0x3fcu : (wa << 2) & 0x3fcu, o1 = (q & 1) ? (wa >> 22) & 0x3fcu : (wa >> 6) & 0x3fcu;
-                            const uint32_t o2 = (q & 1) ? (wb >> 14) & 0x3fcu : (wb << 2) & 0x3fcu, o3 = (q & 1) ? (wb >> 22) & 0x3fcu : (wb >> 6) & 0x3fcu;
-                            const float s0 = *(const float*)((const char*)lut + o0), s1 = *(const float*)((const char*)lut + o1);
-                            const float s2 = *(const float*)((const char*)lut_b + o2), s3 = *(const float*)((const char*)lut_b + o3);
-#pragma unroll
-                            for (int ps = 0; ps < NP; ps++) {
-                                const uint4 xv = *(const uint4*)(smem + xq_lane[q] + c * cstep + ps * pstep + j * 2048);
-                                float cc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                                mma16816(cc, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
-                                mma16816(cc, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
-                                const float xi = xip[(ps * 4 + mrow) * bpr + 16 * j + (q >> 1)];
-                                pk0[ps][q] = fmaf(fmaf(cc[1], s1, cc[0] * s0), xi, pk0[ps][q]);
-                                pk1[ps][q] = fmaf(fmaf(cc[3], s3, cc[2] * s2), xi, pk1[ps][q]);
-                            }
+                        for (int ps = 0; ps < NP; ps++) {
+                            const uint4 xv = *(const uint4*)(smem + xq_lane[q] + c * cstep + ps * pstep + j * 2048);
+                            float cc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            mma16816(cc, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+                            mma16816(cc, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+                            const float xi = xip[(ps * 4 + mrow) * bpr + 16 * j + (q >> 1)];
+                            pk0[ps][q] = fmaf(fmaf(cc[1], s1, cc[0] * s0), xi, pk0[ps][q]);
+                            pk1[ps][q] = fmaf(fmaf(cc[3], s3, cc[2] * s2), xi, pk1[ps][q]);
                         }
                     }
+                };
+                if (ng == TX / 2) {
+#pragma unroll
+                    for (int j = 0; j < GPW; j++) group(j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < GPW; j++)
+                        if (warp + NW * j < ng) group(j);
                 }
             }
             __syncwarp();
