@@ -15,36 +15,58 @@
 
 namespace {
 
-// order[] = combos sorted by expert id (negative ids last); one CTA, counting sort in shared memory
+// order[] = combos sorted by expert id (negative ids last); one CTA of 1024 threads, counting sort in shared memory
 __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ order, int n, int E) {
-    extern __shared__ int cnt[];  // [E + 2]
-    for (int i = threadIdx.x; i <= E + 1; i += blockDim.x) cnt[i] = 0;
+    extern __shared__ int cnt[];  // [E + 2] counts, then start offsets; [n] the combos' bins
+    int* bin = cnt + E + 2;
+    __shared__ int wsum[32];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    for (int i = tid; i <= E + 1; i += blockDim.x) cnt[i] = 0;
     __syncthreads();
-    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    for (int c = tid; c < n; c += blockDim.x) {
         const int e = ids[c];
-        atomicAdd(&cnt[(e < 0 || e >= E) ? E : e], 1);
+        const int b = (e < 0 || e >= E) ? E : e;
+        bin[c] = b;
+        atomicAdd(&cnt[b], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int i = 0; i <= E; i++) {
-            const int c = cnt[i];
-            cnt[i] = run;
-            run += c;
+    // exclusive prefix sum over the E + 1 bins: every thread takes a contiguous run, the runs' totals are scanned
+    // with warp shuffles
+    const int per = (E + 1 + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int i0 = tid * per, i1 = min(i0 + per, E + 1);
+    int mine = 0;
+    for (int i = i0; i < i1; i++) mine += cnt[i];
+    int inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+    }
+    if (lane == 31) wsum[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        int w = wsum[lane], winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += v;
         }
+        wsum[lane] = winc - w;  // exclusive
+    }
+    __syncthreads();
+    int run = wsum[wid] + inc - mine;
+    for (int i = i0; i < i1; i++) {
+        const int c = cnt[i];
+        cnt[i] = run;
+        run += c;
     }
     __syncthreads();
     // stable within an expert: each combo counts the earlier combos of its expert (n is small)
-    for (int c = threadIdx.x; c < n; c += blockDim.x) {
-        int e = ids[c];
-        e = (e < 0 || e >= E) ? E : e;
+    for (int c = tid; c < n; c += blockDim.x) {
+        const int b = bin[c];
         int before = 0;
-        for (int d = 0; d < c; d++) {
-            int f = ids[d];
-            f = (f < 0 || f >= E) ? E : f;
-            before += f == e;
-        }
-        order[cnt[e] + before] = c;
+        for (int d = 0; d < c; d++) before += bin[d] == b;
+        order[cnt[b] + before] = c;
     }
 }
 
@@ -86,7 +108,9 @@ struct MoePlan {
 
 extern "C" int cn_moe_sort(const int32_t* ids, int32_t* order, int combos, int experts, cn_stream_t stream) {
     if (combos < 1 || experts < 1 || experts > 8192) CN_FAIL(CN_ERR_SHAPE, "cn_moe_sort: %d combos over %d experts", combos, experts);
-    moe_sort_kernel<<<1, 1024, (experts + 2) * sizeof(int), (cudaStream_t)stream>>>(ids, order, combos, experts);
+    const size_t smem = (size_t)(experts + 2 + combos) * sizeof(int);
+    if (smem > 48 * 1024) CN_FAIL(CN_ERR_LIMIT, "cn_moe_sort: %d combos over %d experts need %zu B of shared memory", combos, experts, smem);
+    moe_sort_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>(ids, order, combos, experts);
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }

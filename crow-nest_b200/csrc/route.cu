@@ -7,8 +7,9 @@
 // host twin glm5_moe::route_from_logits, engine/src/glm5_moe.rs:196-236).
 //
 // One CTA per token row, one thread per expert slot (P = next power of two >= E, <= 1024).
-// Reductions are the pairwise shared-memory trees of the reference kernel (stride P/2, P/4, ..),
-// so sums round exactly as there. exp() is taken in f64 and rounded once, which gives the
+// The softmax sum is the pairwise tree of the reference kernel (stride P/2, P/4, ..), so it rounds
+// exactly as there; maxima and index minima do not depend on the order and are taken with warp
+// shuffles (two barriers per selection round). exp() is taken in f64 and rounded once, which gives the
 // correctly rounded f32 value the host twins' libm returns; selection is K rounds of "best value,
 // lowest index on ties", as in both reference routers.
 #include "common.cuh"
@@ -17,74 +18,97 @@ namespace {
 
 __device__ __forceinline__ float exp_rn(float x) { return (float)exp((double)x); }
 
-// red[0] = max or sum over red[0..P) by the stride-halving tree; every thread calls it
-template <bool MAX>
-__device__ __forceinline__ float tree(float* red, int e, int P) {
-    for (int st = P >> 1; st > 0; st >>= 1) {
-        __syncthreads();
-        if (e < st) red[e] = MAX ? fmaxf(red[e], red[e + st]) : red[e] + red[e + st];
-    }
+// max over the block's values (NaN operands are ignored, as fmaxf does in the reference's tree; the value does
+// not depend on the order). buf: 32 floats; one barrier, the next use of `buf` must be a barrier later.
+__device__ __forceinline__ float block_max(float v, float* buf, int e, int P) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((e & 31) == 0) buf[e >> 5] = v;
     __syncthreads();
-    const float r = red[0];
+    float r = (e & 31) < (P >> 5) ? buf[e & 31] : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
+    return r;
+}
+__device__ __forceinline__ int block_min(int v, int* buf, int e, int P) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((e & 31) == 0) buf[e >> 5] = v;
     __syncthreads();
+    int r = (e & 31) < (P >> 5) ? buf[e & 31] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r = min(r, __shfl_xor_sync(0xffffffffu, r, o));
     return r;
 }
 
-// K rounds of argmax over score[] with ties to the lowest index; picks -> s_ids, returns nothing.
-// `score` is private per thread (slot e), retired slots become -inf-like sentinels (`gone`).
-__device__ __forceinline__ int pick_best(float* red, int* s_pick, float mine, bool alive, int e, int P, int E) {
-    red[e] = alive ? mine : -INFINITY;
-    const float best = tree<true>(red, e, P);
-    if (e == 0) *s_pick = E;
+// One round of "best value, lowest index on ties" over the live slots: the best value, then the lowest slot that
+// holds it (E when no live slot compares equal, i.e. a row of NaN). Two barriers; bmax / bmin: 32 words each.
+__device__ __forceinline__ int pick_best(float* bmax, int* bmin, float mine, bool alive, int e, int P, int E) {
+    const float best = block_max(alive ? mine : -INFINITY, bmax, e, P);
+    return block_min((alive && mine == best) ? e : E, bmin, e, P);
+}
+
+// red[0..P) summed by the reference's stride-halving tree (red[e] += red[e + st], st = P/2, P/4, ..): strides of 32
+// and more through shared memory, the last five inside warp 0 with the same pairs; every thread gets the sum
+__device__ __forceinline__ float tree_sum(float* red, float* out, int e, int P) {
+    for (int st = P >> 1; st >= 32; st >>= 1) {
+        __syncthreads();
+        if (e < st) red[e] = red[e] + red[e + st];
+    }
     __syncthreads();
-    if (alive && mine == best) atomicMin(s_pick, e);
+    if (e < 32) {
+        float v = red[e];
+#pragma unroll
+        for (int st = 16; st > 0; st >>= 1) {
+            const float o = __shfl_down_sync(0xffffffffu, v, st);
+            if (e < st) v = v + o;
+        }
+        if (e == 0) *out = v;
+    }
     __syncthreads();
-    int pick = *s_pick;
-    __syncthreads();
-    return pick;
+    return *out;
 }
 
 __global__ void route_softmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids, float* __restrict__ wts, int E, int K) {
     extern __shared__ float sm[];
-    float* red = sm;           // [P]
+    float* red = sm;               // [P]
     float* s_w = sm + blockDim.x;  // [K]
-    __shared__ int s_pick;
+    __shared__ float bmax[32];
+    __shared__ int bmin[32];
+    __shared__ float s_den;
     const int P = blockDim.x, e = threadIdx.x, t = blockIdx.x;
     const bool in = e < E;
     const float l = in ? logits[(size_t)t * E + e] : -INFINITY;
     // missing leaves of a non-power-of-two E are absent from the trees: -inf for max, 0 for sum
-    red[e] = l;
-    const float mx = tree<true>(red, e, P);
+    const float mx = block_max(l, bmax, e, P);
     const float ex = in ? exp_rn(l - mx) : 0.0f;
     red[e] = ex;
-    const float den = tree<false>(red, e, P);
+    const float den = tree_sum(red, &s_den, e, P);
     float p = in ? ex / den : -1.0f;
     bool alive = in;
-    float sum = 0.0f;  // kept by thread 0 in pick order
     for (int j = 0; j < K; j++) {
-        int pick = pick_best(red, &s_pick, p, alive, e, P, E);
+        int pick = pick_best(bmax, bmin, p, alive, e, P, E);
         if (pick >= E) pick = 0;  // a row of NaN: keep indices valid
         if (e == pick) {
             s_w[j] = p;
             alive = false;
-        }
-        __syncthreads();
-        if (e == 0) {
-            sum += s_w[j];
             ids[(size_t)t * K + j] = pick;
         }
     }
     __syncthreads();
-    if (e == 0)
+    if (e == 0) {
+        float sum = 0.0f;  // in pick order
+        for (int j = 0; j < K; j++) sum += s_w[j];
         for (int j = 0; j < K; j++) wts[(size_t)t * K + j] = s_w[j] / sum;
+    }
 }
 
 __global__ void route_sigmoid_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int32_t* __restrict__ ids,
                                      float* __restrict__ wts, int E, int K, float scale) {
     extern __shared__ float sm[];
-    float* red = sm;
     float* s_w = sm + blockDim.x;
-    __shared__ int s_pick;
+    __shared__ float bmax[32];
+    __shared__ int bmin[32];
     const int P = blockDim.x, e = threadIdx.x, t = blockIdx.x;
     const bool in = e < E;
     float s = 0.0f, c = -INFINITY;
@@ -95,14 +119,13 @@ __global__ void route_sigmoid_kernel(const float* __restrict__ logits, const flo
     }
     bool alive = in;
     for (int j = 0; j < K; j++) {
-        int pick = pick_best(red, &s_pick, c, alive, e, P, E);
+        int pick = pick_best(bmax, bmin, c, alive, e, P, E);
         if (pick >= E) pick = 0;
         if (e == pick) {
             s_w[j] = s;
             alive = false;
+            ids[(size_t)t * K + j] = pick;
         }
-        __syncthreads();
-        if (e == 0) ids[(size_t)t * K + j] = pick;
     }
     __syncthreads();
     if (e == 0) {
