@@ -77,14 +77,32 @@ template <int YT>
 __global__ void moe_combine_kernel(const float* __restrict__ eo, const float* __restrict__ wts, const int32_t* __restrict__ ids,
                                    const unsigned long long* __restrict__ tab, const float* __restrict__ shared,
                                    const float* __restrict__ sgate, void* __restrict__ y, int H, int K) {
+    // the token's K weights and "has a local matrix" flags once per CTA, so that the K loads of a column do not
+    // wait on an id -> table -> value chain each
+    constexpr int KC = 16;
+    __shared__ float s_w[KC];
+    __shared__ int s_ok[KC];
     const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
-    if (c >= H) return;
     float acc = 0.0f;
-    for (int j = 0; j < K; j++) {
-        const int e = ids[t * K + j];
-        if (e < 0 || (tab && tab[e] == 0ull)) continue;
-        acc = __fadd_rn(acc, __fmul_rn(wts[t * K + j], eo[((size_t)t * K + j) * H + c]));
+    for (int j0 = 0; j0 < K; j0 += KC) {
+        const int kc = min(KC, K - j0);
+        if (j0 > 0) __syncthreads();
+        if ((int)threadIdx.x < kc) {
+            const int e = ids[t * K + j0 + threadIdx.x];
+            s_ok[threadIdx.x] = !(e < 0 || (tab && tab[e] == 0ull));
+            s_w[threadIdx.x] = wts[t * K + j0 + threadIdx.x];
+        }
+        __syncthreads();
+        if (c < H) {
+            float v[KC];
+#pragma unroll
+            for (int j = 0; j < KC; j++) v[j] = (j < kc && s_ok[j]) ? eo[((size_t)t * K + j0 + j) * H + c] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < KC; j++)
+                if (j < kc && s_ok[j]) acc = __fadd_rn(acc, __fmul_rn(s_w[j], v[j]));
+        }
     }
+    if (c >= H) return;
     float base = shared ? shared[(size_t)t * H + c] : 0.0f;
     if (shared && sgate) base = __fmul_rn(1.0f / (1.0f + expf(-sgate[t])), base);
     const float v = __fadd_rn(base, acc);
