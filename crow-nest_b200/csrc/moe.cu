@@ -120,6 +120,10 @@ struct MoePlan {
     float* ys;       // [max_tokens][hidden]
     int32_t* order;  // [max_tokens * topk]
     int shared_inter;
+    // the shared expert does not depend on the routed experts until the combine: it is enqueued on a side stream
+    // between two events (fork after the caller's earlier work, join before the combine), also under stream capture
+    cudaStream_t side;
+    cudaEvent_t fork, join;
 };
 
 }  // namespace
@@ -157,6 +161,9 @@ extern "C" int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, 
     CN_CUDA(cudaMalloc(&p->hs, (size_t)max_tokens * (shared_inter > 0 ? shared_inter : 1) * sizeof(float)));
     CN_CUDA(cudaMalloc(&p->ys, (size_t)max_tokens * hidden * sizeof(float)));
     CN_CUDA(cudaMalloc(&p->order, combos * sizeof(int32_t)));
+    CN_CUDA(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
+    CN_CUDA(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
+    CN_CUDA(cudaEventCreateWithFlags(&p->join, cudaEventDisableTiming));
     *plan_out = p;
     return CN_OK;
 }
@@ -165,6 +172,9 @@ extern "C" int cn_moe_nvfp4_plan_destroy(void* plan) {
     MoePlan* p = (MoePlan*)plan;
     if (!p) return CN_OK;
     cudaFree(p->h), cudaFree(p->eo), cudaFree(p->hs), cudaFree(p->ys), cudaFree(p->order);
+    if (p->side) cudaStreamDestroy(p->side);
+    if (p->fork) cudaEventDestroy(p->fork);
+    if (p->join) cudaEventDestroy(p->join);
     delete p;
     return CN_OK;
 }
@@ -182,35 +192,47 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
     const int ydtype = dtype == CN_BF16 ? CN_BF16 : CN_F32;  // expert-parallel partial sums leave in f32
     if (dtype == CN_BF16_IN_F32_OUT) dtype = CN_BF16;
     const int combos = tokens * p->topk;
-    if (int rc = cn_moe_sort(ids, p->order, combos, p->experts, stream_)) return rc;
-    // routed gate|up + activation: h[c] = act(gate_e x_t, up_e x_t), c = t * topk + j
-    GemvCall a = {};
-    a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
-    a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = p->order, a.tab0 = table_gu, a.tab1 = table_up;
-    a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = p->topk, a.combos = combos;
-    if (int rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4_run (gate/up)")) return rc;
-    // routed down: eo[c] = down_e h[c]
-    GemvCall d = {};
-    d.gs0 = gs_dn, d.x = p->h, d.y = p->eo, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
-    d.x_f16_ok = 0, d.ids = ids, d.order = p->order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
-    if (int rc = cn_gemv_launch(d, stream, "cn_moe_nvfp4_run (down)")) return rc;
-    // shared expert on every token, up to 8 rows per pass
+    // shared expert on every token, up to 8 rows per pass, on the side stream; whatever happens after the fork,
+    // the side stream is joined again before this call returns (a capture of the caller's stream stays valid)
     const float* shared = nullptr;
+    int rc = CN_OK;
     if (shared_gate) {
+        CN_CUDA(cudaEventRecord(p->fork, stream));
+        CN_CUDA(cudaStreamWaitEvent(p->side, p->fork, 0));
         const size_t es = dtype == CN_BF16 ? 2 : 4;
-        for (int t0 = 0; t0 < tokens; t0 += CN_MAX_M) {
+        for (int t0 = 0; t0 < tokens && rc == CN_OK; t0 += CN_MAX_M) {
             const int m = tokens - t0 < CN_MAX_M ? tokens - t0 : CN_MAX_M;
             GemvCall g = {};
             g.w0 = shared_gate, g.w1 = shared_up, g.gs0 = shared_gs, g.gs1 = shared_gs + 1, g.x = (const char*)x + (size_t)t0 * p->hidden * es;
             g.y = p->hs + (size_t)t0 * p->shared_inter, g.rows = p->shared_inter, g.k = p->hidden, g.m = m, g.ldy = p->shared_inter;
             g.limit = limit, g.dtype = dtype, g.out_f32 = 1;
-            if (int rc = cn_gemv_launch(g, stream, "cn_moe_nvfp4_run (shared gate/up)")) return rc;
+            rc = cn_gemv_launch(g, p->side, "cn_moe_nvfp4_run (shared gate/up)");
+            if (rc != CN_OK) break;
             GemvCall s = {};
             s.w0 = shared_down, s.gs0 = shared_gs + 2, s.x = p->hs + (size_t)t0 * p->shared_inter, s.y = p->ys + (size_t)t0 * p->hidden;
             s.rows = p->hidden, s.k = p->shared_inter, s.m = m, s.ldy = p->hidden, s.dtype = CN_F32, s.out_f32 = 1, s.x_f16_ok = 0;
-            if (int rc = cn_gemv_launch(s, stream, "cn_moe_nvfp4_run (shared down)")) return rc;
+            rc = cn_gemv_launch(s, p->side, "cn_moe_nvfp4_run (shared down)");
         }
+        CN_CUDA(cudaEventRecord(p->join, p->side));
         shared = p->ys;
     }
+    if (rc == CN_OK) rc = cn_moe_sort(ids, p->order, combos, p->experts, stream_);
+    if (rc == CN_OK) {
+        // routed gate|up + activation: h[c] = act(gate_e x_t, up_e x_t), c = t * topk + j
+        GemvCall a = {};
+        a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
+        a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = p->order, a.tab0 = table_gu, a.tab1 = table_up;
+        a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = p->topk, a.combos = combos;
+        rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4_run (gate/up)");
+    }
+    if (rc == CN_OK) {
+        // routed down: eo[c] = down_e h[c]
+        GemvCall d = {};
+        d.gs0 = gs_dn, d.x = p->h, d.y = p->eo, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
+        d.x_f16_ok = 0, d.ids = ids, d.order = p->order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
+        rc = cn_gemv_launch(d, stream, "cn_moe_nvfp4_run (down)");
+    }
+    if (shared) CN_CUDA(cudaStreamWaitEvent(stream, p->join, 0));
+    if (rc != CN_OK) return rc;
     return cn_moe_combine(p->eo, wts, ids, table_dn, shared, sgate, y, tokens, p->hidden, p->topk, ydtype, stream_);
 }
