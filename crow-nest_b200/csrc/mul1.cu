@@ -403,6 +403,9 @@ struct Mul1Plan {
     float *part_a, *part_b;  // [slots][16][T][kmax]
     unsigned long long* ptrs;  // [slots] gathered record addresses (MoE form)
     float* eo;                 // [slots][T][hidden] expert outputs (MoE form)
+    // the up projection does not depend on the gate projection: it runs on a side stream between two events
+    cudaStream_t side;
+    cudaEvent_t fork, join;
 };
 
 int ksplit(int k) {
@@ -507,6 +510,9 @@ extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int b
     CN_CUDA(cudaMalloc(&p->part_b, rows * 16 * p->kmax * 4));
     CN_CUDA(cudaMalloc(&p->ptrs, (size_t)max_slots * 8));
     CN_CUDA(cudaMalloc(&p->eo, rows * hidden * 4));
+    CN_CUDA(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
+    CN_CUDA(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
+    CN_CUDA(cudaEventCreateWithFlags(&p->join, cudaEventDisableTiming));
     *plan_out = p;
     return CN_OK;
 }
@@ -516,6 +522,9 @@ extern "C" int cn_mul1_plan_destroy(void* plan) {
     if (!p) return CN_OK;
     cudaFree(p->xh_a), cudaFree(p->xh_b), cudaFree(p->xinv_a), cudaFree(p->xinv_b), cudaFree(p->part_a), cudaFree(p->part_b), cudaFree(p->ptrs),
         cudaFree(p->eo);
+    if (p->side) cudaStreamDestroy(p->side);
+    if (p->fork) cudaEventDestroy(p->fork);
+    if (p->join) cudaEventDestroy(p->join);
     delete p;
     return CN_OK;
 }
@@ -542,10 +551,16 @@ extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptr
 static int mul1_ffn(Mul1Plan* p, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, float limit, int dtype,
                     int out_f32, cudaStream_t st) {
     const Mul1Spec g = spec_of(p, 0), u = spec_of(p, 1), d = spec_of(p, 2);
-    if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, p->plane, st)) return rc;
-    if (int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, p->plane, st)) return rc;
-    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, p->plane, st)) return rc;
-    if (int rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, p->plane, st)) return rc;
+    // up branch on the side stream; it is joined again on every path, so a capture of `st` stays valid
+    CN_CUDA(cudaEventRecord(p->fork, st));
+    CN_CUDA(cudaStreamWaitEvent(p->side, p->fork, 0));
+    int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, p->plane, p->side);
+    if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, p->plane, p->side);
+    CN_CUDA(cudaEventRecord(p->join, p->side));
+    if (rc == CN_OK) rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, p->plane, st);
+    if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, p->plane, st);
+    CN_CUDA(cudaStreamWaitEvent(st, p->join, 0));
+    if (rc != CN_OK) return rc;
     CN_CUDA(cn_launch_pdl(mul1_act_had_in_kernel, dim3(p->inter / 128, t, slots), dim3(32), 0, st, ptrs, p->part_a, p->part_b, p->xh_a, p->xinv_a, p->inter, ksplit(p->hidden), t,
                                                                          g.svh_off, u.svh_off, d.suh_off, limit, p->plane));
     CN_CUDA(cudaGetLastError());
