@@ -216,12 +216,18 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
         CN_CUDA(cudaEventRecord(p->join, p->side));
         shared = p->ys;
     }
-    if (rc == CN_OK) rc = cn_moe_sort(ids, p->order, combos, p->experts, stream_);
+    // Combos sorted by expert keep the CTAs that read one expert's matrices next to each other in launch order. With
+    // few combos every CTA of the step is resident at once and L2 serves a second reader anyway: no sort, one launch less.
+    const int32_t* order = nullptr;
+    if (combos > 128) {
+        if (rc == CN_OK) rc = cn_moe_sort(ids, p->order, combos, p->experts, stream_);
+        order = p->order;
+    }
     if (rc == CN_OK) {
         // routed gate|up + activation: h[c] = act(gate_e x_t, up_e x_t), c = t * topk + j
         GemvCall a = {};
         a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
-        a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = p->order, a.tab0 = table_gu, a.tab1 = table_up;
+        a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = order, a.tab0 = table_gu, a.tab1 = table_up;
         a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = p->topk, a.combos = combos;
         rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4_run (gate/up)");
     }
@@ -229,7 +235,7 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
         // routed down: eo[c] = down_e h[c]
         GemvCall d = {};
         d.gs0 = gs_dn, d.x = p->h, d.y = p->eo, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
-        d.x_f16_ok = 0, d.ids = ids, d.order = p->order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
+        d.x_f16_ok = 0, d.ids = ids, d.order = order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
         rc = cn_gemv_launch(d, stream, "cn_moe_nvfp4_run (down)");
     }
     if (shared) CN_CUDA(cudaStreamWaitEvent(stream, p->join, 0));

@@ -115,7 +115,11 @@ int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const 
 
 /* The routed-expert decode step, GpuMoePlan-shaped (engine/src/glm5_moe.rs:518-793; Flash-Next call
  * site Engine::moe_run, engine/src/gen.rs:4168-4532). The plan owns the scratch (the only
- * allocation; run() allocates nothing and does not synchronise).
+ * allocation; run() allocates nothing and does not synchronise). The plan also owns one side stream
+ * and two events: run() enqueues the shared expert there between a fork event recorded on `stream`
+ * and a join event `stream` waits for before the combine, so everything is ordered with the caller's
+ * stream as if it ran on it (a capture of `stream` takes the side branch in). cn_mul1_ffn and
+ * cn_moe_mul1_run do the same with the up projection.
  * Tables are device arrays [experts] of device addresses (0 = expert not resident: its combos are
  * skipped, the contract of engine/src/kernels_mul1.cu:118-119): table_gu = gate [inter][hidden], or
  * the fused gate|up slab [2*inter][hidden] when table_up == null; table_dn = down [hidden][inter].
