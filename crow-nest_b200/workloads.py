@@ -59,6 +59,7 @@ class MoeDecode:
             self.own = torch.empty((tokens, hidden), dtype=torch.float32, device=device)
             self.hs = torch.empty((tokens, shared_inter), dtype=torch.bfloat16, device=device)
             self.ys = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device)
+            self.side = torch.cuda.Stream(device=device)  # the shared expert runs beside dispatch, experts and combine
         self.launches_per_step = 5 + 2 * ((tokens + 7) // 8)  # router, sort, gate/up, down, combine, shared gate/up + down per 8 rows
 
     def step(self):
@@ -66,18 +67,22 @@ class MoeDecode:
         if self.world == 1:
             return self.plan.run(self.w, self.logits, self.x, self.y)
         import torch.distributed as dist
+        # shared expert on the rank's own rows, 8 at a time (the kernels take up to 8 activation rows): it needs x only,
+        # so it goes on a side stream that forks here and joins before the final sum (also under graph capture)
+        cur = torch.cuda.current_stream()
+        self.side.wait_stream(cur)
+        with torch.cuda.stream(self.side):
+            for t0 in range(0, self.tokens, 8):
+                t1 = min(t0 + 8, self.tokens)
+                ops.launch_gemv_gu(self.shared_fp4[0], self.shared_fp4[1], self.x[t0:t1], self.hs[t0:t1])
+                ops.launch_gemv(self.shared_fp4[2], self.hs[t0:t1], self.ys[t0:t1])
         dist.all_gather_into_tensor(self.x_all, self.x, group=self.group)
         dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.group)
         ids, wts = moe.route_softmax_topk(self.logits_all, self.topk)
         self.plan.experts_run(self.w, ids, wts, self.x_all, self.part, partial=True)
         dist.reduce_scatter_tensor(self.own, self.part, op=dist.ReduceOp.SUM, group=self.group)
-        # shared expert on the rank's own rows, 8 at a time (the kernels take up to 8 activation rows)
-        for t0 in range(0, self.tokens, 8):
-            t1 = min(t0 + 8, self.tokens)
-            ops.launch_gemv_gu(self.shared_fp4[0], self.shared_fp4[1], self.x[t0:t1], self.hs[t0:t1])
-            ops.launch_gemv(self.shared_fp4[2], self.hs[t0:t1], self.ys[t0:t1])
-        torch.add(self.own, self.ys, out=self.own)
-        self.y.copy_(self.own)
+        cur.wait_stream(self.side)
+        torch.add(self.own, self.ys, out=self.y)  # f32 sum, rounded to bf16 once
         return self.y
 
     def bytes_per_step(self, ids=None):
