@@ -538,7 +538,16 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     if (routed && (long long)ntiles * a.combos > 3LL * 148 * cps / 2) {
         // many combos: a few persistent CTAs per combo (the activation row is staged once per CTA), about one wave in all
         grid = 148 * cps / a.combos;
-        if (grid < 1) grid = 1;
+        if (grid < 1) {
+            // more combos than CTA slots: 1..4 CTAs per combo, whichever fills the last wave best (fewer on a near tie)
+            const double slots = 148.0 * cps;
+            double best = 0.0;
+            for (int gx = 1; gx <= 4 && gx <= ntiles; gx++) {
+                const double waves = gx * (double)a.combos / slots, eff = waves / (double)(long long)(waves + 0.999999);
+                if (eff > best + 0.03) best = eff, grid = gx;
+            }
+            if (grid < 1) grid = 1;
+        }
         grid = (ntiles + ((ntiles + grid - 1) / grid) - 1) / ((ntiles + grid - 1) / grid);  // the same tiles per CTA, fewer CTAs
     }
     // When the tiles do not fill the last wave, pairs of CTAs (a cluster of two) share every tile, each over half of
