@@ -538,11 +538,11 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     if (routed && (long long)ntiles * a.combos > 3LL * 148 * cps / 2) {
         // many combos: a few persistent CTAs per combo (the activation row is staged once per CTA), about one wave in all
         grid = 148 * cps / a.combos;
-        if (grid < 1) {
-            // more combos than CTA slots: 1..4 CTAs per combo, whichever fills the last wave best (fewer on a near tie)
+        if (grid <= 2) {
+            // combos near or beyond the CTA slots: 1..6 CTAs per combo, whichever fills the last wave best (fewer on a near tie)
             const double slots = 148.0 * cps;
             double best = 0.0;
-            for (int gx = 1; gx <= 4 && gx <= ntiles; gx++) {
+            for (int gx = 1; gx <= 6 && gx <= ntiles; gx++) {
                 const double waves = gx * (double)a.combos / slots, eff = waves / (double)(long long)(waves + 0.999999);
                 if (eff > best + 0.03) best = eff, grid = gx;
             }
