@@ -42,7 +42,7 @@ _SIGS = {
     "cn_route_softmax_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "cn_route_sigmoid_topk": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cn_moe_sort": [_vp, _vp, _i, _i, _vp],
-    "cn_moe_combine": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "cn_moe_combine": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cn_moe_nvfp4_plan_create": [C.POINTER(C.c_void_p), _i, _i, _i, _i, _i, _i],
     "cn_moe_nvfp4_plan_destroy": [_vp],
     "cn_moe_nvfp4_run": [_vp] * 16 + [_i, _f, _i, _vp],
@@ -56,16 +56,15 @@ _SIGS = {
     "cn_mul1_plan_destroy": [_vp],
     "cn_mul1_gemv": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cn_mul1_ffn": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
-    "cn_moe_mul1_run": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp],
+    "cn_moe_mul1_run": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "cn_mul1_gemv_noalloc": [_i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cn_mul1_reconstruct": [_vp, _vp, _i, _i, _i, _i, _vp],
     "cn_fp8_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cn_device_status": [C.POINTER(C.c_int)],
-    "cn_set_tuning": [_i, _i],
     "cn_last_error_string": [],
     "cn_version": [],
 }
-_RESTYPES = {"cn_last_error_string": C.c_char_p, "cn_version": C.c_char_p, "cn_set_tuning": None}
+_RESTYPES = {"cn_last_error_string": C.c_char_p, "cn_version": C.c_char_p}
 
 
 def exported_symbols():

@@ -2,6 +2,9 @@
 // version string.
 #include <cstdarg>
 #include <cstdio>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -14,6 +17,20 @@ void cn_set_error(const char* fmt, ...) {
     va_start(ap, fmt);
     vsnprintf(t_err, sizeof t_err, fmt, ap);
     va_end(ap);
+}
+
+cudaError_t cn_allow_smem(const void* kernel, int bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, int> done;  // (kernel, device) -> largest size allowed so far
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    int& have = done[std::make_pair(kernel, dev)];
+    if (have >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) have = bytes;
+    return e;
 }
 
 extern "C" const char* cn_last_error_string(void) { return t_err; }

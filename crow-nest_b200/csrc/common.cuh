@@ -21,6 +21,11 @@ void cn_set_error(const char* fmt, ...);
         if (e__ != cudaSuccess) CN_FAIL(CN_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
     } while (0)
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only: remembered per (kernel, device),
+// so that a process that drives several GPUs raises the limit on each of them (capi.cu).
+cudaError_t cn_allow_smem(const void* kernel, int bytes);
+#define CN_ALLOW_SMEM(kern, bytes) CN_CUDA(cn_allow_smem((const void*)(kern), (bytes)))
+
 // ---------------------------------------------------------------- device: status word
 // A wait that runs out of its iteration budget stores a code here (first writer wins) and the
 // kernel returns; nothing traps and nothing spins without a limit.

@@ -125,11 +125,7 @@ int launch(const void* w, const float* scale, const void* x, void* y, int rows, 
     if (grid > 148 * 8) grid = 148 * 8;
 #define CN_FP8_CASE(MPV)                                                                                                  \
     if (mp == MPV) {                                                                                                      \
-        static bool attr = false;                                                                                         \
-        if (!attr) {                                                                                                      \
-            CN_CUDA(cudaFuncSetAttribute(fp8_gemv_kernel<XT, MPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
-            attr = true;                                                                                                  \
-        }                                                                                                                 \
+        CN_ALLOW_SMEM((fp8_gemv_kernel<XT, MPV>), 200 * 1024);                                                            \
         fp8_gemv_kernel<XT, MPV><<<grid, WARPS * 32, smem, st>>>((const uint8_t*)w, scale, x, y, rows, cols, m, ldy);    \
     }
     CN_FP8_CASE(1) CN_FP8_CASE(2) CN_FP8_CASE(4) CN_FP8_CASE(8)

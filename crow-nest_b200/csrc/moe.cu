@@ -76,7 +76,7 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int32_t* __rest
 template <int YT>
 __global__ void moe_combine_kernel(const float* __restrict__ eo, const float* __restrict__ wts, const int32_t* __restrict__ ids,
                                    const unsigned long long* __restrict__ tab, const float* __restrict__ shared,
-                                   const float* __restrict__ sgate, void* __restrict__ y, int H, int K) {
+                                   const float* __restrict__ sgate, void* __restrict__ y, int H, int K, int E) {
     // the token's K weights and "has a local matrix" flags once per CTA, so that the K loads of a column do not
     // wait on an id -> table -> value chain each
     constexpr int KC = 16;
@@ -89,7 +89,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ eo, const float* __
         if (j0 > 0) __syncthreads();
         if ((int)threadIdx.x < kc) {
             const int e = ids[t * K + j0 + threadIdx.x];
-            s_ok[threadIdx.x] = !(e < 0 || (tab && tab[e] == 0ull));
+            s_ok[threadIdx.x] = !(e < 0 || (E > 0 && e >= E) || (tab && tab[e] == 0ull));
             s_w[threadIdx.x] = wts[t * K + j0 + threadIdx.x];
         }
         __syncthreads();
@@ -138,16 +138,19 @@ extern "C" int cn_moe_sort(const int32_t* ids, int32_t* order, int combos, int e
 }
 
 extern "C" int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const unsigned long long* table, const float* shared,
-                              const float* sgate, void* y, int tokens, int hidden, int topk, int dtype, cn_stream_t stream) {
+                              const float* sgate, void* y, int tokens, int hidden, int topk, int experts, int dtype, cn_stream_t stream) {
     if (tokens < 1 || hidden < 1 || topk < 1) CN_FAIL(CN_ERR_SHAPE, "cn_moe_combine: tokens %d hidden %d topk %d", tokens, hidden, topk);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_combine: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     dim3 grid((hidden + 255) / 256, tokens);
     if (dtype == CN_BF16)
-        moe_combine_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(eo, wts, ids, table, shared, sgate, y, hidden, topk);
+        moe_combine_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(eo, wts, ids, table, shared, sgate, y, hidden, topk, experts);
     else
-        moe_combine_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(eo, wts, ids, table, shared, sgate, y, hidden, topk);
+        moe_combine_kernel<0><<<grid, 256, 0, (cudaStream_t)stream>>>(eo, wts, ids, table, shared, sgate, y, hidden, topk, experts);
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
+
+extern "C" int cn_moe_nvfp4_plan_destroy(void* plan);
 
 extern "C" int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, int shared_inter, int experts, int topk, int max_tokens) {
     if (!plan_out || hidden % 256 || inter % 256 || shared_inter % 256 || experts < 1 || topk < 1 || max_tokens < 1)
@@ -156,14 +159,21 @@ extern "C" int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, 
     p->hidden = hidden, p->inter = inter, p->experts = experts, p->topk = topk, p->max_tokens = max_tokens, p->shared_inter = shared_inter;
     CN_CUDA(cudaGetDevice(&p->device));
     const size_t combos = (size_t)max_tokens * topk;
-    CN_CUDA(cudaMalloc(&p->h, combos * inter * sizeof(float)));
-    CN_CUDA(cudaMalloc(&p->eo, combos * hidden * sizeof(float)));
-    CN_CUDA(cudaMalloc(&p->hs, (size_t)max_tokens * (shared_inter > 0 ? shared_inter : 1) * sizeof(float)));
-    CN_CUDA(cudaMalloc(&p->ys, (size_t)max_tokens * hidden * sizeof(float)));
-    CN_CUDA(cudaMalloc(&p->order, combos * sizeof(int32_t)));
-    CN_CUDA(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
-    CN_CUDA(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
-    CN_CUDA(cudaEventCreateWithFlags(&p->join, cudaEventDisableTiming));
+    // a failure part-way frees what the earlier steps got (the destroy call takes a half-built plan)
+    cudaError_t e = cudaSuccess;
+    auto step = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+    step(cudaMalloc(&p->h, combos * inter * sizeof(float)));
+    step(cudaMalloc(&p->eo, combos * hidden * sizeof(float)));
+    step(cudaMalloc(&p->hs, (size_t)max_tokens * (shared_inter > 0 ? shared_inter : 1) * sizeof(float)));
+    step(cudaMalloc(&p->ys, (size_t)max_tokens * hidden * sizeof(float)));
+    step(cudaMalloc(&p->order, combos * sizeof(int32_t)));
+    step(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
+    step(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
+    step(cudaEventCreateWithFlags(&p->join, cudaEventDisableTiming));
+    if (e != cudaSuccess) {
+        cn_moe_nvfp4_plan_destroy(p);
+        CN_FAIL(CN_ERR_CUDA, "cn_moe_nvfp4_plan_create: %s", cudaGetErrorString(e));
+    }
     *plan_out = p;
     return CN_OK;
 }
@@ -230,17 +240,17 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
         GemvCall a = {};
         a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
         a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = order, a.tab0 = table_gu, a.tab1 = table_up;
-        a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = p->topk, a.combos = combos;
+        a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = p->topk, a.combos = combos, a.experts = p->experts;
         rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4_run (gate/up)");
     }
     if (rc == CN_OK) {
         // routed down: eo[c] = down_e h[c]
         GemvCall d = {};
         d.gs0 = gs_dn, d.x = p->h, d.y = p->eo, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
-        d.x_f16_ok = 0, d.ids = ids, d.order = order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos;
+        d.x_f16_ok = 0, d.ids = ids, d.order = order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos, d.experts = p->experts;
         rc = cn_gemv_launch(d, stream, "cn_moe_nvfp4_run (down)");
     }
     if (shared) CN_CUDA(cudaStreamWaitEvent(stream, p->join, 0));
     if (rc != CN_OK) return rc;
-    return cn_moe_combine(p->eo, wts, ids, table_dn, shared, sgate, y, tokens, p->hidden, p->topk, ydtype, stream_);
+    return cn_moe_combine(p->eo, wts, ids, table_dn, shared, sgate, y, tokens, p->hidden, p->topk, p->experts, ydtype, stream_);
 }

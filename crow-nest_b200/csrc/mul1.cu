@@ -462,11 +462,7 @@ int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float*
     const int mt = T == 1 ? 1 : (T == 2 ? 2 : (T <= 4 ? 4 : 8));
 #define CN_MUL1_CASE(K3V, MTV)                                                                                                      \
     if (k3 == K3V && mt == MTV) {                                                                                                   \
-        static bool attr = false;                                                                                                   \
-        if (!attr) {                                                                                                                \
-            CN_CUDA(cudaFuncSetAttribute(mul1_gemv_kernel<K3V, MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));     \
-            attr = true;                                                                                                            \
-        }                                                                                                                           \
+        CN_ALLOW_SMEM((mul1_gemv_kernel<K3V, MTV>), 160 * 1024);                                                                    \
         CN_CUDA(cn_launch_pdl((mul1_gemv_kernel<K3V, MTV>), grid, dim3(288), smem, st, ptrs, xh, xinv, part, s, S, T, plane, spc));        \
     }
     CN_MUL1_CASE(true, 1) CN_MUL1_CASE(true, 2) CN_MUL1_CASE(true, 4) CN_MUL1_CASE(true, 8)
@@ -483,14 +479,17 @@ int check_run(const Mul1Plan* p, int slots, int T, const char* who) {
     return CN_OK;
 }
 
-__global__ void mul1_gather_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ ids, unsigned long long* ptrs, int n) {
+__global__ void mul1_gather_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ ids, unsigned long long* ptrs, int n,
+                                   int experts) {
     pdl_launch_dependents();
     pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c < n) ptrs[c] = ids[c] < 0 ? 0ull : table[ids[c]];
+    if (c < n) ptrs[c] = (ids[c] < 0 || (experts > 0 && ids[c] >= experts)) ? 0ull : table[ids[c]];
 }
 
 }  // namespace
+
+extern "C" int cn_mul1_plan_destroy(void* plan);
 
 extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int bits, int half, int max_slots, int max_t) {
     if (!plan_out || hidden <= 0 || inter <= 0 || hidden % 128 || inter % 128)
@@ -502,17 +501,24 @@ extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int b
     p->kmax = hidden > inter ? hidden : inter;
     const size_t rows = (size_t)max_slots * max_t;
     p->plane = rows * p->kmax;
-    CN_CUDA(cudaMalloc(&p->xh_a, 2 * p->plane * 2));
-    CN_CUDA(cudaMalloc(&p->xh_b, 2 * p->plane * 2));
-    CN_CUDA(cudaMalloc(&p->xinv_a, rows * (p->kmax / 128) * 4));
-    CN_CUDA(cudaMalloc(&p->xinv_b, rows * (p->kmax / 128) * 4));
-    CN_CUDA(cudaMalloc(&p->part_a, rows * 16 * p->kmax * 4));
-    CN_CUDA(cudaMalloc(&p->part_b, rows * 16 * p->kmax * 4));
-    CN_CUDA(cudaMalloc(&p->ptrs, (size_t)max_slots * 8));
-    CN_CUDA(cudaMalloc(&p->eo, rows * hidden * 4));
-    CN_CUDA(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
-    CN_CUDA(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
-    CN_CUDA(cudaEventCreateWithFlags(&p->join, cudaEventDisableTiming));
+    // a failure part-way frees what the earlier steps got (the destroy call takes a half-built plan)
+    cudaError_t e = cudaSuccess;
+    auto step = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+    step(cudaMalloc(&p->xh_a, 2 * p->plane * 2));
+    step(cudaMalloc(&p->xh_b, 2 * p->plane * 2));
+    step(cudaMalloc(&p->xinv_a, rows * (p->kmax / 128) * 4));
+    step(cudaMalloc(&p->xinv_b, rows * (p->kmax / 128) * 4));
+    step(cudaMalloc(&p->part_a, rows * 16 * p->kmax * 4));
+    step(cudaMalloc(&p->part_b, rows * 16 * p->kmax * 4));
+    step(cudaMalloc(&p->ptrs, (size_t)max_slots * 8));
+    step(cudaMalloc(&p->eo, rows * hidden * 4));
+    step(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
+    step(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
+    step(cudaEventCreateWithFlags(&p->join, cudaEventDisableTiming));
+    if (e != cudaSuccess) {
+        cn_mul1_plan_destroy(p);
+        CN_FAIL(CN_ERR_CUDA, "cn_mul1_plan_create: %s", cudaGetErrorString(e));
+    }
     *plan_out = p;
     return CN_OK;
 }
@@ -534,6 +540,7 @@ extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptr
     Mul1Plan* p = (Mul1Plan*)plan;
     if (int rc = check_run(p, slots, t, "cn_mul1_gemv")) return rc;
     if (which < 0 || which > 2 || x_div < 1) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv: matrix %d (0 gate, 1 up, 2 down), x_div %d", which, x_div);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     cudaStream_t st = (cudaStream_t)stream;
     const Mul1Spec s = spec_of(p, which);
     if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, s, slots, t, x_div, dtype, p->plane, st)) return rc;
@@ -579,22 +586,24 @@ extern "C" int cn_mul1_ffn(void* plan, const unsigned long long* ptrs, const voi
     Mul1Plan* p = (Mul1Plan*)plan;
     if (int rc = check_run(p, slots, t, "cn_mul1_ffn")) return rc;
     if (x_div < 1) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_ffn: x_div %d", x_div);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_ffn: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     return mul1_ffn(p, ptrs, x, y, slots, t, x_div, limit, dtype, 0, (cudaStream_t)stream);
 }
 
 extern "C" int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const unsigned long long* table, const float* shared,
-                              const float* sgate, void* y, int tokens, int hidden, int topk, int dtype, cn_stream_t stream);
+                              const float* sgate, void* y, int tokens, int hidden, int topk, int experts, int dtype, cn_stream_t stream);
 
 extern "C" int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared, const void* x,
-                               void* y, int tokens, int topk, float limit, int dtype, cn_stream_t stream) {
+                               void* y, int tokens, int topk, int experts, float limit, int dtype, cn_stream_t stream) {
     Mul1Plan* p = (Mul1Plan*)plan;
     const int combos = tokens * topk;
     if (int rc = check_run(p, combos, 1, "cn_moe_mul1_run")) return rc;
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_run: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     cudaStream_t st = (cudaStream_t)stream;
-    CN_CUDA(cn_launch_pdl(mul1_gather_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->ptrs, combos));
+    CN_CUDA(cn_launch_pdl(mul1_gather_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->ptrs, combos, experts));
     CN_CUDA(cudaGetLastError());
     if (int rc = mul1_ffn(p, p->ptrs, x, p->eo, combos, 1, topk, limit, dtype, 1, st)) return rc;
-    return cn_moe_combine(p->eo, wts, ids, table, shared, nullptr, y, tokens, p->hidden, topk, dtype, stream);
+    return cn_moe_combine(p->eo, wts, ids, table, shared, nullptr, y, tokens, p->hidden, topk, experts, dtype, stream);
 }
 
 extern "C" int cn_mul1_reconstruct(const void* trellis, void* w_out, int k, int n, int bits, int half, cn_stream_t stream) {
@@ -658,6 +667,8 @@ extern "C" int cn_mul1_gemv_noalloc(int which, int hidden, int inter, int bits, 
         CN_FAIL(CN_ERR_LIMIT, "cn_mul1_gemv_noalloc: %d slots x %d rows; the fixed scratch holds %zu rows in all (use a plan for more)", slots, t, NA_ROWS);
     if ((size_t)hidden > NA_DIM || (size_t)inter > NA_DIM)
         CN_FAIL(CN_ERR_LIMIT, "cn_mul1_gemv_noalloc: hidden %d / inter %d beyond the fixed scratch's %zu (use a plan for more)", hidden, inter, NA_DIM);
+    // before the first launch: the kernels read x in this type
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv_noalloc: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     unsigned char* base = nullptr;
     if (int rc = static_scratch(&base)) return rc;
     Mul1Plan view = {};
@@ -675,10 +686,8 @@ extern "C" int cn_mul1_gemv_noalloc(int which, int hidden, int inter, int bits, 
     dim3 grid(s.n / 128, t, slots);
     if (dtype == CN_BF16)
         CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off));
-    else if (dtype == CN_F32)
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off));
     else
-        CN_FAIL(CN_ERR_SHAPE, "cn_mul1_gemv_noalloc: dtype %d is neither CN_F32 nor CN_BF16", dtype);
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }

@@ -373,12 +373,8 @@ extern "C" int cn_nvfp4_gemm(const void* w, const float* gs, const void* x, void
     else
         gemm_prep_x_kernel<0><<<m, 256, 0, stream>>>(x, xh, rs, k);
     CN_CUDA(cudaGetLastError());
-    static bool attr = false;
-    if (!attr) {
-        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemm_tc5_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(128)));
-        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemm_tc5_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_of(256)));
-        attr = true;
-    }
+    CN_ALLOW_SMEM(nvfp4_gemm_tc5_kernel<128>, (int)smem_of(128));
+    CN_ALLOW_SMEM(nvfp4_gemm_tc5_kernel<256>, (int)smem_of(256));
     GemmParams p;
     p.w = (const uint8_t*)w, p.gs = gs, p.xh = xh, p.rs = rs, p.y = y, p.rows = rows, p.k = k, p.m = m, p.ldy = ldy, p.out_bf16 = dtype == CN_BF16;
     p.ksplits = 1, p.part = nullptr;

@@ -87,9 +87,13 @@ __global__ void __launch_bounds__(NTHREADS, (MP <= 2 ? 4 : 1)) nvfp4_gemv_kernel
     const char* xbase = (const char*)p.x;
     char* ybase = (char*)p.y;
     if (p.ids) {
+        // ids, order and tables may come from the kernels just before this one, and a CTA whose expert is not resident
+        // returns at once: wait for the predecessor grid first, so that even a grid whose CTAs all return early
+        // completes only after its predecessor has
+        pdl_wait();
         const int c = p.order ? p.order[blockIdx.y] : (int)blockIdx.y;
         const int e = p.ids[c];
-        if (e < 0) return;  // uniform over the CTA, before any barrier
+        if (e < 0 || (p.experts > 0 && e >= p.experts)) return;  // uniform over the CTA, before any barrier
         w0 = (const uint8_t*)p.tab0[e];
         if (!w0) return;  // the expert is not resident here: nothing to read or write
         w1 = p.tab1 ? (const uint8_t*)p.tab1[e] : (p.fused_up_rows > 0 ? w0 + (size_t)p.fused_up_rows * row_bytes : nullptr);
@@ -462,16 +466,10 @@ __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ w, const float*
     }
 }
 
-int g_tune_mode = 0, g_tune_rt = 0, g_tune_stages = 0, g_tune_pdl = 1, g_tune_engine = 0;
-
 template <int XT, int MP, int RT, int MODE>
 int launch_one(const GemvParams& p, int grid, int gy, size_t smem, cudaStream_t stream) {
-    static bool attr_done = false;
     auto kern = nvfp4_gemv_kernel<XT, MP, RT, MODE>;
-    if (!attr_done) {
-        CN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done = true;
-    }
+    CN_ALLOW_SMEM(kern, 200 * 1024);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, (unsigned)gy);
     cfg.blockDim = dim3(NTHREADS);
@@ -479,7 +477,7 @@ int launch_one(const GemvParams& p, int grid, int gy, size_t smem, cudaStream_t 
     cfg.stream = stream;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = g_tune_pdl ? 1 : 0;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
     CN_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
@@ -508,20 +506,18 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
         CN_FAIL(CN_ERR_SHAPE, "%s: weight and activation pointers must be 16-byte aligned", who);
     const bool routed = a.ids != nullptr;
     if (routed && (m != 1 || a.combos < 1 || a.x_div < 1)) CN_FAIL(CN_ERR_SHAPE, "%s: the routed form takes one row per combo", who);
-    // bf16 activations: the tensor-core kernel (tuning key 5 = 1 keeps them on this file's CUDA-core kernel)
-    if (a.dtype == CN_BF16 && g_tune_engine != 1 && g_tune_mode != 1) return cn_gemv_m1_launch(a, stream, who);
+    // bf16 activations: the tensor-core kernel
+    if (a.dtype == CN_BF16) return cn_gemv_m1_launch(a, stream, who);
     const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;
     const int bpr = k / 64;
     const int tx = bpr % 16 == 0 ? 16 : (bpr % 8 == 0 ? 8 : 4);
     const int mp = m == 1 ? 1 : (m == 2 ? 2 : (m <= 4 ? 4 : 8));
     // f32 activations keep exact f32 arithmetic unless the caller allows rounding them to f16 at staging
-    int mode = (a.dtype == CN_BF16 || a.x_f16_ok) ? 1 : 0;
-    if (g_tune_mode == 1) mode = 0;
+    const int mode = (a.dtype == CN_BF16 || a.x_f16_ok) ? 1 : 0;
     const int G = NW * (32 / tx);
     int rt = 4;
     const long long slots = (long long)rows * (gu ? 2 : 1) * (routed ? a.combos : 1);
     if (slots / (G * 4) < 2 * 148) rt = 2;
-    if (g_tune_rt == 2 || g_tune_rt == 4) rt = g_tune_rt;
     const int ROWS = G * rt;
     const int per_cta = gu ? ROWS / 2 : ROWS;
     const int grid = (rows + per_cta - 1) / per_cta;
@@ -538,7 +534,6 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     long long cap = (208 * 1024) / resident - (long long)HDR_BYTES - (long long)xbytes;  // what fits beside the activations
     if (want > cap) want = cap;
     int stages = (int)((want + (long long)stage_bytes - 1) / (long long)stage_bytes);
-    if (g_tune_stages > 0) stages = g_tune_stages;
     stages = stages < 2 ? 2 : (stages > MAX_STAGES ? MAX_STAGES : stages);
     if (stages > nchunks) stages = nchunks < 1 ? 1 : nchunks;
     const size_t smem = HDR_BYTES + xbytes + stages * stage_bytes;
@@ -560,6 +555,7 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.w0 = (const uint8_t*)a.w0, p.w1 = (const uint8_t*)a.w1, p.gs0 = a.gs0, p.gs1 = a.gs1 ? a.gs1 : a.gs0, p.x = a.x, p.y = a.y;
     p.rows = rows, p.k = k, p.m = m, p.ldy = a.ldy, p.limit = a.limit, p.tx = tx, p.stages = stages, p.out_f32 = a.out_f32;
     p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
+    p.experts = a.experts;
     const int gy = routed ? a.combos : 1;
     if (a.dtype == CN_BF16) return mode == 1 ? launch_m<1, 1>(p, mp, rt, grid, gy, smem, stream) : launch_m<1, 0>(p, mp, rt, grid, gy, smem, stream);
     return mode == 1 ? launch_m<0, 1>(p, mp, rt, grid, gy, smem, stream) : launch_m<0, 0>(p, mp, rt, grid, gy, smem, stream);
@@ -589,13 +585,4 @@ extern "C" int cn_nvfp4_dequant(const void* w, const float* gs, float* out, int 
     nvfp4_dequant_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>((const uint8_t*)w, gs, out, nwords, rule);
     CN_CUDA(cudaGetLastError());
     return CN_OK;
-}
-
-extern "C" void cn_set_tuning(int key, int value) {
-    if (key == CN_TUNE_GEMV_MODE) g_tune_mode = value;
-    if (key == CN_TUNE_GEMV_RT) g_tune_rt = value;
-    if (key == CN_TUNE_GEMV_STAGES) g_tune_stages = value;
-    if (key == 4) g_tune_pdl = value;
-    if (key == 5) g_tune_engine = value;
-    if (key >= 7 && key <= 10) cn_gemv_m1_set(key - 7, value);
 }

@@ -21,6 +21,7 @@ struct GemvCall {
     const unsigned long long* tab0;
     const unsigned long long* tab1;
     int fused_up_rows, x_div, combos;
+    int experts;  // entries of the tables (0 = unknown: ids are trusted); an id beyond them skips the combo
 };
 
 int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who);
@@ -50,6 +51,7 @@ struct GemvParams {
     const unsigned long long* tab1;  // [experts] up (null with a fused slab or a plain matrix)
     int fused_up_rows;               // > 0: up = gate + fused_up_rows rows of the same slab
     int x_div;
+    int experts;  // entries of tab0 / tab1 (0 = unknown); ids outside 0..experts-1 skip the combo
     int red_depth;  // multi-row tensor-core kernel: tile-sum slots in flight
     int ksplit;     // 2: launched as two-CTA clusters, each CTA of a pair over half of K (one activation row only)
 };
@@ -65,4 +67,3 @@ __device__ __forceinline__ float act_gu(float g, float u, float limit) {
 
 // bf16 activation rows (1..8): persistent CTAs, tensor-core inner loop in word form (nvfp4_gemv_m1.cu)
 int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who);
-void cn_gemv_m1_set(int key, int value);  // 0 ring depth, 1 CTAs per SM, 2 blocks per row and stage (0 = automatic)

@@ -108,9 +108,14 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     const char* xbase = (const char*)p.x + (size_t)b0 * 128;
     char* ybase = (char*)p.y;
     if (p.ids) {
+        // Routed form: ids, order and the tables may come from the kernels just before this one, and a CTA whose
+        // expert is not resident returns at once. Every thread therefore waits for the predecessor grid first, so that
+        // a grid in which every CTA returns early still completes only after its predecessor has, and a later
+        // kernel's wait on this grid keeps covering the whole chain.
+        pdl_wait();
         const int c = p.order ? p.order[blockIdx.y] : (int)blockIdx.y;
         const int e = p.ids[c];
-        if (e < 0) return;  // uniform over the CTA, before any barrier
+        if (e < 0 || (p.experts > 0 && e >= p.experts)) return;  // uniform over the CTA, before any barrier
         w0 = (const uint8_t*)p.tab0[e];
         if (!w0) return;
         w1 = p.tab1 ? (const uint8_t*)p.tab1[e] : (p.fused_up_rows > 0 ? w0 + (size_t)p.fused_up_rows * row_bytes : nullptr);
@@ -482,27 +487,14 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     if (KS == 2) cluster_sync_all();  // nobody leaves while the peer may still send or receive
 }
 
-int g_m1_stages = 0, g_m1_cps = 0, g_m1_tx = 0, g_m1_ksplit = 0;
-
 template <int TX, int CPS, int MT, int KS = 1>
 int launch_m1(const cudaLaunchConfig_t& cfg, const GemvParams& p) {
-    static bool attr = false;
-    if (!attr) {
-        CN_CUDA(cudaFuncSetAttribute(nvfp4_gemv_m1_kernel<TX, CPS, MT, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        attr = true;
-    }
+    CN_ALLOW_SMEM((nvfp4_gemv_m1_kernel<TX, CPS, MT, KS>), 226 * 1024);
     CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS, MT, KS>, p));
     return CN_OK;
 }
 
 }  // namespace
-
-void cn_gemv_m1_set(int key, int value) {
-    if (key == 0) g_m1_stages = value;
-    if (key == 1) g_m1_cps = value;
-    if (key == 2) g_m1_tx = value;
-    if (key == 3) g_m1_ksplit = value;  // 0 automatic, 1 never, 2 whenever the shape allows
-}
 
 int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     const int rows = a.rows, k = a.k, m = a.m;
@@ -512,8 +504,7 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     const int mt = m == 1 ? 1 : (m == 2 ? 2 : (m <= 4 ? 4 : 8));
     // blocks per row and stage: the same rule for every row count, so that row i of an m-row call is summed in the
     // order of a one-row call
-    int tx = bpr >= 32 ? 32 : 16;
-    if (g_m1_tx == 32 || g_m1_tx == 16) tx = g_m1_tx;
+    const int tx = bpr >= 32 ? 32 : 16;
     const int pstride = tx * 36 + 16;
     const size_t stage_bytes = (size_t)ROWS * pstride;
     const size_t xbytes = (size_t)mt * bpr * XB + (size_t)((mt * bpr + 3) & ~3) * 4;
@@ -531,7 +522,6 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
             break;
         }
     if (mt == 1 && cps < 2) cps = 2;
-    if (g_m1_cps >= 1 && g_m1_cps <= 4 && (mt == 1 ? g_m1_cps >= 2 : g_m1_cps <= 2)) cps = g_m1_cps;
     // persistent CTAs, each walking its share of the tiles (the routed form keeps one tile per CTA)
     int grid = ntiles;
     if (!routed && grid > 148 * cps) grid = 148 * cps;
@@ -554,12 +544,12 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     // K, and the pair's second CTA hands its 16 sums to the first through distributed shared memory: the wave
     // quantum drops from a tile to half a tile. Taken when that shortens the longest CTA by a tenth or more.
     int ksplit = 1;
-    if (!routed && mt == 1 && tx == 32 && cps <= 3 && bpr % 8 == 0 && g_m1_ksplit != 1) {
+    if (!routed && mt == 1 && tx == 32 && cps <= 3 && bpr % 8 == 0) {
         const int slots = 148 * cps, pairs = slots / 2;
         const int waves1 = (ntiles + slots - 1) / slots, waves2 = (ntiles + pairs - 1) / pairs;  // tiles / CTA, half tiles / CTA
         // worth it only when a CTA's share is long enough to hide the pair's hand-over (measured: 235 KB yes, 69 KB no)
         const long long share = (long long)waves2 * ROWS * bpr * 36 / 2;
-        if (waves2 <= XCH_SLOTS && (g_m1_ksplit == 2 || (10 * waves2 <= 18 * waves1 && share >= 160 * 1024))) {
+        if (waves2 <= XCH_SLOTS && 10 * waves2 <= 18 * waves1 && share >= 160 * 1024) {
             ksplit = 2;
             grid = 2 * (ntiles < pairs ? ntiles : pairs);
         }
@@ -573,7 +563,6 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     int fit = MAX_STAGES;  // ring depth that fits beside the fixed part
     while (fit > 1 && fixed2(fit) + (long long)fit * (long long)stage_bytes > (227 * 1024) / cps - 1024) fit--;
     int stages = fit;
-    if (g_m1_stages > 0 && g_m1_stages < stages) stages = g_m1_stages;
     const int total_chunks = nch * ((ntiles + grid / ksplit - 1) / (grid / ksplit));
     if (stages > total_chunks) stages = total_chunks;
     if (stages < 1) stages = 1;
@@ -597,6 +586,7 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
     p.red_depth = red_depth;
     p.ksplit = ksplit;
+    p.experts = a.experts;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, (unsigned)(routed ? a.combos : 1));
     cfg.blockDim = dim3(NTHREADS);

@@ -72,7 +72,7 @@ class Mul1Plan:
         if y is None:
             y = torch.empty_like(x)
         check(lib().cn_moe_mul1_run(self.handle, table.data_ptr(), ids.data_ptr(), wts.data_ptr(), None if shared is None else shared.data_ptr(),
-                                    x.data_ptr(), y.data_ptr(), tokens, topk, float(limit), _dt(x), _stream()))
+                                    x.data_ptr(), y.data_ptr(), tokens, topk, int(table.numel()), float(limit), _dt(x), _stream()))
         return y
 
     def free(self):

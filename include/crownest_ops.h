@@ -107,11 +107,12 @@ int cn_moe_sort(const int32_t* ids, int32_t* order, int combos, int experts, cn_
 
 /* y[t] = base[t] + sum_j wts[t][j] * eo[t*topk + j], j in pick order; base = shared[t] (times
  * sigmoid(sgate[t]) when sgate != null), 0 when shared == null. A combo whose table entry is null
- * adds nothing (table may be null: every combo counts). Replaces acc_combo + gate_shared
+ * adds nothing (table may be null: every combo counts), and so does an id outside 0..experts-1 (experts = entries
+ * of table; 0 = not checked). Replaces acc_combo + gate_shared
  * (engine/src/kernels.rs:1583-1599) and glm5_moe_combine (engine/src/kernels_glm5_moe.cu:141).
  * eo, shared f32; y in `dtype`. */
 int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const unsigned long long* table, const float* shared,
-                   const float* sgate, void* y, int tokens, int hidden, int topk, int dtype, cn_stream_t stream);
+                   const float* sgate, void* y, int tokens, int hidden, int topk, int experts, int dtype, cn_stream_t stream);
 
 /* The routed-expert decode step, GpuMoePlan-shaped (engine/src/glm5_moe.rs:518-793; Flash-Next call
  * site Engine::moe_run, engine/src/gen.rs:4168-4532). The plan owns the scratch (the only
@@ -121,7 +122,8 @@ int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const 
  * stream as if it ran on it (a capture of `stream` takes the side branch in). cn_mul1_ffn and
  * cn_moe_mul1_run do the same with the up projection.
  * Tables are device arrays [experts] of device addresses (0 = expert not resident: its combos are
- * skipped, the contract of engine/src/kernels_mul1.cu:118-119): table_gu = gate [inter][hidden], or
+ * skipped, the contract of engine/src/kernels_mul1.cu:118-119; so are ids outside 0..experts-1). ids, order and the
+ * tables must be complete when the call is enqueued or be written by earlier work on `stream`. table_gu = gate [inter][hidden], or
  * the fused gate|up slab [2*inter][hidden] when table_up == null; table_dn = down [hidden][inter].
  * gs_gu / gs_up / gs_dn: device f32 tensor scales shared by all experts (gs_up may be null = gs_gu).
  * shared_*: the shared expert's matrices (null = none) with shared_gs a device f32[3] (gate, up,
@@ -176,9 +178,10 @@ int cn_mul1_ffn(void* plan, const unsigned long long* ptrs, const void* x, void*
 /* The GLM-style routed step over MUL1 experts: ptrs[c] = table[ids[c]] (glm5_moe_gather), one slot
  * per (token, rank) combo, the FFN of every slot, then y[t] = sum_j wts[t][j] * eo[t*topk + j] +
  * shared[t] (shared: optional f32 [tokens][hidden], e.g. the NVFP4 shared expert's output).
- * GpuMoePlan::experts (engine/src/glm5_moe.rs:741-793). The plan needs max_slots >= tokens * topk. */
+ * GpuMoePlan::experts (engine/src/glm5_moe.rs:741-793). The plan needs max_slots >= tokens * topk. experts = entries of
+ * table: an id outside 0..experts-1 is skipped like a null entry (0 = ids are not checked). */
 int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared,
-                    const void* x, void* y, int tokens, int topk, float limit, int dtype, cn_stream_t stream);
+                    const void* x, void* y, int tokens, int topk, int experts, float limit, int dtype, cn_stream_t stream);
 
 /* The MUL1 GEMV of cn_mul1_gemv without a plan and without any allocation: for a caller that cannot
  * allocate device memory where it makes the call (a decode loop that must not hit the device-wide
@@ -224,14 +227,6 @@ int cn_peer_open(const void* handle64, size_t offset, void** ptr);
 int cn_peer_close(void* ptr, size_t offset);
 int cn_tp_allgather(const void* const* peer_bases, int rank, int world, size_t data_off, size_t slice_bytes, size_t flag_off,
                     cn_stream_t stream);
-
-/* diagnostics: select an inner-loop variant of the NVFP4 GEMV for A/B timing (0 = default) */
-void cn_set_tuning(int key, int value);
-#define CN_TUNE_GEMV_MODE 1 /* 0 default, 1 force f32 FMA path, 2 force f16 mixed-FMA path */
-#define CN_TUNE_GEMV_RT 2   /* rows per thread: 0 heuristic, else 1, 2 or 4 */
-#define CN_TUNE_GEMV_STAGES 3
-/* 4: programmatic dependent launch on (1, default) / off (0); 5: 1 = send bf16 calls to the CUDA-core kernel too;
- * 7, 8, 9: tensor-core GEMV ring depth, CTAs per SM, blocks per row and stage (0 = chosen by the library) */
 
 #ifdef __cplusplus
 }

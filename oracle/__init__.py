@@ -17,7 +17,7 @@ _SO = os.path.join(_HERE, "libcn_oracle.so")
 
 def build(force=False):
     """Compile the C restatement with gcc (a few seconds)."""
-    srcs = [os.path.join(_HERE, f) for f in ("nvfp4.c", "fp8.c", "route.c", "mul1.c", "Makefile")]
+    srcs = [os.path.join(_HERE, f) for f in ("nvfp4.c", "fp8.c", "route.c", "mul1.c", "cascade.c", "pool.c", "Makefile")]
     stale = not os.path.exists(_SO) or any(os.path.getmtime(s) > os.path.getmtime(_SO) for s in srcs)
     if force or stale:
         subprocess.run(["make", "-C", _HERE, "-B", "libcn_oracle.so"], check=True, capture_output=True)
@@ -78,6 +78,15 @@ def _declare(L):
     L.cn_o_f32_to_f16.restype = C.c_uint16
     L.cn_o_f32_to_f16.argtypes = [C.c_float]
     L.cn_o_mul1_reconstruct.argtypes = [_u16p, _i64, _i64, C.c_int, C.c_int, _u16p]
+    L.cn_o_q_e2m1.restype = C.c_uint32
+    L.cn_o_q_e2m1.argtypes = [C.c_float]
+    L.cn_o_enc_ue4m3_up.restype = C.c_uint8
+    L.cn_o_enc_ue4m3_up.argtypes = [C.c_float]
+    L.cn_o_row_prescale_k.argtypes = [C.c_float]
+    L.cn_o_act_cascade.argtypes = [_f32p, _i64, C.c_int, C.c_int, C.c_int, _u8p]
+    L.cn_o_act_cascade.restype = None
+    L.cn_o_act_cascade_dequant.argtypes = [_u8p, _i64, C.c_int, C.c_int, _f32p]
+    L.cn_o_act_cascade_dequant.restype = None
     L.cn_o_mul1_synth_words.argtypes = [_u16p, _i64, C.c_uint32]
     L.cn_o_fwht128.argtypes = [_f32p]
     L.cn_o_mul1_gemv.argtypes = [_u8p, _u8p, _u8p, _i64, _i64, C.c_int, C.c_int, _f32p, _i64, _f32p, C.c_int]
@@ -146,6 +155,23 @@ def nvfp4_gemv_f64(w, rows, cols, gs, x, rule=True):
 
 
 # ---------------------------------------------------------------- FP8
+
+def act_cascade(x, levels=3, prescale=True, level_shift=0):
+    """One f32 row -> `levels` NVFP4 levels of residuals + the row factor 2^-k (engine/src/kernels.rs:5418-5437,
+    three levels there): uint8 [levels * k/64 * 36 + 4]."""
+    x = _c(x, np.float32).reshape(-1)
+    out = np.zeros(levels * (x.size // 64) * 36 + 4, np.uint8)
+    lib().cn_o_act_cascade(_p(x, _f32p), x.size, levels, int(prescale), level_shift, _p(out, _u8p))
+    return out
+
+
+def act_cascade_dequant(q, k, levels=3, level_shift=0):
+    """The row the MMA consumers see: (sum of the levels) * 2^-k (engine/src/kernels.rs:5462-5474)."""
+    q = _c(q, np.uint8)
+    out = np.empty(k, np.float32)
+    lib().cn_o_act_cascade_dequant(_p(q, _u8p), k, levels, level_shift, _p(out, _f32p))
+    return out
+
 
 def e4m3_table():
     return np.array([lib().cn_o_e4m3_to_f32(b) for b in range(256)], np.float32)

@@ -19,6 +19,9 @@
  */
 #include <math.h>
 #include <pthread.h>
+#include <stddef.h>
+
+void cn_o_pool_run(void* (*fn)(void*), void* jobs, size_t stride, int n);
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -267,15 +270,14 @@ static int gemv_mat(const mul1_mat* m, const float* x, int64_t tokens, float* y,
     prep_all(m, x, tokens, xp);
     int k = threads < 1 ? 1 : threads;
     if (k > tn) k = (int)tn;
-    pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)k);
+    if (k > 257) k = 257; /* the pool's size */
     col_job* jobs = (col_job*)malloc(sizeof(col_job) * (size_t)k);
     for (int i = 0; i < k; i++) {
         col_job j = {m, lo, xp, tokens, tn * i / k, tn * (i + 1) / k, raw};
         jobs[i] = j;
-        if (i > 0) pthread_create(&th[i], NULL, col_worker, &jobs[i]);
     }
-    col_worker(&jobs[0]);
-    for (int i = 1; i < k; i++) pthread_join(th[i], NULL);
+    /* parked workers (the reference's persistent pool, engine/src/cpu_mul1.rs:2114-2318), not a thread start per call */
+    cn_o_pool_run(col_worker, jobs, sizeof(col_job), k);
     float v[HAD];
     for (int64_t t = 0; t < tokens; t++)
         for (int64_t b = 0; b < m->n / HAD; b++) {
@@ -283,7 +285,6 @@ static int gemv_mat(const mul1_mat* m, const float* x, int64_t tokens, float* y,
             cn_o_fwht128(v);
             for (int i = 0; i < HAD; i++) y[t * m->n + b * HAD + i] = (v[i] * (1.0f / 128.0f)) * scale_at(m->svh, b * HAD + i);
         }
-    free(th);
     free(jobs);
     free(xp);
     free(raw);

@@ -27,6 +27,8 @@
 #include <immintrin.h>
 #endif
 
+void cn_o_pool_run(void* (*fn)(void*), void* jobs, size_t stride, int n);
+
 #define CN_BLOCK_BYTES 36
 #define CN_BLOCK_VALUES 64
 #define CN_TOK_TILE 4
@@ -225,16 +227,13 @@ static void gemv_xp(int path, const uint8_t* w, int64_t rows, int64_t cols, cons
         rows_into(path, w, rows, cols, lut, xp, tokens, 0, rows, y);
         return;
     }
-    pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)k);
+    if (k > 257) k = 257; /* the pool's size */
     gemv_job* jobs = (gemv_job*)malloc(sizeof(gemv_job) * (size_t)k);
     for (int i = 0; i < k; i++) {
         gemv_job j = {path, w, rows, cols, tokens, rows * i / k, rows * (i + 1) / k, lut, xp, y};
         jobs[i] = j;
-        if (i > 0) pthread_create(&th[i], NULL, gemv_worker, &jobs[i]);
     }
-    gemv_worker(&jobs[0]);
-    for (int i = 1; i < k; i++) pthread_join(th[i], NULL);
-    free(th);
+    cn_o_pool_run(gemv_worker, jobs, sizeof(gemv_job), k); /* parked workers, not a thread start per call */
     free(jobs);
 }
 

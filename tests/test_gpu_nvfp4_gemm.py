@@ -66,3 +66,24 @@ def test_gemm_agrees_with_the_gemv_on_the_same_rows():
     a = from_dev_bf16(ops.launch_gemm(fw, to_dev_bf16(xb)))
     b = from_dev_bf16(ops.launch_gemv(fw, to_dev_bf16(xb)))
     assert np.max(np.abs(a - b)) <= 2 * np.max(np.abs(b)) * 2.0 ** -8
+
+
+@pytest.mark.parametrize("rows,k", [(17408, 5120), (5120, 17408)])
+@pytest.mark.parametrize("m,nrows,ntok", [(64, 256, 64), (512, 256, 512), (4096, 96, 192)])
+def test_gemm_on_the_batched_benchmark_matrices(rows, k, m, nrows, ntok):
+    """The two matrices of the batched configuration at M = 64 / 512 / 4096, checked on a sample: `nrows` output rows
+    spread over every row tile region (first and last rows included) for `ntok` of the tokens (all of them up to
+    M = 512). The CPU reference only needs the sampled weight rows and tokens."""
+    rng = np.random.default_rng(rows + m)
+    w = synth.nvfp4_matrix(rows, k, rng)
+    gs = np.float32(0.21)
+    xb, xf = synth.activations(m, k, rng)
+    fw = ops.Fp4.from_host(w, rows, k, gs)
+    y = ops.launch_gemm(fw, to_dev_bf16(xb))
+    pick = np.unique(np.concatenate([[0, 1, 127, 128, rows - 129, rows - 1], rng.integers(0, rows, size=nrows)]))
+    toks = np.arange(m) if ntok >= m else np.unique(np.concatenate([[0, 127, 128, 255, 256, m - 1], rng.integers(0, m, size=ntok)]))
+    rb = k // 64 * 36
+    sub = np.ascontiguousarray(w.reshape(rows, rb)[pick]).reshape(-1)
+    ref = cpu_rows(sub, len(pick), k, gs, np.ascontiguousarray(xf[toks]))
+    got = from_dev_bf16(y)[np.ix_(toks, pick)]
+    check_close(got, ref, f"gemm {rows}x{k} m={m} (sample)", ulp_floor=1.0 / 64)

@@ -136,11 +136,9 @@ def test_fused_gate_up_matches_the_cpu_ffn_stage(limit, m):
     act = np.vectorize(lambda a, b: L.cn_o_swiglu_clamp(a, b, limit) if limit > 0 else L.cn_o_silu_mul(a, b))
     ref = act(g, u).astype(np.float32)
     h = ops.launch_gemv_gu(ops.Fp4.from_host(wg, inter, cols, gsg), ops.Fp4.from_host(wu, inter, cols, gsu), to_dev_bf16(xb), limit=limit)
-    # h = silu(g) * u amplifies the bf16-ulp-level differences of g and u: compare in rel L2 and in
-    # ulps of the larger factor
-    got = from_dev_bf16(h)
-    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
-    assert rel <= 4e-3, rel
+    # the reference rounded once to bf16, like every other case; the ulp is taken no lower than rms / 64 because
+    # h = silu(g) * u cancels towards zero where g does
+    check_close(from_dev_bf16(h), ref, f"gate/up m={m} limit={limit}", ulp_floor=1.0 / 64)
 
 
 def test_full_ffn_against_cpu_expert_ffn():
@@ -166,28 +164,26 @@ def test_errors_are_named_not_fatal():
         ops.Fp4.from_host(np.zeros(10, np.uint8), 64, 256, 1.0)
 
 
-@pytest.mark.parametrize("rows,cols,gu", [(640, 4096, False), (5120, 17408, False), (512, 2048, True)])
+@pytest.mark.parametrize("rows,cols,gu", [(5120, 17408, False), (6000, 17408, False), (2560, 17408, True)])
 def test_k_shared_by_a_cta_pair_matches_the_cpu_reference(rows, cols, gu):
-    """Tuning key 10 = 2 forces the two-CTA-cluster form (each CTA of a pair over half of K, sums handed over through
-    distributed shared memory) wherever the shape allows; the library itself picks it for the down projection."""
-    from crownest_b200._lib import lib
+    """Shapes for which the library launches two-CTA clusters (tiles that do not fill the last wave and a long K, the
+    down projection of the dense stack among them): each CTA of a pair sums half of K and the halves meet through
+    distributed shared memory in a fixed order."""
     rng, w, fw = make(rows, cols, rows + cols)
     xb, xf = synth.activations(1, cols, rng)
-    lib().cn_set_tuning(10, 2)
-    try:
-        if gu:
-            w2 = synth.nvfp4_matrix(rows, cols, rng)
-            fw2 = ops.Fp4.from_host(w2, rows, cols, 1.0)
-            y = ops.launch_gemv_gu(fw, fw2, to_dev_bf16(xb))
-            g = oracle.nvfp4_gemv(w, rows, cols, np.float32(1.0), xf, threads=8, path=1)
-            u = oracle.nvfp4_gemv(w2, rows, cols, np.float32(1.0), xf, threads=8, path=1)
-            ref = np.vectorize(oracle.lib().cn_o_silu_mul)(g, u).astype(np.float32)
-        else:
-            y = ops.launch_gemv(fw, to_dev_bf16(xb))
-            ref = oracle.nvfp4_gemv(w, rows, cols, np.float32(1.0), xf, threads=8, path=1)
-        y2 = ops.launch_gemv_gu(fw, fw2, to_dev_bf16(xb)) if gu else ops.launch_gemv(fw, to_dev_bf16(xb))
-    finally:
-        lib().cn_set_tuning(10, 0)
+    if gu:
+        w2 = synth.nvfp4_matrix(rows, cols, rng)
+        fw2 = ops.Fp4.from_host(w2, rows, cols, 1.0)
+        y = ops.launch_gemv_gu(fw, fw2, to_dev_bf16(xb))
+        g = oracle.nvfp4_gemv(w, rows, cols, np.float32(1.0), xf, threads=8, path=1)
+        u = oracle.nvfp4_gemv(w2, rows, cols, np.float32(1.0), xf, threads=8, path=1)
+        ref = np.vectorize(oracle.lib().cn_o_silu_mul)(g, u).astype(np.float32)
+    else:
+        y = ops.launch_gemv(fw, to_dev_bf16(xb))
+        ref = oracle.nvfp4_gemv(w, rows, cols, np.float32(1.0), xf, threads=8, path=1)
+    y2 = ops.launch_gemv_gu(fw, fw2, to_dev_bf16(xb)) if gu else ops.launch_gemv(fw, to_dev_bf16(xb))
     assert torch.equal(y.view(torch.int16), y2.view(torch.int16))  # run to run: the same bits
-    check_close(from_dev_bf16(y), ref, f"cluster pair {rows}x{cols} gu={gu}", ulp_floor=1.0 / 64 if gu else 0.0)
+    # 5120 .. 6000 outputs over k = 17408: a few cancel to 1e-4 of the row's scale, where the f32 accumulation error of
+    # either side is already several bf16 ulp of the value; the ulp is taken no lower than rms / 256
+    check_close(from_dev_bf16(y), ref, f"cluster pair {rows}x{cols} gu={gu}", ulp_floor=1.0 / 64 if gu else 1.0 / 256)
     assert device_status() == 0

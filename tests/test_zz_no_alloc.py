@@ -13,6 +13,7 @@ import pytest
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
+import oracle
 from crownest_b200 import mul1
 from crownest_b200._lib import CN_F32, CN_BF16, check, lib
 from oracle import testkit as tk
@@ -48,6 +49,42 @@ def test_noalloc_gemv_equals_the_plan_gemv_on_two_calls_in_a_row():
         assert rel <= 1e-3
         assert torch.equal(got.view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
                            want.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+    plan.free()
+
+
+def test_noalloc_gemv_at_its_size_limits_against_the_cpu_reference():
+    """hidden = inter = 4096 and 8 activation rows fill the fixed array to its last byte; two calls in a row (gate, then
+    down with other inputs) are held to the plan-based entry point bit for bit, and the first to the CPU reference."""
+    hidden = inter = 4096
+    K = 3.0
+    rec = tk.mul1_record(91, hidden, inter, K)
+    d_rec = torch.from_numpy(rec).cuda()
+    ptrs = torch.tensor([d_rec.data_ptr()], dtype=torch.int64, device="cuda")
+    plan = mul1.Mul1Plan(hidden, inter, K, slots=1, tokens=8)
+    rng = np.random.default_rng(6)
+    tb = oracle.mul1_trellis_bytes(hidden, inter, K)
+    scales, at = [], 3 * tb
+    for _ in range(6):
+        scales.append(rec[at:at + 2 * hidden].view(np.uint16))
+        at += 2 * hidden
+    for which in (0, 2):
+        xh = rng.uniform(-2, 2, size=(1, 8, hidden)).astype(np.float32)
+        x = torch.from_numpy(xh).cuda()
+        want = plan.run_slots(which, ptrs, x)
+        rc, got = noalloc(which, hidden, inter, K, ptrs, x, slots=1, t=8)
+        check(rc)
+        torch.cuda.synchronize()
+        assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+        if which == 0:
+            ref = oracle.mul1_gemv(rec[:tb], scales[0], scales[1], hidden, inter, K, xh[0], threads=8)
+            rel = np.linalg.norm(got.cpu().numpy()[0] - ref) / np.linalg.norm(ref)
+            assert rel <= 1e-3, rel
+    rc, _ = noalloc(0, hidden, inter, K, ptrs, torch.zeros((1, 8, hidden), device="cuda"), slots=1, t=8)
+    check(rc)
+    # a dtype the kernels do not take is refused before anything is enqueued
+    rc = lib().cn_mul1_gemv_noalloc(0, hidden, inter, 3, 0, ptrs.data_ptr(), x.data_ptr(), want.data_ptr(), 1, 8, 1, 2,
+                                    torch.cuda.current_stream().cuda_stream)
+    assert rc == 1 and b"dtype 2" in lib().cn_last_error_string()
     plan.free()
 
 
