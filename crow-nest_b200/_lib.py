@@ -39,6 +39,9 @@ _SIGS = {
     "cn_nvfp4_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cn_nvfp4_gemv_gu": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "cn_nvfp4_dequant": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "cn_nvfp4_seq_create": [C.POINTER(C.c_void_p), _vp, _i],
+    "cn_nvfp4_seq_run": [_vp, _vp],
+    "cn_nvfp4_seq_destroy": [_vp],
     "cn_route_softmax_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "cn_route_sigmoid_topk": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cn_moe_sort": [_vp, _vp, _i, _i, _vp],
@@ -65,6 +68,12 @@ _SIGS = {
     "cn_version": [],
 }
 _RESTYPES = {"cn_last_error_string": C.c_char_p, "cn_version": C.c_char_p}
+
+
+class GemvStep(C.Structure):
+    """cn_gemv_step of include/crownest_ops.h"""
+    _fields_ = [("w", _vp), ("w_up", _vp), ("gs", _vp), ("gs_up", _vp), ("x", _vp), ("y", _vp), ("rows", _i), ("k", _i), ("limit", _f),
+                ("after", _i), ("out_f32", _i)]
 
 
 def exported_symbols():

@@ -155,6 +155,27 @@ class DenseStack:
                     self.peer, self.peer_error = None, str(e)
         self.launches_per_step = 4 * self.layers
         self.graph = None
+        self.chains = None
+
+    def fuse(self, per_launch="token"):
+        """Run the stack's projections as persistent chains (`ops.GemvSeq`): "token" = the whole stack in one launch,
+        "layer" = one launch per layer. One activation row, one GPU. Every step waits for its predecessor, as the
+        projections of a real decode step do."""
+        if self.world != 1 or self.dtype != torch.bfloat16:
+            raise CrownestError("the fused chain takes one bf16 row on one GPU")
+        self.chains = []
+        seq, prev = ops.GemvSeq(), None
+        x = self.x[:1]
+        for i, mats in enumerate(self.w):
+            prev = seq.gemv(mats["qkv"], x, self.q[:1], after=prev)
+            prev = seq.gemv(mats["o"], x, self.o[:1], after=prev)
+            prev = seq.gemv_gu(mats["gate"], mats["up"], x, self.h[:1], after=prev)
+            prev = seq.gemv(mats["down"], self.h[:1], self.y[:1], after=prev)
+            if per_launch == "layer" or i == len(self.w) - 1:
+                self.chains.append(seq.build())
+                seq, prev = ops.GemvSeq(), None
+        self.launches_per_step = len(self.chains)
+        return self
 
     # algorithmic bytes of one step over all ranks: every weight byte once, plus the tensor scale and the
     # activations in and out of each projection at the boundary dtype
@@ -186,7 +207,11 @@ class DenseStack:
             self._gather(name, full, m)
 
     def run_layers(self, m=1):
-        """Enqueue the whole stack on the current stream (4 launches per layer)."""
+        """Enqueue the whole stack on the current stream (4 launches per layer, or the fused chains)."""
+        if self.chains is not None and m == 1:
+            for c in self.chains:
+                c.run()
+            return self.y[:1]
         x = self.x[:m]
         for mats in self.w:
             self._proj(mats["qkv"], x, "q", self.q, m)

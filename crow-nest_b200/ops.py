@@ -106,6 +106,58 @@ def dense_ffn_w(gate: Fp4, up: Fp4, down: Fp4, x, limit=0.0):
     return launch_gemv(down, launch_gemv_gu(gate, up, x, limit=limit))
 
 
+class GemvSeq:
+    """A chain of one-row GEMV steps run by one persistent launch (cn_nvfp4_seq_*): the fused form of
+    Engine::dense_ffn_w (engine/src/gen.rs:3974-3990) and of a stack of projections. Steps are added with
+    ``gemv`` / ``gemv_gu`` (which return the step's index, to be named as a later step's ``after``), then ``build()``
+    once and ``run()`` per token. The tensors named by the steps are borrowed: keep them alive."""
+
+    def __init__(self):
+        self.steps, self.keep, self.handle = [], [], None
+
+    def _add(self, w, up, x, y, limit, after):
+        if x.dtype != torch.bfloat16 or x.numel() != w.cols:
+            raise CrownestError(f"gemv chain: x must be one bf16 row of {w.cols} values")
+        if y.numel() != w.rows or y.dtype not in (torch.bfloat16, torch.float32):
+            raise CrownestError(f"gemv chain: y must be one bf16 or f32 row of {w.rows} values")
+        st = _lib.GemvStep(w.w.data_ptr(), None if up is None else up.w.data_ptr(), w.gs.data_ptr(), None if up is None else up.gs.data_ptr(),
+                           x.data_ptr(), y.data_ptr(), w.rows, w.cols, float(limit), -1 if after is None else int(after),
+                           int(y.dtype == torch.float32))
+        self.steps.append(st)
+        self.keep += [w, up, x, y]
+        return len(self.steps) - 1
+
+    def gemv(self, w: Fp4, x, y, after=None):
+        return self._add(w, None, x, y, 0.0, after)
+
+    def gemv_gu(self, gate: Fp4, up: Fp4, x, h, limit=0.0, after=None):
+        if (gate.rows, gate.cols) != (up.rows, up.cols):
+            raise CrownestError("gemv chain: gate and up shapes differ")
+        return self._add(gate, up, x, h, limit, after)
+
+    def build(self):
+        import ctypes as C
+        arr = (_lib.GemvStep * len(self.steps))(*self.steps)
+        h = C.c_void_p()
+        check(lib().cn_nvfp4_seq_create(C.byref(h), arr, len(self.steps)))
+        self.handle = h
+        return self
+
+    def run(self):
+        check(lib().cn_nvfp4_seq_run(self.handle, _stream()))
+
+    def free(self):
+        if self.handle:
+            check(lib().cn_nvfp4_seq_destroy(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 def dequant(w: Fp4, rule=False):
     """f32 [rows][cols] = e2m1(code) * (ue4m3(byte) * gs): dequant_fp4_flat (engine/src/kernels.rs:1460)."""
     out = torch.empty((w.rows, w.cols), dtype=torch.float32, device=w.w.device)

@@ -80,6 +80,34 @@ int cn_nvfp4_gemv(const void* w, const float* gs, const void* x, void* y, int ro
 int cn_nvfp4_gemv_gu(const void* wg, const void* wu, const float* gs_g, const float* gs_u, const void* x, void* h,
                      int inter, int k, int m, int ldh, float limit, int dtype, cn_stream_t stream);
 
+/* A chain of one-row (bf16) NVFP4 GEMV steps in ONE persistent launch: the fused form of the decode step's
+ * projection chain. Replaces the launch sequence of Engine::dense_ffn_w (engine/src/gen.rs:3974-3990: gemv_nvfp4_gu then
+ * gemv_nvfp4_w), the FusedFfn operator (engine/src/kernels.rs:6777-6840) and, for a stack of projections, the launches of
+ * Engine::decode_step (engine/src/gen.rs:6117-6190). The CTAs stay resident over all steps: weights of the next step are
+ * already streaming while a step finishes, and every step's work is dealt to the CTAs in equal shares whatever its row
+ * count. Step i: y = W x, or h = act(W x, W_up x) when w_up != null (limit as in cn_nvfp4_gemv_gu); x bf16 [k], y bf16
+ * [rows] (f32 when out_f32). `after`: index of the earlier step whose output this step reads (it starts reading x only
+ * once that step is complete on every CTA), -1 when x is ready before the launch. A step that overwrites a buffer an
+ * earlier step reads must be ordered after it through `after` links. k a multiple of 256, k >= 2048.
+ * The plan copies the descriptors to the device and owns the hand-over scratch (the only allocation; run() allocates
+ * nothing and does not synchronise; the launch is cooperative). One run at a time per plan. After a device-side wait
+ * has failed (cn_device_status) the plan's counters are undefined: destroy it. */
+typedef struct cn_gemv_step {
+    const void* w;      /* [rows][k] NVFP4, or gate */
+    const void* w_up;   /* up (fused gate/up + activation), else null */
+    const float* gs;    /* device f32 tensor scale of w */
+    const float* gs_up; /* of w_up (null: gs) */
+    const void* x;      /* bf16 [k] */
+    void* y;            /* bf16 (or f32) [rows] */
+    int rows, k;
+    float limit;
+    int after;
+    int out_f32;
+} cn_gemv_step;
+int cn_nvfp4_seq_create(void** plan_out, const cn_gemv_step* steps, int nsteps);
+int cn_nvfp4_seq_run(void* plan, cn_stream_t stream);
+int cn_nvfp4_seq_destroy(void* plan);
+
 /* Bit-exact dequantisation self-check: out[r][c] f32 = e2m1(code) * (ue4m3(scale byte) * gs).
  * Replaces dequant_fp4_flat (engine/src/kernels.rs:1460), host twin cnq::dequant_block
  * (engine/src/cnq.rs:1298). rule != 0 reads 0x7F as 0x7E first (the GEMV's reading). */
