@@ -49,6 +49,13 @@ _SIGS = {
     "cn_moe_nvfp4_plan_create": [C.POINTER(C.c_void_p), _i, _i, _i, _i, _i, _i],
     "cn_moe_nvfp4_plan_destroy": [_vp],
     "cn_moe_nvfp4_run": [_vp] * 16 + [_i, _f, _i, _vp],
+    "cn_moe_nvfp4_experts": [_vp] * 11 + [_i, _i, _f, _i, _vp],
+    "cn_moe_nvfp4_finish": [_vp] * 12 + [_i, _f, _i, _vp],
+    "cn_moe_nvfp4_shared_begin": [_vp] * 6 + [_i, _f, _i, _vp],
+    "cn_moe_mul1_experts": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "cn_ep_flag_bytes": [],
+    "cn_ep_dispatch": [C.POINTER(C.c_void_p), _i, _i, _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp],
+    "cn_ep_return": [C.POINTER(C.c_void_p), _i, _i, _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _vp],
     "cn_nvfp4_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
     "cn_nvfp4_gemm_workspace_bytes": [_i, _i],
     "cn_peer_export": [_vp, _vp, C.POINTER(C.c_size_t)],
@@ -81,7 +88,7 @@ def exported_symbols():
     return sorted(_SIGS)
 
 
-_RESTYPES_INIT = {"cn_nvfp4_gemm_workspace_bytes": C.c_size_t}
+_RESTYPES_INIT = {"cn_nvfp4_gemm_workspace_bytes": C.c_size_t, "cn_ep_flag_bytes": C.c_size_t}
 
 
 def register(name, argtypes, restype=C.c_int):

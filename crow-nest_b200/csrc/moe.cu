@@ -124,6 +124,7 @@ struct MoePlan {
     // between two events (fork after the caller's earlier work, join before the combine), also under stream capture
     cudaStream_t side;
     cudaEvent_t fork, join;
+    bool shared_pending;  // cn_moe_nvfp4_shared_begin has enqueued the shared expert; the next finish joins it
 };
 
 }  // namespace
@@ -189,6 +190,107 @@ extern "C" int cn_moe_nvfp4_plan_destroy(void* plan) {
     return CN_OK;
 }
 
+namespace {
+
+// the shared expert on every token, up to 8 rows per pass, on the plan's side stream between the fork and join events:
+// whatever happens after the fork, the side stream is joined again (a capture of the caller's stream stays valid)
+int shared_branch(MoePlan* p, const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs, const void* x,
+                  int tokens, float limit, int dtype, cudaStream_t stream) {
+    CN_CUDA(cudaEventRecord(p->fork, stream));
+    CN_CUDA(cudaStreamWaitEvent(p->side, p->fork, 0));
+    const size_t es = dtype == CN_BF16 ? 2 : 4;
+    int rc = CN_OK;
+    for (int t0 = 0; t0 < tokens && rc == CN_OK; t0 += CN_MAX_M) {
+        const int m = tokens - t0 < CN_MAX_M ? tokens - t0 : CN_MAX_M;
+        GemvCall g = {};
+        g.w0 = shared_gate, g.w1 = shared_up, g.gs0 = shared_gs, g.gs1 = shared_gs + 1, g.x = (const char*)x + (size_t)t0 * p->hidden * es;
+        g.y = p->hs + (size_t)t0 * p->shared_inter, g.rows = p->shared_inter, g.k = p->hidden, g.m = m, g.ldy = p->shared_inter;
+        g.limit = limit, g.dtype = dtype, g.out_f32 = 1;
+        rc = cn_gemv_launch(g, p->side, "cn_moe_nvfp4_run (shared gate/up)");
+        if (rc != CN_OK) break;
+        GemvCall s = {};
+        s.w0 = shared_down, s.gs0 = shared_gs + 2, s.x = p->hs + (size_t)t0 * p->shared_inter, s.y = p->ys + (size_t)t0 * p->hidden;
+        s.rows = p->hidden, s.k = p->shared_inter, s.m = m, s.ldy = p->hidden, s.dtype = CN_F32, s.out_f32 = 1, s.x_f16_ok = 0;
+        rc = cn_gemv_launch(s, p->side, "cn_moe_nvfp4_run (shared down)");
+    }
+    CN_CUDA(cudaEventRecord(p->join, p->side));
+    return rc;
+}
+
+// routed gate|up + activation, then routed down, one launch each over `combos` (token, pick) pairs: combo c reads
+// activation row c / x_div and writes eo row c (or to eo_ptrs[c] when given: a row of another buffer, e.g. in a peer's memory)
+int routed_experts(MoePlan* p, const unsigned long long* table_gu, const unsigned long long* table_up, const unsigned long long* table_dn,
+                   const float* gs_gu, const float* gs_up, const float* gs_dn, const int32_t* ids, const void* x, float* eo,
+                   const unsigned long long* eo_ptrs, int combos, int x_div, float limit, int dtype, cudaStream_t stream) {
+    // Combos sorted by expert keep the CTAs that read one expert's matrices next to each other in launch order. With
+    // few combos most CTAs of the step are resident at once and L2 serves a second reader anyway: no sort, one launch
+    // less on the critical path (measured with top-10 of 512 experts: 10 % faster unsorted at 8 and 16 tokens, even at
+    // 32, 1 % slower at 64). The sort is one CTA and ranks each combo among all others: left out for long lists too.
+    const int32_t* order = nullptr;
+    if (combos > 320 && combos <= 1024) {
+        if (int rc = cn_moe_sort(ids, p->order, combos, p->experts, (cn_stream_t)stream)) return rc;
+        order = p->order;
+    }
+    GemvCall a = {};
+    a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
+    a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = order, a.tab0 = table_gu, a.tab1 = table_up;
+    a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = x_div, a.combos = combos, a.experts = p->experts;
+    if (int rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4 (gate/up)")) return rc;
+    GemvCall d = {};
+    d.gs0 = gs_dn, d.x = p->h, d.y = eo, d.yptrs = eo_ptrs, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
+    d.x_f16_ok = 0, d.ids = ids, d.order = order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos, d.experts = p->experts;
+    return cn_gemv_launch(d, stream, "cn_moe_nvfp4 (down)");
+}
+
+}  // namespace
+
+extern "C" int cn_moe_nvfp4_experts(void* plan, const unsigned long long* table_gu, const unsigned long long* table_up,
+                                    const unsigned long long* table_dn, const float* gs_gu, const float* gs_up, const float* gs_dn,
+                                    const int32_t* ids, const void* x, float* eo, const unsigned long long* eo_ptrs, int combos, int x_div,
+                                    float limit, int dtype, cn_stream_t stream) {
+    MoePlan* p = (MoePlan*)plan;
+    if (!p) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_experts: null plan");
+    if (combos < 1 || combos > p->max_tokens * p->topk) CN_FAIL(CN_ERR_LIMIT, "cn_moe_nvfp4_experts: %d combos, the plan holds %d", combos, p->max_tokens * p->topk);
+    if (x_div < 1) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_experts: x_div %d", x_div);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_experts: dtype %d is neither CN_F32 nor CN_BF16", dtype);
+    if (!eo && !eo_ptrs) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_experts: no output");
+    return routed_experts(p, table_gu, table_up, table_dn, gs_gu, gs_up, gs_dn, ids, x, eo, eo_ptrs, combos, x_div, limit, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int cn_moe_nvfp4_shared_begin(void* plan, const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs,
+                                         const void* x, int tokens, float limit, int dtype, cn_stream_t stream) {
+    MoePlan* p = (MoePlan*)plan;
+    if (!p || !shared_gate || !shared_up || !shared_down || !shared_gs) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_shared_begin: null argument");
+    if (tokens < 1 || tokens > p->max_tokens) CN_FAIL(CN_ERR_LIMIT, "cn_moe_nvfp4_shared_begin: %d tokens, the plan holds %d", tokens, p->max_tokens);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_shared_begin: dtype %d is neither CN_F32 nor CN_BF16", dtype);
+    const int rc = shared_branch(p, shared_gate, shared_up, shared_down, shared_gs, x, tokens, limit, dtype, (cudaStream_t)stream);
+    p->shared_pending = true;  // also after a failure: the side stream was forked and must be joined
+    return rc;
+}
+
+extern "C" int cn_moe_nvfp4_finish(void* plan, const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs,
+                                   const float* sgate, const int32_t* ids, const float* wts, const unsigned long long* table, const void* x,
+                                   const float* eo, void* y, int tokens, float limit, int dtype, cn_stream_t stream_) {
+    MoePlan* p = (MoePlan*)plan;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!p) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_finish: null plan");
+    if (tokens < 1 || tokens > p->max_tokens) CN_FAIL(CN_ERR_LIMIT, "cn_moe_nvfp4_finish: %d tokens, the plan holds %d", tokens, p->max_tokens);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_finish: dtype %d is neither CN_F32 nor CN_BF16", dtype);
+    const float* shared = nullptr;
+    int rc = CN_OK;
+    if (p->shared_pending) {
+        p->shared_pending = false;
+        CN_CUDA(cudaStreamWaitEvent(stream, p->join, 0));
+        shared = p->ys;
+    } else if (shared_gate) {
+        rc = shared_branch(p, shared_gate, shared_up, shared_down, shared_gs, x, tokens, limit, dtype, stream);
+        CN_CUDA(cudaStreamWaitEvent(stream, p->join, 0));
+        shared = p->ys;
+    }
+    if (rc != CN_OK) return rc;
+    return cn_moe_combine(eo, wts, ids, table, shared, sgate, y, tokens, p->hidden, p->topk, p->experts, dtype, stream_);
+}
+
 extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, const unsigned long long* table_up,
                                 const unsigned long long* table_dn, const float* gs_gu, const float* gs_up, const float* gs_dn,
                                 const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs,
@@ -201,55 +303,14 @@ extern "C" int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, 
     if (dtype != CN_F32 && dtype != CN_BF16 && dtype != CN_BF16_IN_F32_OUT) CN_FAIL(CN_ERR_SHAPE, "cn_moe_nvfp4_run: dtype %d", dtype);
     const int ydtype = dtype == CN_BF16 ? CN_BF16 : CN_F32;  // expert-parallel partial sums leave in f32
     if (dtype == CN_BF16_IN_F32_OUT) dtype = CN_BF16;
-    const int combos = tokens * p->topk;
-    // shared expert on every token, up to 8 rows per pass, on the side stream; whatever happens after the fork,
-    // the side stream is joined again before this call returns (a capture of the caller's stream stays valid)
     const float* shared = nullptr;
     int rc = CN_OK;
     if (shared_gate) {
-        CN_CUDA(cudaEventRecord(p->fork, stream));
-        CN_CUDA(cudaStreamWaitEvent(p->side, p->fork, 0));
-        const size_t es = dtype == CN_BF16 ? 2 : 4;
-        for (int t0 = 0; t0 < tokens && rc == CN_OK; t0 += CN_MAX_M) {
-            const int m = tokens - t0 < CN_MAX_M ? tokens - t0 : CN_MAX_M;
-            GemvCall g = {};
-            g.w0 = shared_gate, g.w1 = shared_up, g.gs0 = shared_gs, g.gs1 = shared_gs + 1, g.x = (const char*)x + (size_t)t0 * p->hidden * es;
-            g.y = p->hs + (size_t)t0 * p->shared_inter, g.rows = p->shared_inter, g.k = p->hidden, g.m = m, g.ldy = p->shared_inter;
-            g.limit = limit, g.dtype = dtype, g.out_f32 = 1;
-            rc = cn_gemv_launch(g, p->side, "cn_moe_nvfp4_run (shared gate/up)");
-            if (rc != CN_OK) break;
-            GemvCall s = {};
-            s.w0 = shared_down, s.gs0 = shared_gs + 2, s.x = p->hs + (size_t)t0 * p->shared_inter, s.y = p->ys + (size_t)t0 * p->hidden;
-            s.rows = p->hidden, s.k = p->shared_inter, s.m = m, s.ldy = p->hidden, s.dtype = CN_F32, s.out_f32 = 1, s.x_f16_ok = 0;
-            rc = cn_gemv_launch(s, p->side, "cn_moe_nvfp4_run (shared down)");
-        }
-        CN_CUDA(cudaEventRecord(p->join, p->side));
+        rc = shared_branch(p, shared_gate, shared_up, shared_down, shared_gs, x, tokens, limit, dtype, stream);
         shared = p->ys;
     }
-    // Combos sorted by expert keep the CTAs that read one expert's matrices next to each other in launch order. With
-    // few combos most CTAs of the step are resident at once and L2 serves a second reader anyway: no sort, one launch
-    // less on the critical path (measured with top-10 of 512 experts: 10 % faster unsorted at 8 and 16 tokens, even at
-    // 32, 1 % slower at 64).
-    const int32_t* order = nullptr;
-    if (combos > 320) {
-        if (rc == CN_OK) rc = cn_moe_sort(ids, p->order, combos, p->experts, stream_);
-        order = p->order;
-    }
-    if (rc == CN_OK) {
-        // routed gate|up + activation: h[c] = act(gate_e x_t, up_e x_t), c = t * topk + j
-        GemvCall a = {};
-        a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
-        a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = order, a.tab0 = table_gu, a.tab1 = table_up;
-        a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = p->topk, a.combos = combos, a.experts = p->experts;
-        rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4_run (gate/up)");
-    }
-    if (rc == CN_OK) {
-        // routed down: eo[c] = down_e h[c]
-        GemvCall d = {};
-        d.gs0 = gs_dn, d.x = p->h, d.y = p->eo, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
-        d.x_f16_ok = 0, d.ids = ids, d.order = order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos, d.experts = p->experts;
-        rc = cn_gemv_launch(d, stream, "cn_moe_nvfp4_run (down)");
-    }
+    if (rc == CN_OK)
+        rc = routed_experts(p, table_gu, table_up, table_dn, gs_gu, gs_up, gs_dn, ids, x, p->eo, nullptr, tokens * p->topk, p->topk, limit, dtype, stream);
     if (shared) CN_CUDA(cudaStreamWaitEvent(stream, p->join, 0));
     if (rc != CN_OK) return rc;
     return cn_moe_combine(p->eo, wts, ids, table_dn, shared, sgate, y, tokens, p->hidden, p->topk, p->experts, ydtype, stream_);

@@ -593,16 +593,22 @@ extern "C" int cn_mul1_ffn(void* plan, const unsigned long long* ptrs, const voi
 extern "C" int cn_moe_combine(const float* eo, const float* wts, const int32_t* ids, const unsigned long long* table, const float* shared,
                               const float* sgate, void* y, int tokens, int hidden, int topk, int experts, int dtype, cn_stream_t stream);
 
-extern "C" int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared, const void* x,
-                               void* y, int tokens, int topk, int experts, float limit, int dtype, cn_stream_t stream) {
+extern "C" int cn_moe_mul1_experts(void* plan, const unsigned long long* table, const int32_t* ids, const void* x, float* eo, int combos, int x_div,
+                                   int experts, float limit, int dtype, cn_stream_t stream) {
     Mul1Plan* p = (Mul1Plan*)plan;
-    const int combos = tokens * topk;
-    if (int rc = check_run(p, combos, 1, "cn_moe_mul1_run")) return rc;
-    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_run: dtype %d is neither CN_F32 nor CN_BF16", dtype);
+    if (int rc = check_run(p, combos, 1, "cn_moe_mul1_experts")) return rc;
+    if (x_div < 1 || !eo) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_experts: x_div %d, eo %p", x_div, (void*)eo);
+    if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_experts: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     cudaStream_t st = (cudaStream_t)stream;
     CN_CUDA(cn_launch_pdl(mul1_gather_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->ptrs, combos, experts));
     CN_CUDA(cudaGetLastError());
-    if (int rc = mul1_ffn(p, p->ptrs, x, p->eo, combos, 1, topk, limit, dtype, 1, st)) return rc;
+    return mul1_ffn(p, p->ptrs, x, eo, combos, 1, x_div, limit, dtype, 1, st);
+}
+
+extern "C" int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared, const void* x,
+                               void* y, int tokens, int topk, int experts, float limit, int dtype, cn_stream_t stream) {
+    Mul1Plan* p = (Mul1Plan*)plan;
+    if (int rc = cn_moe_mul1_experts(plan, table, ids, x, p ? p->eo : nullptr, tokens * topk, topk, experts, limit, dtype, stream)) return rc;
     return cn_moe_combine(p->eo, wts, ids, table, shared, nullptr, y, tokens, p->hidden, topk, experts, dtype, stream);
 }
 

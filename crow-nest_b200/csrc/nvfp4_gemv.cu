@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(NTHREADS, (MP <= 2 ? 4 : 1)) nvfp4_gemv_kernel
         if (!w0) return;  // the expert is not resident here: nothing to read or write
         w1 = p.tab1 ? (const uint8_t*)p.tab1[e] : (p.fused_up_rows > 0 ? w0 + (size_t)p.fused_up_rows * row_bytes : nullptr);
         xbase += (size_t)(c / p.x_div) * p.k * (XT == 1 ? 2 : 4);
-        ybase += (size_t)c * p.ldy * ((XT == 1 && !p.out_f32) ? 2 : 4);
+        ybase = p.yptrs ? (char*)p.yptrs[c] : ybase + (size_t)c * p.ldy * ((XT == 1 && !p.out_f32) ? 2 : 4);
     }
     const bool gu = w1 != nullptr;
 
@@ -555,7 +555,7 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.w0 = (const uint8_t*)a.w0, p.w1 = (const uint8_t*)a.w1, p.gs0 = a.gs0, p.gs1 = a.gs1 ? a.gs1 : a.gs0, p.x = a.x, p.y = a.y;
     p.rows = rows, p.k = k, p.m = m, p.ldy = a.ldy, p.limit = a.limit, p.tx = tx, p.stages = stages, p.out_f32 = a.out_f32;
     p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
-    p.experts = a.experts;
+    p.experts = a.experts, p.yptrs = a.yptrs;
     const int gy = routed ? a.combos : 1;
     if (a.dtype == CN_BF16) return mode == 1 ? launch_m<1, 1>(p, mp, rt, grid, gy, smem, stream) : launch_m<1, 0>(p, mp, rt, grid, gy, smem, stream);
     return mode == 1 ? launch_m<0, 1>(p, mp, rt, grid, gy, smem, stream) : launch_m<0, 0>(p, mp, rt, grid, gy, smem, stream);

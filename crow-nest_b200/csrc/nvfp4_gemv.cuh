@@ -22,6 +22,7 @@ struct GemvCall {
     const unsigned long long* tab1;
     int fused_up_rows, x_div, combos;
     int experts;  // entries of the tables (0 = unknown: ids are trusted); an id beyond them skips the combo
+    const unsigned long long* yptrs;  // routed form: output row address per combo (null: y + combo * ldy); may name peer memory
 };
 
 int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who);
@@ -52,6 +53,7 @@ struct GemvParams {
     int fused_up_rows;               // > 0: up = gate + fused_up_rows rows of the same slab
     int x_div;
     int experts;  // entries of tab0 / tab1 (0 = unknown); ids outside 0..experts-1 skip the combo
+    const unsigned long long* yptrs;  // output row address per combo (null: y + combo * ldy)
     int red_depth;  // multi-row tensor-core kernel: tile-sum slots in flight
     int ksplit;     // 2: launched as two-CTA clusters, each CTA of a pair over half of K (one activation row only)
 };

@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         if (!w0) return;
         w1 = p.tab1 ? (const uint8_t*)p.tab1[e] : (p.fused_up_rows > 0 ? w0 + (size_t)p.fused_up_rows * row_bytes : nullptr);
         xbase += (size_t)(c / p.x_div) * p.k * 2;
-        ybase += (size_t)c * p.ldy * (p.out_f32 ? 4 : 2);
+        ybase = p.yptrs ? (char*)p.yptrs[c] : ybase + (size_t)c * p.ldy * (p.out_f32 ? 4 : 2);
     }
     const bool gu = w1 != nullptr;
 
@@ -586,7 +586,7 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.ids = a.ids, p.order = a.order, p.tab0 = a.tab0, p.tab1 = a.tab1, p.fused_up_rows = a.fused_up_rows, p.x_div = a.x_div;
     p.red_depth = red_depth;
     p.ksplit = ksplit;
-    p.experts = a.experts;
+    p.experts = a.experts, p.yptrs = a.yptrs;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, (unsigned)(routed ? a.combos : 1));
     cfg.blockDim = dim3(NTHREADS);

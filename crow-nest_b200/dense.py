@@ -56,9 +56,7 @@ class PeerExchange:
 
     def __init__(self, vectors, rank, world, device, group=None):
         """vectors: {name: elements}, bf16, one row; every vector's length divides by `world`."""
-        import ctypes as C
-        import torch.distributed as dist
-        from ._lib import check, lib
+        from .peer import PeerBuffer
         self.rank, self.world = rank, world
         self.off, at = {}, 0
         for name, n in vectors.items():
@@ -68,37 +66,8 @@ class PeerExchange:
         for name in vectors:
             self.flag_off[name] = at
             at += 64
-        self.buf = torch.zeros(at, dtype=torch.uint8, device=device)
-        # every step below is collective: a rank whose export or open fails still takes part, and all ranks raise together
-        handle, offset, err = C.create_string_buffer(64), C.c_size_t(0), None
-        try:
-            check(lib().cn_peer_export(self.buf.data_ptr(), handle, C.byref(offset)))
-        except CrownestError as e:
-            err = str(e)
-        everyone = [None] * world
-        dist.all_gather_object(everyone, (bytes(handle.raw), int(offset.value), err), group=group)
-        self.bases = (C.c_void_p * world)()
-        self.opened = []
-        if not any(e for _, _, e in everyone):
-            for r, (h, o, _) in enumerate(everyone):
-                if r == rank:
-                    self.bases[r] = self.buf.data_ptr()
-                    continue
-                p = C.c_void_p()
-                try:
-                    check(lib().cn_peer_open(h, o, C.byref(p)))
-                except CrownestError as e:
-                    err = str(e)
-                    break
-                self.bases[r] = p.value
-                self.opened.append((p.value, o))
-        errs = [None] * world
-        dist.all_gather_object(errs, err, group=group)
-        torch.cuda.synchronize()
-        dist.barrier(group=group)  # every buffer is zeroed and open before the first exchange
-        bad = [e for e in errs if e] + [e for _, _, e in everyone if e]
-        if bad:
-            raise CrownestError("peer exchange unavailable: " + bad[0])
+        self.mem = PeerBuffer(at, rank, world, device, group)
+        self.buf, self.bases = self.mem.buf, self.mem.bases
 
     def vector(self, name, n):
         """The local copy of a vector as a [1][n] bf16 tensor."""

@@ -91,6 +91,33 @@ class GpuMoePlan:
                                      ids.data_ptr(), wts.data_ptr(), x.data_ptr(), y.data_ptr(), tokens, float(limit), dt, _stream()))
         return y
 
+    def experts_only(self, w: GpuMoeWeights, ids, x, eo=None, eo_ptrs=None, x_div=1, limit=0.0):
+        """Routed gate|up and down over ids.numel() combos (cn_moe_nvfp4_experts): combo c reads row c // x_div of x and
+        writes f32 row c of `eo`, or to the device address eo_ptrs[c]."""
+        combos = ids.numel()
+        dt = CN_BF16 if x.dtype == torch.bfloat16 else CN_F32
+        check(lib().cn_moe_nvfp4_experts(self.handle, _ptr(w.table_gu), _ptr(w.table_up), _ptr(w.table_dn), _ptr(w.gs_gu), _ptr(w.gs_up),
+                                         _ptr(w.gs_dn), ids.data_ptr(), x.data_ptr(), _ptr(eo), _ptr(eo_ptrs), combos, x_div, float(limit), dt,
+                                         _stream()))
+        return eo
+
+    def shared_begin(self, w: GpuMoeWeights, x, limit=0.0):
+        """Enqueue the shared expert now, beside what follows on the current stream; the next finish() joins it."""
+        dt = CN_BF16 if x.dtype == torch.bfloat16 else CN_F32
+        check(lib().cn_moe_nvfp4_shared_begin(self.handle, _ptr(w.shared[0]), _ptr(w.shared[1]), _ptr(w.shared[2]), _ptr(w.shared_gs), x.data_ptr(),
+                                              x.shape[0], float(limit), dt, _stream()))
+
+    def finish(self, w: GpuMoeWeights, ids, wts, x, eo, y=None, limit=0.0, sgate=None, table=None):
+        """Shared expert on x and the weighted sum of the expert outputs `eo` [tokens * topk][hidden] f32 (cn_moe_nvfp4_finish)."""
+        tokens = x.shape[0]
+        if y is None:
+            y = torch.empty_like(x)
+        dt = CN_BF16 if x.dtype == torch.bfloat16 else CN_F32
+        sh = w.shared or (None, None, None)
+        check(lib().cn_moe_nvfp4_finish(self.handle, _ptr(sh[0]), _ptr(sh[1]), _ptr(sh[2]), _ptr(w.shared_gs), _ptr(sgate), ids.data_ptr(),
+                                        wts.data_ptr(), _ptr(table), x.data_ptr(), eo.data_ptr(), y.data_ptr(), tokens, float(limit), dt, _stream()))
+        return y
+
     def run(self, w: GpuMoeWeights, logits, x, y=None, router="softmax", bias=None, scale=1.0, limit=0.0, sgate=None):
         """route + experts (GpuMoePlan::run, engine/src/glm5_moe.rs:709)."""
         if router == "softmax":

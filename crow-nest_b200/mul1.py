@@ -75,6 +75,12 @@ class Mul1Plan:
                                     x.data_ptr(), y.data_ptr(), tokens, topk, int(table.numel()), float(limit), _dt(x), _stream()))
         return y
 
+    def experts_only(self, table, ids, x, eo, x_div=1, limit=0.0):
+        """eo[c] (f32 [combos][hidden]) = FFN of expert ids[c] on row c // x_div of x (cn_moe_mul1_experts)."""
+        check(lib().cn_moe_mul1_experts(self.handle, table.data_ptr(), ids.data_ptr(), x.data_ptr(), eo.data_ptr(), ids.numel(), x_div,
+                                        int(table.numel()), float(limit), _dt(x), _stream()))
+        return eo
+
     def free(self):
         if self.handle:
             check(lib().cn_mul1_plan_destroy(self.handle))

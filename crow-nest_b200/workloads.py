@@ -4,23 +4,20 @@ expert, softmax top-10) and the MUL1 (EXL3, K = 3) routed step (hidden 4096, int
 experts, top-4).
 
 Expert parallelism: expert e lives on rank e // (experts / world); the other entries of a rank's
-pointer table are null, which the routed kernels skip (the reference's residency contract,
-engine/src/kernels_mul1.cu:118-119). One step with B tokens per rank:
-  dispatch  all-gather of the token rows and router logits (every rank sees all world * B tokens;
-            the router is replicated and bit-identical on every rank),
-  compute   routed experts of this rank over all tokens -> f32 partial sums,
-  combine   reduce-scatter (sum) of the partial sums: each rank receives its own B rows,
-  shared    the shared expert (replicated) on the rank's own rows, added after the combine.
+pointer table are null. One step with B tokens per rank (all-to-all over NVLink peer memory, `peer.EpExchange`):
+  route     every rank routes its own B tokens,
+  dispatch  the activation row of every (token, expert) combo goes to the rank that holds the expert, and only there,
+  compute   a rank runs its experts over the rows it received (B * topk / world combos on average, whatever the
+            world size), the down projection storing each result straight into the token's home rank,
+  return    the ranks meet; every rank now holds the expert outputs of its own combos,
+  combine   weighted sum in pick order plus the shared expert (replicated), on the token's home rank: the same sum,
+            in the same order, as on one GPU.
 """
 import torch
 
 from . import moe, mul1, ops
 from .dense import _rand_nvfp4_device
-
-
-def ep_owner(expert, experts, world):
-    """Rank that holds `expert`: contiguous blocks of experts / world."""
-    return expert // (experts // world)
+from .peer import EpExchange, ep_owner
 
 
 class MoeDecode:
@@ -44,46 +41,29 @@ class MoeDecode:
               _rand_nvfp4_device(hidden, shared_inter, gen, device)]
         one = torch.ones(1, dtype=torch.float32, device=device)
         self.shared_fp4 = [ops.Fp4(sh[0], one, shared_inter, hidden), ops.Fp4(sh[1], one, shared_inter, hidden), ops.Fp4(sh[2], one, hidden, shared_inter)]
-        self.w = moe.GpuMoeWeights(hidden, inter, experts, 1.0, 1.0, gate_up=gu, down=dn, shared=sh if world == 1 else None,
-                                   shared_gs=[1.0, 1.0, 1.0] if world == 1 else None, device=device)
-        all_tokens = tokens * world
-        self.plan = moe.GpuMoePlan(hidden, inter, experts, topk, max_tokens=all_tokens, shared_inter=shared_inter if world == 1 else 0)
+        self.w = moe.GpuMoeWeights(hidden, inter, experts, 1.0, 1.0, gate_up=gu, down=dn, shared=sh, shared_gs=[1.0, 1.0, 1.0], device=device)
+        self.plan = moe.GpuMoePlan(hidden, inter, experts, topk, max_tokens=tokens, shared_inter=shared_inter)
         gen.manual_seed(seed * 100003 + experts + 1 + rank)
         self.x = torch.randn((tokens, hidden), device=device, generator=gen).to(torch.bfloat16)
         self.logits = torch.randn((tokens, experts), device=device, generator=gen)
         self.y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device)
         if world > 1:
-            self.x_all = torch.empty((all_tokens, hidden), dtype=torch.bfloat16, device=device)
-            self.logits_all = torch.empty((all_tokens, experts), dtype=torch.float32, device=device)
-            self.part = torch.empty((all_tokens, hidden), dtype=torch.float32, device=device)
-            self.own = torch.empty((tokens, hidden), dtype=torch.float32, device=device)
-            self.hs = torch.empty((tokens, shared_inter), dtype=torch.bfloat16, device=device)
-            self.ys = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device)
-            self.side = torch.cuda.Stream(device=device)  # the shared expert runs beside dispatch, experts and combine
-        self.launches_per_step = 5 + 2 * ((tokens + 7) // 8)  # router, sort, gate/up, down, combine, shared gate/up + down per 8 rows
+            self.ep = EpExchange(tokens, topk, hidden, experts, rank, world, device, group)
+            # the rows a rank receives are one combo each: a second plan with top-1 geometry over all inbox slots
+            self.plan_in = moe.GpuMoePlan(hidden, inter, experts, 1, max_tokens=self.ep.slots)
+        self.launches_per_step = 5 + 2 * ((tokens + 7) // 8) + (5 if world > 1 else 0)
 
     def step(self):
         """One decode step over this rank's tokens; returns y [tokens][hidden] bf16."""
         if self.world == 1:
             return self.plan.run(self.w, self.logits, self.x, self.y)
-        import torch.distributed as dist
-        # shared expert on the rank's own rows, 8 at a time (the kernels take up to 8 activation rows): it needs x only,
-        # so it goes on a side stream that forks here and joins before the final sum (also under graph capture)
-        cur = torch.cuda.current_stream()
-        self.side.wait_stream(cur)
-        with torch.cuda.stream(self.side):
-            for t0 in range(0, self.tokens, 8):
-                t1 = min(t0 + 8, self.tokens)
-                ops.launch_gemv_gu(self.shared_fp4[0], self.shared_fp4[1], self.x[t0:t1], self.hs[t0:t1])
-                ops.launch_gemv(self.shared_fp4[2], self.hs[t0:t1], self.ys[t0:t1])
-        dist.all_gather_into_tensor(self.x_all, self.x, group=self.group)
-        dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.group)
-        ids, wts = moe.route_softmax_topk(self.logits_all, self.topk)
-        self.plan.experts_run(self.w, ids, wts, self.x_all, self.part, partial=True)
-        dist.reduce_scatter_tensor(self.own, self.part, op=dist.ReduceOp.SUM, group=self.group)
-        cur.wait_stream(self.side)
-        torch.add(self.own, self.ys, out=self.y)  # f32 sum, rounded to bf16 once
-        return self.y
+        ids, wts = moe.route_softmax_topk(self.logits, self.topk)
+        self.ids, self.wts = ids, wts
+        self.plan.shared_begin(self.w, self.x)  # beside dispatch, experts and return
+        self.ep.dispatch(ids, self.x)
+        self.plan_in.experts_only(self.w, self.ep.ids_in, self.ep.inbox_x, eo_ptrs=self.ep.out_ptrs, x_div=1)
+        self.ep.finish()
+        return self.plan.finish(self.w, ids, wts, self.x, self.ep.ret, self.y)
 
     def bytes_per_step(self, ids=None):
         """Algorithmic bytes over all ranks: every distinct routed expert once, the shared expert once, activations."""
@@ -126,31 +106,27 @@ class Mul1MoeDecode:
                 gen.manual_seed(seed * 100003 + 7 * e)
                 self.recs[e] = _rand_mul1_record(hidden, inter, K, gen, device)
         self.table = torch.tensor([0 if r is None else r.data_ptr() for r in self.recs], dtype=torch.int64, device=device)
-        all_tokens = tokens * world
-        self.plan = mul1.Mul1Plan(hidden, inter, K, slots=all_tokens * topk, tokens=1)
+        self.plan = mul1.Mul1Plan(hidden, inter, K, slots=tokens * topk * world, tokens=1)
         gen.manual_seed(seed * 100003 + 7 * experts + rank)
         self.x = (torch.randn((tokens, hidden), device=device, generator=gen) * 0.25).to(torch.bfloat16)
         self.logits = torch.randn((tokens, experts), device=device, generator=gen)
         self.y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=device)
         if world > 1:
-            self.x_all = torch.empty((all_tokens, hidden), dtype=torch.bfloat16, device=device)
-            self.logits_all = torch.empty((all_tokens, experts), dtype=torch.float32, device=device)
-            self.xf = torch.empty((all_tokens, hidden), dtype=torch.float32, device=device)
-            self.part = torch.empty((all_tokens, hidden), dtype=torch.float32, device=device)
-            self.own = torch.empty((tokens, hidden), dtype=torch.float32, device=device)
+            self.ep = EpExchange(tokens, topk, hidden, experts, rank, world, device, group)
+            self.eo = torch.empty((self.ep.slots, hidden), dtype=torch.float32, device=device)
+        self.launches_per_step = 11 + (6 if world > 1 else 0)
 
     def step(self):
+        ids, wts = moe.route_softmax_topk(self.logits, self.topk)
         if self.world == 1:
-            ids, wts = moe.route_softmax_topk(self.logits, self.topk)
             return self.plan.moe(self.table, ids, wts, self.x, y=self.y, limit=10.0)
-        import torch.distributed as dist
-        dist.all_gather_into_tensor(self.x_all, self.x, group=self.group)
-        dist.all_gather_into_tensor(self.logits_all, self.logits, group=self.group)
-        ids, wts = moe.route_softmax_topk(self.logits_all, self.topk)
-        self.xf.copy_(self.x_all)  # f32 in, f32 partial sums out
-        self.plan.moe(self.table, ids, wts, self.xf, y=self.part, limit=10.0)
-        dist.reduce_scatter_tensor(self.own, self.part, op=dist.ReduceOp.SUM, group=self.group)
-        self.y.copy_(self.own)
+        from ._lib import CN_BF16, check, lib
+        self.ids, self.wts = ids, wts
+        self.ep.dispatch(ids, self.x)
+        self.plan.experts_only(self.table, self.ep.ids_in, self.ep.inbox_x, self.eo, x_div=1, limit=10.0)
+        self.ep.finish(self.eo)
+        check(lib().cn_moe_combine(self.ep.ret.data_ptr(), wts.data_ptr(), ids.data_ptr(), None, None, None, self.y.data_ptr(), self.tokens,
+                                   self.hidden, self.topk, self.experts, CN_BF16, torch.cuda.current_stream().cuda_stream))
         return self.y
 
     def bytes_per_step(self):

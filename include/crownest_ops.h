@@ -167,6 +167,25 @@ int cn_moe_nvfp4_run(void* plan, const unsigned long long* table_gu, const unsig
                      const float* sgate, const int32_t* ids, const float* wts, const void* x, void* y, int tokens, float limit,
                      int dtype, cn_stream_t stream);
 
+/* The two halves of cn_moe_nvfp4_run for callers that put something between them (expert parallelism: the rows come from
+ * other ranks and the results go back to them). cn_moe_nvfp4_experts: routed gate|up + activation and routed down over
+ * `combos` rows, combo c reading activation row c / x_div of x and writing f32 row c of eo - or to the address eo_ptrs[c]
+ * when eo_ptrs != null (a row of any device-visible buffer, a peer GPU's included); ids[c] < 0, beyond the tables or with
+ * a null table entry skips the combo. The plan needs max_tokens * topk >= combos. cn_moe_nvfp4_finish: the shared expert
+ * on x (when given) and y[t] = shared[t] + sum_j wts[t][j] * eo[t * topk + j] over the plan's top-k, `table` as in
+ * cn_moe_combine (null: every combo counts). cn_moe_nvfp4_shared_begin enqueues the shared expert early, on the plan's
+ * side stream, so that it runs beside whatever the caller puts on `stream` next (an exchange between ranks); the next
+ * cn_moe_nvfp4_finish on the plan then joins it instead of computing it (its shared_* arguments are ignored). */
+int cn_moe_nvfp4_shared_begin(void* plan, const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs,
+                              const void* x, int tokens, float limit, int dtype, cn_stream_t stream);
+int cn_moe_nvfp4_experts(void* plan, const unsigned long long* table_gu, const unsigned long long* table_up,
+                         const unsigned long long* table_dn, const float* gs_gu, const float* gs_up, const float* gs_dn,
+                         const int32_t* ids, const void* x, float* eo, const unsigned long long* eo_ptrs, int combos, int x_div, float limit,
+                         int dtype, cn_stream_t stream);
+int cn_moe_nvfp4_finish(void* plan, const void* shared_gate, const void* shared_up, const void* shared_down, const float* shared_gs,
+                        const float* sgate, const int32_t* ids, const float* wts, const unsigned long long* table, const void* x,
+                        const float* eo, void* y, int tokens, float limit, int dtype, cn_stream_t stream);
+
 /* ---------------------------------------------------------------- NVFP4 GEMM (prefill / batched rows)
  * Y[t][n] = gs * sum_k X[t][k] * W[n][k] for any m >= 1 activation rows (meant for m > 8; up to 8 rows
  * cn_nvfp4_gemv streams the weights once and is faster), on tcgen05 tensor cores with the accumulator in
@@ -211,6 +230,11 @@ int cn_mul1_ffn(void* plan, const unsigned long long* ptrs, const void* x, void*
 int cn_moe_mul1_run(void* plan, const unsigned long long* table, const int32_t* ids, const float* wts, const float* shared,
                     const void* x, void* y, int tokens, int topk, int experts, float limit, int dtype, cn_stream_t stream);
 
+/* The expert half of cn_moe_mul1_run alone: eo[c] (f32 [combos][hidden], caller's buffer) = FFN of expert ids[c] on
+ * activation row c / x_div; the combine is cn_moe_combine. For expert parallelism (rows from other ranks). */
+int cn_moe_mul1_experts(void* plan, const unsigned long long* table, const int32_t* ids, const void* x, float* eo, int combos, int x_div,
+                        int experts, float limit, int dtype, cn_stream_t stream);
+
 /* The MUL1 GEMV of cn_mul1_gemv without a plan and without any allocation: for a caller that cannot
  * allocate device memory where it makes the call (a decode loop that must not hit the device-wide
  * synchronisation an allocation implies, a host that hands out all device memory at start-up, a
@@ -241,6 +265,29 @@ int cn_mul1_reconstruct(const void* trellis, void* w_out, int k, int n, int bits
  * f32 activations are rounded to f16 (11 bits) when staged; bf16 activations are exact. */
 int cn_fp8_gemv(const void* w, const float* scale, const void* x, void* y, int rows, int cols, int m, int ldy, int dtype,
                 cn_stream_t stream);
+
+/* ---------------------------------------------------------------- expert-parallel token exchange over peer memory
+ * No counterpart in the reference (single GPU); it stands where glm5_moe_gather / glm5_moe_combine
+ * (engine/src/kernels_glm5_moe.cu:101-156) gather rows for the expert kernels and sum their outputs. Expert e lives on rank
+ * e / (experts / world). Every rank holds one buffer of the same layout, opened by all peers (cn_peer_export / cn_peer_open),
+ * zero before the first use:
+ *   inbox_x    [world][cap][hidden] bf16, inbox_meta [world][cap] {i32, i32}, ret [cap][hidden] f32, flags cn_ep_flag_bytes()
+ * cap = the most combos a rank sends per step (its tokens x top-k; the same on every rank).
+ * cn_ep_dispatch: all-to-all dispatch. Pushes activation row c / topk (bf16) of every local combo c to the rank that owns
+ * expert ids[c] (order = the combos sorted by expert, from cn_moe_sort), meets the other ranks, and fills for the routed
+ * kernels ids_in [world * cap] (expert of every inbox slot, -1 = empty) and out_ptrs [world * cap] (where that slot's
+ * result goes: row c of the source rank's ret). The inbox rows are then the x of cn_moe_nvfp4_experts / cn_moe_mul1_experts
+ * with x_div = 1.
+ * cn_ep_return: all-to-all return. With eo != null copies result row i of eo [world * cap][hidden] f32 to out_ptrs[i] first
+ * (not needed when the expert kernel stored there itself); then meets the other ranks: afterwards ret holds the f32 output of
+ * every local combo, ready for cn_moe_combine / cn_moe_nvfp4_finish with the rank's own ids and weights - the same sum in
+ * the same order as on one GPU. Two launches per call at most, graph-capturable, bounded waits; world <= 8. */
+size_t cn_ep_flag_bytes(void);
+int cn_ep_dispatch(const void* const* peer_bases, int rank, int world, int cap, int hidden, size_t inbox_x, size_t inbox_meta, size_t ret,
+                   size_t flags, const int32_t* ids, const int32_t* order, const void* x, int combos, int topk, int experts,
+                   int32_t* ids_in, unsigned long long* out_ptrs, cn_stream_t stream);
+int cn_ep_return(const void* const* peer_bases, int rank, int world, int cap, int hidden, size_t inbox_x, size_t inbox_meta, size_t ret,
+                 size_t flags, const float* eo, const int32_t* ids_in, const unsigned long long* out_ptrs, cn_stream_t stream);
 
 /* ---------------------------------------------------------------- tensor-parallel exchange over peer memory
  * No counterpart in the reference (it is single-GPU). Every rank holds one buffer of the same layout; a rank

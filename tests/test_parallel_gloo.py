@@ -1,6 +1,6 @@
 """The multi-rank host logic on CPU: two gloo ranks. Tensor parallel: row ranges + all-gather give the
-one-rank result bit for bit. Expert parallel: every expert has one owner, and the ranks' partial sums
-add up to the one-rank layer output."""
+one-rank result bit for bit. Expert parallel: every expert has one owner, and the all-to-all dispatch and return
+with the device's placement rule reproduce the one-rank layer output bit for bit."""
 import os
 import socket
 import sys
@@ -48,46 +48,64 @@ def _tp_worker(rank, world, port, out):
 
 
 def _ep_worker(rank, world, port, out):
+    """The all-to-all of the expert-parallel step with the placement rule of cn_ep_dispatch (`peer.ep_slots`): every rank
+    routes its own tokens, sends each combo's row to the expert's owner in slot order, the owner computes and sends the
+    result back to row `combo` of the source, and the source combines in pick order - bit for bit the one-rank result."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import oracle
-    from crownest_b200 import synth, workloads
-    hidden, inter, experts, k, tokens_per_rank = 256, 256, 8, 3, 2
+    from crownest_b200 import peer, synth
+    hidden, inter, experts, k, tokens = 256, 256, 8, 3, 3
     rng = np.random.default_rng(5)
     rb = hidden // 64 * 36
     gu = [synth.nvfp4_matrix(2 * inter, hidden, rng) for _ in range(experts)]
     dn = [synth.nvfp4_matrix(hidden, inter, rng) for _ in range(experts)]
-    # dispatch: every rank's rows and logits, gathered (the same generator on both ranks stands in for the exchange)
-    x_all = rng.standard_normal((world * tokens_per_rank, hidden)).astype(np.float32)
-    logits_all = rng.standard_normal((world * tokens_per_rank, experts)).astype(np.float32)
-    mine_x = torch.from_numpy(x_all[rank * tokens_per_rank:(rank + 1) * tokens_per_rank].copy())
-    got = torch.empty((world * tokens_per_rank, hidden))
-    dist.all_gather_into_tensor(got, mine_x)
-    assert np.array_equal(got.numpy(), x_all)
-    ids, wts = oracle.route_softmax_topk(logits_all, k)
-    tokens = x_all.shape[0]
+    x_all = rng.standard_normal((world, tokens, hidden)).astype(np.float32)
+    logits_all = rng.standard_normal((world, tokens, experts)).astype(np.float32)
+    x, logits = x_all[rank], logits_all[rank]
+    ids, wts = oracle.route_softmax_topk(logits, k)
+    cap = tokens * k
 
-    def expert_out(c):
-        e = ids.reshape(-1)[c]
+    def ffn(e, row):
         g, u = gu[e][: inter * rb], gu[e][inter * rb:]
-        return oracle.nvfp4_ffn(g, u, dn[e], hidden, inter, [0.25, 0.25, 0.5], x_all[c // k: c // k + 1], threads=1, path=0)[0]
+        return oracle.nvfp4_ffn(g, u, dn[e], hidden, inter, [0.25, 0.25, 0.5], row[None], threads=1, path=0)[0]
 
-    ye = np.zeros((tokens * k, hidden), np.float32)
-    w_local = wts.copy()
-    for c in range(tokens * k):
-        if workloads.ep_owner(int(ids.reshape(-1)[c]), experts, world) == rank:
-            ye[c] = expert_out(c)
-        else:
-            w_local.reshape(-1)[c] = 0.0  # a null table entry: the combo adds nothing on this rank
-    part = torch.from_numpy(oracle.moe_acc_combo(ye, w_local, None))
-    dist.all_reduce(part)  # combine (gloo has no reduce-scatter: all-reduce, then the rank's own rows)
-    own = part[rank * tokens_per_rank:(rank + 1) * tokens_per_rank].numpy()
-    ye_full = np.stack([expert_out(c) for c in range(tokens * k)])
-    ref = oracle.moe_acc_combo(ye_full, wts, None)[rank * tokens_per_rank:(rank + 1) * tokens_per_rank]
-    err = np.linalg.norm(own - ref) / np.linalg.norm(ref)
-    owners = [workloads.ep_owner(e, experts, world) for e in range(experts)]
-    ok = err < 1e-6 and sorted(set(owners)) == list(range(world)) and all(owners.count(r) == experts // world for r in range(world))
-    out.put((rank, "ok" if ok else f"ep combine rel err {err}, owners {owners}"))
+    # dispatch: per destination the rows in slot order, padded to cap, with {expert, source combo}
+    slots = peer.ep_slots(ids, experts, world)
+    send_x = torch.zeros((world, cap, hidden))
+    send_meta = torch.full((world, cap, 2), -1, dtype=torch.int64)
+    for r, combos in enumerate(slots):
+        for slot, c in enumerate(combos):
+            e = int(ids.reshape(-1)[c])
+            assert peer.ep_owner(e, experts, world) == r
+            send_x[r, slot] = torch.from_numpy(x[c // k])
+            send_meta[r, slot] = torch.tensor([e, int(c)])
+    recv_x, recv_meta = torch.empty_like(send_x), torch.empty_like(send_meta)
+    dist.all_to_all_single(recv_x, send_x)
+    dist.all_to_all_single(recv_meta, send_meta)
+    # the owner's experts over its inbox; every result goes back to row `source combo` of the source rank
+    back = torch.zeros((world, cap, hidden))
+    mine = 0
+    for s_rank in range(world):
+        for slot in range(cap):
+            e, c = (int(v) for v in recv_meta[s_rank, slot])
+            if e < 0:
+                continue
+            assert peer.ep_owner(e, experts, world) == rank
+            back[s_rank, c] = torch.from_numpy(ffn(e, recv_x[s_rank, slot].numpy()))
+            mine += 1
+    ret = torch.empty_like(back)
+    dist.all_to_all_single(ret, back)
+    eo = ret.sum(0).numpy()  # every combo has exactly one owner: one non-zero contribution per row
+    got = oracle.moe_acc_combo(eo, wts, None)
+    ref = oracle.moe_acc_combo(np.stack([ffn(int(ids.reshape(-1)[c]), x[c // k]) for c in range(cap)]), wts, None)
+    counts = torch.tensor([mine])
+    dist.all_reduce(counts)
+    owners = [peer.ep_owner(e, experts, world) for e in range(experts)]
+    ok = (np.array_equal(got.view(np.uint32), ref.view(np.uint32)) and int(counts) == world * cap
+          and all(owners.count(r) == experts // world for r in range(world))
+          and all(list(ids.reshape(-1)[c]) == sorted(ids.reshape(-1)[c]) for c in slots))
+    out.put((rank, "ok" if ok else f"expert-parallel exchange differs from the one-rank result (combos handled {int(counts)})"))
     dist.destroy_process_group()
 
 
