@@ -1,15 +1,20 @@
-"""Benchmark of the quantized GEMV hot path: the NVFP4 dense decode layer stack (27B-shaped, 64
-layers, M = 1) on N B200 GPUs of one node.
+"""Benchmark of the quantized GEMV / MoE decode hot path on N B200 GPUs of one node.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload dense|gemv|moe|mul1|gemm] ...
 
-A step is one token through the whole stack (4 GEMV launches per layer). `value` is the algorithmic
-bytes of a step (every weight byte once + activations) over the device time of a step, inputs
-resident in HBM; `e2e` is the same through the host-facing call with pinned host buffers copied in
-and out every step. One JSON line on stdout (rank 0).
+Default workload (the headline): the NVFP4 dense decode layer stack (27B-shaped, 64 layers, M = 1). A step is one
+token through the whole stack (4 GEMV launches per layer, one CUDA-graph replay). `value` = algorithmic bytes of a
+step (every weight byte once + activations) / device time of a step, inputs resident in HBM; `e2e` = the same through
+the host-facing call with pinned host buffers copied in and out every step. The same JSON line carries a `moe` block:
+the routed-expert decode steps of the MoE configurations measured in the same process (on N > 1 GPUs expert-parallel,
+all-to-all over peer memory), with both scaling definitions. One JSON line on stdout (rank 0).
+
+Timing: W >= 3 warm-up steps, then blocks of K steps between two CUDA events (as many blocks as half a second needs);
+ms_per_step is the median block, the spread is reported. Every multi-rank figure is the max over ranks.
 """
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -24,13 +29,14 @@ UNIT = "GB/s"
 # DRAM bytes moved per algorithmic byte by the M = 1 kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
 # captured gate/up launch (103.4 MB) over its algorithmic bytes (100.3 MB); the capture is summarised under profiles/
 TRAFFIC_RATIO = 1.031
+MIN_TIMED_S = 0.5
 
 
-def measured_peak():
+def measured_peak(key="hbm_gbs", fallback=6650.0):
     try:
-        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))[key]), "measured"
     except Exception:
-        return 6650.0, "fallback"
+        return fallback, "fallback"
 
 
 class ClockSampler:
@@ -71,13 +77,104 @@ class ClockSampler:
                     if v.lower().startswith("active"):
                         reasons.add(name)
         mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": sorted(reasons),
+        # under load: the upper half of the samples (the sampler also sees the idle gaps between the parts of the run)
+        load = sm[len(sm) // 2:]
+        return {"sm_mhz": load[len(load) // 2] if load else None, "sm_max_mhz": mx[0] if mx else None, "reasons": sorted(reasons),
                 "samples": len(sm)}
 
 
-def cpu_baseline_run(host_layers, threads, seconds_budget, m=1):
-    """The CPU checker's NVFP4 GEMV (AVX2 arm of the reference's operation order, rows split over
-    `threads`) over whole layers, rotating over the given distinct layers. Returns (GB/s, passes)."""
+class Timer:
+    """Blocks of `steps` steps between two CUDA events on the current stream, repeated until MIN_TIMED_S is covered
+    (at most 50 blocks); barrier + synchronize on both sides of the whole region; max over ranks per block."""
+
+    def __init__(self, world):
+        self.world = world
+
+    def barrier(self):
+        import torch
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def run(self, step, steps, warmup):
+        import torch
+        for _ in range(warmup):
+            step()
+        self.barrier()
+        # one probe block sizes the repeat count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        self.barrier()
+        probe = max(e0.elapsed_time(e1) * 1e-3, 1e-6)
+        blocks = max(1, min(50, int(math.ceil(MIN_TIMED_S / probe))))
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([blocks], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            blocks = int(t.item())
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(blocks)]
+        self.barrier()
+        for a, b in ev:
+            a.record()
+            for _ in range(steps):
+                step()
+            b.record()
+        self.barrier()
+        ms = torch.tensor([a.elapsed_time(b) for a, b in ev], dtype=torch.float64, device="cuda")
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        ms = sorted(ms.tolist())
+        return {"ms_per_step": ms[len(ms) // 2] / steps, "blocks": blocks, "ms_per_step_min": ms[0] / steps, "ms_per_step_max": ms[-1] / steps}
+
+    def wall(self, step, steps):
+        """End-to-end: wall clock over `steps` host-facing calls (each synchronises), max over ranks."""
+        import torch
+        for _ in range(2):
+            step()
+        self.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        self.barrier()
+        s = time.perf_counter() - t0
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([s], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            s = float(t.item())
+        return s / steps
+
+
+# ---------------------------------------------------------------------------------------------- CPU baselines
+def _median_calls(fn, budget_s, min_calls=24, max_calls=200):
+    """median seconds of `fn(i)` over at least `min_calls` calls (more while the budget lasts)"""
+    fn(0)  # page faults, worker start
+    ts, t_all = [], 0.0
+    i = 0
+    while i < max_calls and (i < min_calls or t_all < budget_s):
+        t0 = time.perf_counter()
+        fn(i)
+        dt = time.perf_counter() - t0
+        ts.append(dt)
+        t_all += dt
+        i += 1
+        if t_all > 3 * budget_s and i >= 3:
+            break
+    ts.sort()
+    return ts[len(ts) // 2], len(ts)
+
+
+def cpu_dense_baseline(host_layers, m, budget_s=10.0):
+    """The CPU checker's NVFP4 GEMV (AVX2 arm of the reference's operation order, rows split over the threads, parked
+    worker pool) over whole layers, rotating over distinct layers (each 186 MB, beyond any L3): thread counts 1 / 8 /
+    all, median of >= 24 layer passes each where the budget allows - the reference's own method
+    (engine/src/cpu_nvfp4.rs:729-777)."""
     import numpy as np
     import oracle
     rng = np.random.default_rng(0)
@@ -87,24 +184,60 @@ def cpu_baseline_run(host_layers, threads, seconds_budget, m=1):
             xs.setdefault(k, rng.standard_normal((m, k)).astype(np.float32))
     path = 1 if oracle.lib().cn_o_have_avx2() else 0
     layer_bytes = sum(w.size for w, _, _ in host_layers[0].values())
-    t_total, passes = 0.0, 0
-    # one untimed pass: page faults, thread start
-    for name, (w, rows, k) in host_layers[0].items():
-        oracle.nvfp4_gemv(w, rows, k, 1.0, xs[k], threads=threads, path=path)
-    while t_total < seconds_budget and passes < 64:
-        mats = host_layers[passes % len(host_layers)]
-        t0 = time.perf_counter()
-        for name, (w, rows, k) in mats.items():
-            oracle.nvfp4_gemv(w, rows, k, 1.0, xs[k], threads=threads, path=path)
-        t_total += time.perf_counter() - t0
-        passes += 1
-    return (layer_bytes * passes / t_total / 1e9 if t_total > 0 else 0.0), passes
+    cores = os.cpu_count() or 1
+    sweep = {}
+    for threads in sorted({1, min(8, cores), cores}):
+        def one(i, threads=threads):
+            for _, (w, rows, k) in host_layers[i % len(host_layers)].items():
+                oracle.nvfp4_gemv(w, rows, k, 1.0, xs[k], threads=threads, path=path)
+        share = budget_s * (0.5 if threads == cores else 0.25)
+        med, calls = _median_calls(one, share, min_calls=24 if threads > 1 else 4)
+        sweep[str(threads)] = {"gbs": layer_bytes / med / 1e9, "calls": calls}
+    return {"value": sweep[str(cores)]["gbs"], "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"median of {sweep[str(cores)]['calls']} passes over one whole layer ({layer_bytes} B: qkv, o, gate, up, down), "
+                      f"{len(host_layers)} distinct layers rotated, AVX2 arm, parked worker pool",
+            "threads_sweep": sweep}
 
 
+def cpu_moe_baseline(kind, wl, budget_s=6.0):
+    """The routed-expert step on the host cores: every (token, expert) combo of rank 0's batch through the CPU
+    checker's expert FFN (cn_o_nvfp4_ffn / cn_o_mul1_expert_ffn), all threads inside each FFN, median of the passes."""
+    import numpy as np
+    import oracle
+    import torch
+    from crownest_b200 import moe
+    cores = os.cpu_count() or 1
+    ids, _ = moe.route_softmax_topk(wl.logits, wl.topk)
+    ids = ids.cpu().numpy().reshape(-1)
+    x = wl.x.float().cpu().numpy()
+    picked = sorted(set(int(e) for e in ids))
+    if kind == "moe":
+        rb = wl.hidden // 64 * 36
+        gu = {e: wl.w.keep[0][e].cpu().numpy() for e in picked}
+        dn = {e: wl.w.keep[3][e].cpu().numpy() for e in picked}
+        sh = [t.cpu().numpy() for t in wl.w.shared]
+
+        def one(_):
+            for c, e in enumerate(ids):
+                oracle.nvfp4_ffn(gu[e][: wl.inter * rb], gu[e][wl.inter * rb:], dn[e], wl.hidden, wl.inter, [1.0, 1.0, 1.0],
+                                 x[c // wl.topk: c // wl.topk + 1], threads=cores, path=1)
+            oracle.nvfp4_ffn(sh[0], sh[1], sh[2], wl.hidden, wl.shared_inter, [1.0, 1.0, 1.0], x, threads=cores, path=1)
+    else:
+        recs = {e: wl.recs[e].cpu().numpy() for e in picked}
+
+        def one(_):
+            for c, e in enumerate(ids):
+                oracle.mul1_expert_ffn(recs[e], wl.hidden, wl.inter, wl.K, x[c // wl.topk: c // wl.topk + 1], limit=10.0, threads=cores)
+    med, calls = _median_calls(one, budget_s, min_calls=3, max_calls=24)
+    return {"value": wl.tokens / med, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"median of {calls} passes over the step's {len(ids)} (token, expert) FFNs ({len(picked)} distinct experts), all threads per FFN"}
+
+
+# ---------------------------------------------------------------------------------------------- reference arm
 def reference_arm(args, rank):
-    """`--impl reference`: the reference's CPU implementation of the path (its Rust source cannot be
-    built here - no Rust toolchain - so the C port under oracle/ stands in, kind "port"), all host
-    threads, each step one layer of the stack's shapes (186 MB of NVFP4)."""
+    """`--impl reference`: the reference's CPU implementation of the path (its Rust source cannot be built here - no
+    Rust toolchain - so the C port under oracle/ stands in, kind "port"), all host threads, each step one layer of the
+    stack's shapes (186 MB of NVFP4)."""
     if rank != 0:
         return
     import numpy as np
@@ -134,18 +267,19 @@ def reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def moe_arm(args, rank, world, local):
-    """`--workload moe` / `mul1`: the routed-expert decode step (BASELINE configs 2 and 3), `--tokens` rows per rank,
-    experts placed expert-parallel over the ranks (weak scaling: the global batch grows with the ranks)."""
+# ---------------------------------------------------------------------------------------------- MoE parts
+MOE_SHAPES = {"moe": "hidden 2048, 512 experts, inter 512, shared expert 512, softmax top-10, NVFP4",
+              "mul1": "hidden 4096, 64 experts, inter 1536, top-4, EXL3 MUL1 K=3"}
+
+
+def moe_measure(kind, tokens, rank, world, local, steps, warmup, cpu=False, e2e=True):
+    """One routed-expert decode configuration: `tokens` rows per rank, experts spread over the ranks (all-to-all dispatch
+    and return over peer memory when world > 1). Returns the figures of one block of the JSON line (rank 0) or None."""
     import torch
     import torch.distributed as dist
-    from crownest_b200 import _lib, workloads
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    _lib.lib()
-    cls = workloads.MoeDecode if args.workload == "moe" else workloads.Mul1MoeDecode
-    wl = cls(args.tokens, device=f"cuda:{local}", rank=rank, world=world, group=None)
+    from crownest_b200 import _lib, moe, workloads
+    cls = workloads.MoeDecode if kind == "moe" else workloads.Mul1MoeDecode
+    wl = cls(tokens, device=f"cuda:{local}", rank=rank, world=world, group=None)
     x_host = wl.x.cpu().pin_memory()
     y_host = torch.empty_like(x_host).pin_memory()
     st = torch.cuda.Stream()
@@ -156,67 +290,163 @@ def moe_arm(args, rank, world, local):
         with torch.cuda.graph(graph, stream=st):
             wl.step()
     torch.cuda.synchronize()
+    tm = Timer(world)
+    t = tm.run(graph.replay, steps, warmup)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        graph.replay()
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
+    def host_step():
         wl.x.copy_(x_host, non_blocking=True)
         graph.replay()
         y_host.copy_(wl.y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    clocks = sampler.stop() if rank == 0 else None
-    nbytes, distinct = wl.bytes_per_step()
-    t = torch.tensor([ms, e2e_s, float(nbytes), float(distinct)], dtype=torch.float64, device="cuda")
+
+    e2e_s = tm.wall(host_step, steps) if e2e else None
+    # algorithmic bytes of the whole job: every distinct routed expert once (an expert lives on one rank), the shared
+    # expert once per rank, activations in and out
+    ids, _ = moe.route_softmax_topk(wl.logits, wl.topk)
+    distinct = torch.tensor([float(torch.unique(ids).numel())], device="cuda")
     if world > 1:
-        mx = t.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(mx[0]), float(mx[1])
+        allids = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(allids, ids)
+        distinct = torch.tensor([float(torch.unique(torch.cat(allids)).numel())], device="cuda")
+    distinct = int(distinct.item())
+    if kind == "moe":
+        per_expert = 3 * wl.inter * wl.hidden // 64 * 36
+        nbytes = distinct * per_expert + world * (3 * wl.shared_inter * wl.hidden // 64 * 36) + tokens * world * (2 * wl.hidden * 2 + wl.experts * 4)
+    else:
+        from crownest_b200 import mul1
+        nbytes = distinct * mul1.record_bytes(wl.hidden, wl.inter, wl.K) + tokens * world * (2 * wl.hidden * 2 + wl.experts * 4)
+    status = _lib.device_status()
+    out = None
     if rank == 0:
-        ms_step = ms / args.steps
-        toks = args.tokens * world
         peak, peak_kind = measured_peak()
-        gbs = nbytes / (ms_step * 1e-3) / 1e9
-        shape = ("hidden 2048, 512 experts, inter 512, shared expert 512, softmax top-10, NVFP4" if args.workload == "moe" else
-                 "hidden 4096, 64 experts, inter 1536, top-4, EXL3 MUL1 K=3")
-        line = {"metric": "moe_decode_tok_s", "value": toks / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"routed-expert decode step ({shape}), {args.tokens} tokens per rank", "parallelism": f"ep{world}" if world > 1 else "none",
-                           "l2": "the expert set changes with the routing; weights of one step (%.0f MB on rank 0) fit L2, so the working set is flushed "
-                                 "only by its own size at larger batches" % (nbytes / 1e6), "launch": "CUDA graph replay",
-                           "distinct_experts_rank0_tokens": distinct},
-                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind,
-                             "kernel": "nvfp4_gemv_m1_kernel (routed form)" if args.workload == "moe" else "mul1_gemv_kernel",
-                             "note": "algorithmic bytes = distinct experts of rank 0's tokens x expert bytes + shared expert + activations"},
-                "e2e": {"value": toks / (e2e_s / args.steps), "unit": "tok/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-                "gpu_launches": args.steps * getattr(wl, "launches_per_step", 8), "clocks": clocks, "device_status": _lib.device_status()}
+        ms = t["ms_per_step"]
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out = {"workload": f"routed-expert decode step ({MOE_SHAPES[kind]})", "tokens_per_rank": tokens, "global_batch": tokens * world,
+               "tok_s": tokens * world / (ms * 1e-3), "ms_per_step": ms, "blocks": t["blocks"], "ms_per_step_min": t["ms_per_step_min"],
+               "ms_per_step_max": t["ms_per_step_max"], "distinct_experts": distinct, "algorithmic_bytes": nbytes,
+               "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peak, "unit": "GB/s", "frac": gbs / world / peak, "peak_kind": peak_kind,
+                            "scope": "per GPU", "kernel": "nvfp4_gemv_m1_kernel (routed form)" if kind == "moe" else "mul1_gemv_kernel"},
+               "parallelism": f"ep{world}: all-to-all dispatch / return over peer memory" if world > 1 else "none",
+               "launches_per_step": wl.launches_per_step, "device_status": status}
+        if e2e_s is not None:
+            out["e2e_tok_s"] = tokens * world / e2e_s
+            out["h2d_bytes_per_step"] = x_host.numel() * 2
+            out["d2h_bytes_per_step"] = y_host.numel() * 2
+        if cpu and world == 1:
+            out["cpu_baseline"] = cpu_moe_baseline(kind, wl)
+    del graph, wl
+    torch.cuda.empty_cache()
+    return out
+
+
+def moe_block(rank, world, local, steps, warmup, cpu):
+    """The MoE figures that ride on the default line. Weak scaling: 64 (NVFP4) / 16 (MUL1) tokens per rank, the global
+    batch grows with the ranks. Strong scaling: a global batch of 64 split over the ranks."""
+    block = {"scaling_definitions": {"weak": "fixed tokens per rank; tok/s over the global batch", "strong": "global batch 64 split over the ranks"}}
+    block["nvfp4_weak_64_per_rank"] = moe_measure("moe", 64, rank, world, local, steps, warmup, cpu=cpu)
+    if world > 1:
+        block["nvfp4_strong_global_64"] = moe_measure("moe", max(1, 64 // world), rank, world, local, steps, warmup, e2e=False)
+    block["mul1_weak_16_per_rank"] = moe_measure("mul1", 16, rank, world, local, steps, warmup, cpu=cpu)
+    return block
+
+
+def moe_arm(args, rank, world, local):
+    """`--workload moe` / `mul1`: one routed-expert configuration as the line's own metric, `--tokens` rows per rank."""
+    out = moe_measure(args.workload, args.tokens, rank, world, local, args.steps, args.warmup, cpu=not args.no_cpu_baseline)
+    if rank == 0:
+        line = {"metric": "moe_decode_tok_s", "value": out["tok_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": out["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"{out['workload']}, {args.tokens} tokens per rank", "parallelism": out["parallelism"],
+                           "l2": "the expert set changes with the routing; the weights of one step (%.0f MB) are larger than L2 from 64 tokens on" % (out["algorithmic_bytes"] / 1e6),
+                           "launch": "CUDA graph replay", "distinct_experts": out["distinct_experts"]},
+                "roofline": dict(out["roofline"], traffic=None), "blocks": out["blocks"],
+                "e2e": {"value": out.get("e2e_tok_s"), "unit": "tok/s", "h2d_bytes_per_step": out.get("h2d_bytes_per_step"), "d2h_bytes_per_step": out.get("d2h_bytes_per_step")},
+                "gpu_launches": args.steps * out["blocks"] * out["launches_per_step"], "device_status": out["device_status"]}
+        if "cpu_baseline" in out:
+            line["cpu_baseline"] = out["cpu_baseline"]
         print(json.dumps(line), flush=True)
-    leave(world, graph)
+    leave(world)
 
 
+# ---------------------------------------------------------------------------------------------- single GEMV
+def gemv_arm(args, rank, world, local):
+    """`--workload gemv`: one NVFP4 GEMV shape (default: the single 4096 x 4096 matrix at M = 1) the reference's way
+    (engine/src/glm5_model.rs:2414-2432): distinct weight copies of at least 512 MiB in all rotated launch by launch, so
+    that nothing is served from L2, and at least 64 launches per graph replay between the two events."""
+    import numpy as np
+    import torch
+    from crownest_b200 import _lib, dense, ops, synth
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    rows, k, m = args.rows, args.cols, args.m
+    nb = rows * k // 64 * 36
+    copies = max(2, int(math.ceil(512 * 2 ** 20 / nb)))
+    per_graph = max(64, copies)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+    one = torch.ones(1, device=dev)
+    ws = [ops.Fp4(dense._rand_nvfp4_device(rows, k, gen, dev), one, rows, k) for _ in range(copies)]
+    x_host = torch.randn((m, k), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+    y = torch.empty((m, rows), dtype=torch.bfloat16, device=dev)
+    y_host = torch.empty((m, rows), dtype=torch.bfloat16).pin_memory()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        ops.launch_gemv(ws[0], x, y)
+        st.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            for i in range(per_graph):
+                ops.launch_gemv(ws[i % copies], x, y)
+    tm = Timer(1)
+    sampler = ClockSampler(local)
+    sampler.start()
+    t = tm.run(graph.replay, args.steps, args.warmup)
+    i = [0]
+
+    def host_step():
+        x.copy_(x_host, non_blocking=True)
+        ops.launch_gemv(ws[i[0] % copies], x, y)
+        i[0] += 1
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_s = tm.wall(host_step, max(args.steps, 50))
+    clocks = sampler.stop()
+    bytes_launch = nb + 4 + m * (k + rows) * 2
+    us = t["ms_per_step"] * 1e3 / per_graph
+    gbs = bytes_launch / us / 1e3
+    peak, peak_kind = measured_peak()
+    line = {"metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"single NVFP4 GEMV [{rows} x {k}], M={m}; a step = {per_graph} launches", "activations": "bf16 in/out, f32 accumulate",
+                       "l2": f"{copies} distinct weight copies ({copies * nb / 2 ** 20:.0f} MiB) rotated launch by launch: larger than L2",
+                       "launch": f"CUDA graph replay of {per_graph} launches"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "nvfp4_gemv_m1_kernel", "bytes_per_launch": bytes_launch, "us_per_launch": us},
+            "blocks": t["blocks"], "ms_per_step_min": t["ms_per_step_min"], "ms_per_step_max": t["ms_per_step_max"],
+            "e2e": {"value": bytes_launch / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                    "note": "one launch per host call"},
+            "gpu_launches": args.steps * t["blocks"] * per_graph, "clocks": clocks, "device_status": _lib.device_status()}
+    if not args.no_cpu_baseline:
+        import oracle
+        cores = os.cpu_count() or 1
+        hw = [w.w.cpu().numpy() for w in ws[:min(copies, 24)]]
+        xf = x_host.float().numpy()
+        sweep = {}
+        for threads in sorted({1, min(8, cores), cores}):
+            med, calls = _median_calls(lambda j: oracle.nvfp4_gemv(hw[j % len(hw)], rows, k, 1.0, xf, threads=threads, path=1), 3.0)
+            sweep[str(threads)] = {"gbs": nb / med / 1e9, "calls": calls}
+        line["cpu_baseline"] = {"value": sweep[str(cores)]["gbs"], "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"median of {sweep[str(cores)]['calls']} calls rotating over {len(hw)} weight copies ({len(hw) * nb / 2 ** 20:.0f} MiB)",
+                                "threads_sweep": sweep}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------- batched GEMM
 def gemm_arm(args, rank, world, local):
-    """`--workload gemm`: the batched NVFP4 GEMM (BASELINE config 4): W [17408 x 5120] then [5120 x 17408], --m rows,
-    output columns split over the ranks with an all-gather (tensor parallel). A step = both GEMMs once."""
+    """`--workload gemm`: the batched NVFP4 GEMM (W [17408 x 5120] then [5120 x 17408], --m rows), output columns split over
+    the ranks with an all-gather (tensor parallel). A step = both GEMMs once."""
     import torch
     import torch.distributed as dist
     from crownest_b200 import _lib, dense, ops
@@ -234,7 +464,6 @@ def gemm_arm(args, rank, world, local):
         gen.manual_seed(100 * c + rank)
         ups.append(ops.Fp4(dense._rand_nvfp4_device(inter // world, hidden, gen, dev), one, inter // world, hidden))
         downs.append(ops.Fp4(dense._rand_nvfp4_device(hidden // world, inter, gen, dev), one, hidden // world, inter))
-    gen.manual_seed(7)
     x_host = torch.randn((m, hidden), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
     x = x_host.to(dev)
     h = torch.empty((m, inter), dtype=torch.bfloat16, device=dev)
@@ -243,8 +472,11 @@ def gemm_arm(args, rank, world, local):
     yp = torch.empty((m, hidden // world), dtype=torch.bfloat16, device=dev) if world > 1 else y
     y_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
     ws = torch.empty(ops.gemm_workspace_bytes(inter, m), dtype=torch.uint8, device=dev)
+    it = [0]
 
-    def step(i):
+    def step():
+        i = it[0]
+        it[0] += 1
         ops.launch_gemm(ups[i % ncopy], x, hp, workspace=ws)
         if world > 1:
             dense.gather_rows(hp, h, m, world)
@@ -252,55 +484,45 @@ def gemm_arm(args, rank, world, local):
         if world > 1:
             dense.gather_rows(yp, y, m, world)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    def host_step():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
-    barrier()
+    tm = Timer(world)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        x.copy_(x_host, non_blocking=True)
-        step(i)
-        y_host.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-    barrier()
-    e2e_s = time.perf_counter() - t0
+    t = tm.run(step, args.steps, args.warmup)
+    e2e_s = tm.wall(host_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1])
     if rank == 0:
         flops = 2.0 * m * hidden * inter * 2
-        ms_step = ms / args.steps
+        ms_step = t["ms_per_step"]
         tf = flops / (ms_step * 1e-3) / 1e12
-        try:
-            peak, kind = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]), "measured (bf16 GEMM, burst)"
-        except Exception:
-            peak, kind = 1590.0, "fallback"
-        line = {"metric": "nvfp4_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        peak, kind = measured_peak("bf16_tflops", 1590.0)
+        line = {"metric": "nvfp4_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 x f16 -> f32", "data": "synthetic",
                 "config": {"workload": f"nvfp4 GEMM pair [17408 x 5120] and [5120 x 17408], M={m}", "parallelism": f"tp{world} column split + all-gather" if world > 1 else "none",
                            "l2": "three weight copies rotated (300 MB per rank) plus the activations: larger than L2", "launch": "plain launches"},
-                "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s", "frac": tf / world / peak, "traffic": None, "peak_kind": kind,
+                "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s", "frac": tf / world / peak, "traffic": None,
+                             "peak_kind": kind + " (bf16 GEMM, burst)", "scope": "per GPU",
                              "kernel": "nvfp4_gemm_tc5_kernel", "flops_per_launch": flops / 2 / world, "us_per_launch": ms_step * 1e3 / 2,
                              "hbm_gbs": (2 * hidden * inter // 64 * 36 / world + 2.0 * m * (hidden + inter) * 2) / (ms_step * 1e-3) / 1e9},
-                "e2e": {"value": flops / (e2e_s / args.steps) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-                "gpu_launches": args.steps * 4, "clocks": clocks, "device_status": _lib.device_status()}
+                "blocks": t["blocks"], "ms_per_step_min": t["ms_per_step_min"], "ms_per_step_max": t["ms_per_step_max"],
+                "e2e": {"value": flops / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+                "gpu_launches": args.steps * t["blocks"] * 4, "clocks": clocks, "device_status": _lib.device_status()}
+        if world == 1 and not args.no_cpu_baseline:
+            import numpy as np
+            import oracle
+            cores = os.cpu_count() or 1
+            rows_s, toks = 1024, min(m, 8)  # a bounded sample: 1024 output rows of the first matrix for 8 tokens
+            wsub = ups[0].w[: rows_s * (hidden // 64 * 36)].cpu().numpy()
+            xf = x_host[:toks].float().numpy()
+            med, calls = _median_calls(lambda j: oracle.nvfp4_gemv(wsub, rows_s, hidden, 1.0, xf, threads=cores, path=1), 3.0)
+            line["cpu_baseline"] = {"value": 2.0 * toks * rows_s * hidden / med / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"median of {calls} calls of the CPU GEMV over {rows_s} rows of W [17408 x 5120] for {toks} tokens (its token tile)"}
         print(json.dumps(line), flush=True)
     leave(world)
 
@@ -320,32 +542,58 @@ def leave(world, *holders):
     os._exit(0)
 
 
-def trace(msg):
-    """Progress lines on stderr when CN_BENCH_TRACE is set (to see where a multi-rank run stops)."""
-    if os.environ.get("CN_BENCH_TRACE"):
-        print(f"[bench rank {os.environ.get('RANK', 0)} +{time.perf_counter() - T0:.1f}s] {msg}", file=sys.stderr, flush=True)
-
-
-T0 = time.perf_counter()
+def exchange_check(rank, world, local):
+    """N >= 2: the peer-memory exchange of the tensor-parallel stack against the NCCL all-gather path on a three-layer
+    stack (same weights, same input): every replicated vector must agree bit for bit, replay after replay."""
+    import torch
+    import torch.distributed as dist
+    from crownest_b200 import _lib, dense
+    res = "ok"
+    try:
+        a = dense.DenseStack(layers=3, device=f"cuda:{local}", seed=5, rank=rank, world=world, exchange="nccl")
+        b = dense.DenseStack(layers=3, device=f"cuda:{local}", seed=5, rank=rank, world=world, exchange="peer")
+        if b.peer is None:
+            res = "peer exchange unavailable: " + getattr(b, "peer_error", "?")
+        else:
+            x = torch.randn((1, a.hidden), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+            a.x.copy_(x), b.x.copy_(x)
+            a.run_layers(1)
+            b.capture(1)
+            for it in range(2):
+                b.graph.replay()
+                torch.cuda.synchronize()
+                for name in ("q", "o", "h", "y"):
+                    if not torch.equal(getattr(a, name).view(torch.int16), getattr(b, name).view(torch.int16)):
+                        res = f"replay {it}: vector {name} differs from the all-gather path"
+            if _lib.device_status() != 0:
+                res = "device status"
+    except Exception as e:  # noqa: BLE001 - reported in the line
+        res = f"{type(e).__name__}: {e}"
+    flag = torch.tensor([0 if res == "ok" else 1], device="cuda")
+    dist.all_reduce(flag)
+    torch.cuda.synchronize()
+    return res if int(flag.item()) == 0 or res != "ok" else "a peer rank reported a mismatch"
 
 
 def main():
-    if os.environ.get("CN_BENCH_TRACE"):
-        import faulthandler
-        faulthandler.dump_traceback_later(int(os.environ["CN_BENCH_TRACE"]), exit=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     # "--act-rows": the spelling to use under torch.distributed.run, whose own parser takes "--m" for an abbreviation
     ap.add_argument("--m", "--act-rows", dest="m", type=int, default=1, help="activation rows per step (1 decode, 4 = MTP verify)")
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--impl", default="crownest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-moe", action="store_true", help="dense workload: leave the MoE block out of the line")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="tensor parallel: slices pushed over peer memory, or NCCL all-gather")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mul1", "gemm"], help="dense = the headline (config 1); moe / mul1 = configs 2 / 3")
+    ap.add_argument("--fuse", default="none", choices=["none", "layer", "token"], help="dense, one GPU, M = 1: projections as persistent chains (one launch per layer / token)")
+    ap.add_argument("--workload", default="dense", choices=["dense", "gemv", "moe", "mul1", "gemm"],
+                    help="dense = the headline (layer stack); gemv = one matrix (default 4096 x 4096); moe / mul1 = routed experts; gemm = batched rows")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
+    ap.add_argument("--rows", type=int, default=4096, help="gemv: output rows")
+    ap.add_argument("--cols", type=int, default=4096, help="gemv: k")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -354,98 +602,84 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.workload == "gemm":
         return gemm_arm(args, rank, world, local)
-    if args.workload != "dense":
-        return moe_arm(args, rank, world, local)
+    if args.workload == "gemv":
+        return gemv_arm(args, rank, world, local)
 
     import torch
     import torch.distributed as dist
     from crownest_b200 import _lib, dense
     torch.cuda.set_device(local)
-    group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     _lib.lib()  # fail loudly when the CUDA library is missing: there is no fallback
-    trace("process group up")
+    if args.workload != "dense":
+        return moe_arm(args, rank, world, local)
 
-    stack = dense.DenseStack(layers=args.layers, device=f"cuda:{local}", seed=0, rank=rank, world=world, group=group, max_m=args.m,
+    stack = dense.DenseStack(layers=args.layers, device=f"cuda:{local}", seed=0, rank=rank, world=world, group=None, max_m=args.m,
                              exchange=args.exchange)
     m = args.m
+    if args.fuse != "none" and world == 1 and m == 1:
+        stack.fuse(args.fuse)
     gen = torch.Generator(device="cpu").manual_seed(1)
     x_host = torch.randn((m, stack.hidden), generator=gen).to(torch.bfloat16).pin_memory()
     y_host = torch.empty((m, stack.hidden), dtype=torch.bfloat16).pin_memory()
     stack.x[:m].copy_(x_host)
-    # the whole step (256 launches, with their all-gathers when tensor parallel) replays as one CUDA graph
+    # the whole step (256 launches, with their exchanges when tensor parallel) replays as one CUDA graph
     use_graph = not args.eager
     if use_graph:
         stack.capture(m)
     step = (lambda: stack.graph.replay()) if use_graph else (lambda: stack.run_layers(m))
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    trace("captured" if use_graph else "eager")
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    trace("warm")
+    tm = Timer(world)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    t = tm.run(step, args.steps, args.warmup)
     # end to end through the host-facing call: pinned host in, pinned host out, every step
-    for _ in range(2):
-        stack.decode_step(x_host, y_host)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        stack.decode_step(x_host, y_host)
-    barrier()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = tm.wall(lambda: stack.decode_step(x_host, y_host), args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1])
     status = _lib.device_status()
-
+    line = None
     if rank == 0:
         bytes_step = stack.bytes_per_step(m)
-        ms_step = ms / args.steps
+        ms_step = t["ms_per_step"]
         value = bytes_step / (ms_step * 1e-3) / 1e9
         peak, peak_kind = measured_peak()
         per_gpu = value / world
+        fused = stack.chains is not None
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic",
                 "config": {"workload": f"nvfp4 dense decode stack 27B-shaped (hidden 5120, qkv 7168, inter 17408, {stack.layers} layers), M={m}",
                            "activations": "bf16 in/out, f32 accumulate", "parallelism": (f"tp{world} row split + " + ("peer-memory exchange" if stack.peer is not None else "NCCL all-gather")) if world > 1 else "none",
                            "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (bytes_step / 1e9),
-                           "launch": "CUDA graph replay" if use_graph else "eager launches", "tokens_per_s": m / (ms_step * 1e-3)},
-                "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "traffic": TRAFFIC_RATIO * bytes_step / world / stack.launches_per_step if m == 1 else None,
-                             "traffic_note": "dram read+write bytes of one ncu capture of the gate/up launch (profiles/), scaled to the average launch by bytes",
-                             "peak_kind": peak_kind, "kernel": "nvfp4_gemv_m1_kernel" if m == 1 else "nvfp4_gemv_mma_kernel", "bytes_per_launch": bytes_step / world / stack.launches_per_step,
-                             "us_per_launch": ms_step * 1e3 / stack.launches_per_step},
-                "e2e": {"value": bytes_step / (e2e_s / args.steps) / 1e9, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
-                        "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_s / args.steps * 1e3},
-                "gpu_launches": stack.launches_per_step * args.steps, "clocks": clocks, "device_status": status}
+                           "launch": ("CUDA graph replay" if use_graph else "eager launches") + (f", projections fused per {args.fuse}" if fused else ""),
+                           "tokens_per_s": m / (ms_step * 1e-3)},
+                "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "scope": "per GPU",
+                             "traffic": TRAFFIC_RATIO * bytes_step / world / (4 * stack.layers) if m == 1 else None,
+                             "traffic_note": "dram read+write bytes of one ncu capture of the gate/up launch (profiles/), scaled to the average projection by bytes",
+                             "peak_kind": peak_kind, "kernel": "nvfp4_gemv_seq_kernel" if fused else "nvfp4_gemv_m1_kernel", "bytes_per_launch": bytes_step / world / (4 * stack.layers),
+                             "us_per_launch": ms_step * 1e3 / (4 * stack.layers)},
+                "blocks": t["blocks"], "ms_per_step_min": t["ms_per_step_min"], "ms_per_step_max": t["ms_per_step_max"],
+                "e2e": {"value": bytes_step / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2,
+                        "d2h_bytes_per_step": y_host.numel() * 2, "ms_per_step": e2e_s * 1e3},
+                "gpu_launches": stack.launches_per_step * args.steps * t["blocks"], "clocks": clocks, "device_status": status}
         if world == 1 and not args.no_cpu_baseline:
             host_layers = [stack.host_copy(i) for i in range(min(3, stack.layers))]
-            threads = os.cpu_count() or 1
-            gbs, passes = cpu_baseline_run(host_layers, threads, 12.0, m)
-            line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": f"{passes} passes over whole layers ({host_layers and sum(w.size for w, _, _ in host_layers[0].values())} B each), "
-                                              f"{len(host_layers)} distinct layers rotated, AVX2 arm"}
+            line["cpu_baseline"] = cpu_dense_baseline(host_layers, m)
+    del stack
+    torch.cuda.empty_cache()
+    if world > 1:
+        chk = exchange_check(rank, world, local)
+        if rank == 0:
+            line["exchange_check"] = chk
+        torch.cuda.empty_cache()
+    if not args.no_moe:
+        block = moe_block(rank, world, local, max(10, args.steps // 2), args.warmup, cpu=not args.no_cpu_baseline)
+        if rank == 0:
+            line["moe"] = block
+    if rank == 0:
         print(json.dumps(line), flush=True)
-    leave(world, stack)
+    leave(world)
 
 
 if __name__ == "__main__":

@@ -70,6 +70,100 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int32_t* __rest
     }
 }
 
+// Sort the combos by expert and cut every expert's run into groups of up to four rows (one CTA of 1024 threads):
+//   order[]           the combos sorted by expert, stable; combos without a resident expert (id outside 0..E-1, or a
+//                     null entry of `tab`) last and in no group
+//   ga[] / counts[0]  positions (in order[]) of the one-row groups: an expert's single row, or the one left over after
+//                     its groups of four
+//   gb[], gbrows[] / counts[1]  first positions and row counts (2..4) of the other groups
+//   gd[], gdrows[] / counts[2]  the same runs cut into groups of one or two rows (for f32 activations, which take two
+//                     of the kernel's four row slots each: a high and a low f16 plane)
+// Placement is done by one warp walking the combos in order (match.any finds the lanes of a step that share an expert),
+// so the sort stays stable without ranking every combo against all others.
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ ids, const unsigned long long* __restrict__ tab, int n, int E,
+                                                         int32_t* __restrict__ order, int* __restrict__ ga, int* __restrict__ gb,
+                                                         int* __restrict__ gbrows, int* __restrict__ gd, int* __restrict__ gdrows,
+                                                         int* __restrict__ counts) {
+    extern __shared__ int sm[];  // [E + 1] counts, [E + 1] starts, [E + 1] running, [n] bins
+    int* cnt = sm;
+    int* start = sm + (E + 1);
+    int* run = sm + 2 * (E + 1);
+    int* bin = sm + 3 * (E + 1);
+    __shared__ int wsa[32], wsb[32], wsd[32];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int i = tid; i <= E; i += blockDim.x) cnt[i] = 0;
+    __syncthreads();
+    for (int c = tid; c < n; c += blockDim.x) {
+        const int e = ids[c];
+        const int b = (e < 0 || e >= E || (tab && tab[e] == 0ull)) ? E : e;
+        bin[c] = b;
+        atomicAdd(&cnt[b], 1);
+    }
+    __syncthreads();
+    // per expert: one-row groups and larger groups, then three exclusive prefix sums over the experts (rows, a, b)
+    const int per = (E + 1 + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int i0 = min(tid * per, E + 1), i1 = min(i0 + per, E + 1);
+    int rows = 0, na = 0, nb = 0, nd = 0;
+    for (int i = i0; i < i1; i++) {
+        const int k = cnt[i];
+        rows += k;
+        if (i < E) na += (k & 3) == 1, nb += (k >> 2) + ((k & 3) >= 2), nd += (k + 1) >> 1;
+    }
+    int ir = rows, ia = na, ib = nb, id = nd;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int vr = __shfl_up_sync(0xffffffffu, ir, o), va = __shfl_up_sync(0xffffffffu, ia, o), vb = __shfl_up_sync(0xffffffffu, ib, o);
+        const int vd = __shfl_up_sync(0xffffffffu, id, o);
+        if (lane >= o) ir += vr, ia += va, ib += vb, id += vd;
+    }
+    __shared__ int wsr[32];
+    if (lane == 31) wsr[wid] = ir, wsa[wid] = ia, wsb[wid] = ib, wsd[wid] = id;
+    __syncthreads();
+    if (wid == 0) {
+        int r = wsr[lane], a = wsa[lane], b = wsb[lane], d = wsd[lane];
+        const int r0 = r, a0 = a, b0 = b, d0 = d;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int vr = __shfl_up_sync(0xffffffffu, r, o), va = __shfl_up_sync(0xffffffffu, a, o), vb = __shfl_up_sync(0xffffffffu, b, o);
+            const int vd = __shfl_up_sync(0xffffffffu, d, o);
+            if (lane >= o) r += vr, a += va, b += vb, d += vd;
+        }
+        wsr[lane] = r - r0, wsa[lane] = a - a0, wsb[lane] = b - b0, wsd[lane] = d - d0;
+        if (lane == 31) counts[0] = a, counts[1] = b, counts[2] = d;
+    }
+    __syncthreads();
+    int pr = wsr[wid] + ir - rows, pa = wsa[wid] + ia - na, pb = wsb[wid] + ib - nb, pd = wsd[wid] + id - nd;
+    for (int i = i0; i < i1; i++) {
+        const int k = cnt[i];
+        start[i] = pr;
+        run[i] = pr;
+        if (i < E) {
+            for (int q = 0; q < (k >> 2); q++) gb[pb] = pr + 4 * q, gbrows[pb] = 4, pb++;
+            const int rem = k & 3, at = pr + (k & ~3);
+            if (rem == 1) ga[pa++] = at;
+            if (rem >= 2) gb[pb] = at, gbrows[pb] = rem, pb++;
+            for (int q = 0; q < k; q += 2) gd[pd] = pr + q, gdrows[pd] = k - q >= 2 ? 2 : 1, pd++;
+        }
+        pr += k;
+    }
+    __syncthreads();
+    if (wid == 0) {
+        for (int c0 = 0; c0 < n; c0 += 32) {
+            const int c = c0 + lane;
+            const int b = c < n ? bin[c] : -1 - lane;  // lanes beyond the end match nobody
+            const unsigned same = __match_any_sync(0xffffffffu, b);
+            if (c < n) {
+                const int base = run[b];
+                order[base + __popc(same & ((1u << lane) - 1u))] = c;
+            }
+            __syncwarp();
+            if (c < n && lane == __ffs(same) - 1) run[b] += __popc(same);
+            __syncwarp();
+        }
+    }
+}
+
 // y[t][c] = base + sum_j w[t][j] * eo[t*K + j][c], j in pick order; base = shared[t][c]
 // (times sigmoid(sgate[t]) when gated), 0 without a shared expert. A combo whose expert has no
 // local matrix contributes nothing.
@@ -119,6 +213,7 @@ struct MoePlan {
     float* hs;       // [max_tokens][shared inter <= inter_s]
     float* ys;       // [max_tokens][hidden]
     int32_t* order;  // [max_tokens * topk]
+    int* groups;     // [5 * max_tokens * topk + 8]: the group lists of moe_group_kernel and their three counts
     int shared_inter;
     // the shared expert does not depend on the routed experts until the combine: it is enqueued on a side stream
     // between two events (fork after the caller's earlier work, join before the combine), also under stream capture
@@ -168,6 +263,7 @@ extern "C" int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, 
     step(cudaMalloc(&p->hs, (size_t)max_tokens * (shared_inter > 0 ? shared_inter : 1) * sizeof(float)));
     step(cudaMalloc(&p->ys, (size_t)max_tokens * hidden * sizeof(float)));
     step(cudaMalloc(&p->order, combos * sizeof(int32_t)));
+    step(cudaMalloc(&p->groups, (5 * combos + 8) * sizeof(int)));
     step(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
     step(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
     step(cudaEventCreateWithFlags(&p->join, cudaEventDisableTiming));
@@ -182,7 +278,7 @@ extern "C" int cn_moe_nvfp4_plan_create(void** plan_out, int hidden, int inter, 
 extern "C" int cn_moe_nvfp4_plan_destroy(void* plan) {
     MoePlan* p = (MoePlan*)plan;
     if (!p) return CN_OK;
-    cudaFree(p->h), cudaFree(p->eo), cudaFree(p->hs), cudaFree(p->ys), cudaFree(p->order);
+    cudaFree(p->h), cudaFree(p->eo), cudaFree(p->hs), cudaFree(p->ys), cudaFree(p->order), cudaFree(p->groups);
     if (p->side) cudaStreamDestroy(p->side);
     if (p->fork) cudaEventDestroy(p->fork);
     if (p->join) cudaEventDestroy(p->join);
@@ -222,23 +318,55 @@ int shared_branch(MoePlan* p, const void* shared_gate, const void* shared_up, co
 int routed_experts(MoePlan* p, const unsigned long long* table_gu, const unsigned long long* table_up, const unsigned long long* table_dn,
                    const float* gs_gu, const float* gs_up, const float* gs_dn, const int32_t* ids, const void* x, float* eo,
                    const unsigned long long* eo_ptrs, int combos, int x_div, float limit, int dtype, cudaStream_t stream) {
-    // Combos sorted by expert keep the CTAs that read one expert's matrices next to each other in launch order. With
-    // few combos most CTAs of the step are resident at once and L2 serves a second reader anyway: no sort, one launch
-    // less on the critical path (measured with top-10 of 512 experts: 10 % faster unsorted at 8 and 16 tokens, even at
-    // 32, 1 % slower at 64). The sort is one CTA and ranks each combo among all others: left out for long lists too.
-    const int32_t* order = nullptr;
-    if (combos > 320 && combos <= 1024) {
-        if (int rc = cn_moe_sort(ids, p->order, combos, p->experts, (cn_stream_t)stream)) return rc;
-        order = p->order;
+    if (combos > 96 && combos >= 2 * p->experts) {
+        // At least two combo slots per expert (a long batch, or the inbox of an expert-parallel rank, whose few resident
+        // experts take all its rows): sort by expert, cut into groups of up to four rows of one expert, and stream every
+        // expert once per group (persistent CTAs over a device-side group list; empty slots cost nothing). One-row
+        // groups and larger groups are separate launches.
+        const size_t smem = (size_t)(3 * (p->experts + 1) + combos) * sizeof(int);
+        if (smem <= 160 * 1024) {
+            int* ga = p->groups;
+            int* gb = ga + combos;
+            int* gbrows = gb + combos;
+            int* gd = gbrows + combos;
+            int* gdrows = gd + combos;
+            int* counts = gdrows + combos;
+            CN_ALLOW_SMEM(moe_group_kernel, 160 * 1024);
+            CN_CUDA(cn_launch_pdl(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, table_gu, combos, p->experts, p->order, ga, gb, gbrows, gd,
+                                  gdrows, counts));
+            RoutedCall a = {};
+            a.ids = ids, a.order = p->order, a.tab0 = table_gu, a.tab1 = table_up, a.fused_up_rows = table_up ? 0 : p->inter, a.gs0 = gs_gu;
+            a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.x_div = x_div, a.x_f32 = dtype == CN_F32, a.y = p->h, a.ldy = p->inter, a.rows = p->inter, a.k = p->hidden;
+            a.limit = limit;
+            RoutedCall d = {};
+            d.ids = ids, d.order = p->order, d.tab0 = table_dn, d.gs0 = gs_dn, d.x = p->h, d.x_div = 1, d.x_f32 = 1, d.y = eo, d.yptrs = eo_ptrs, d.ldy = p->hidden;
+            d.rows = p->hidden, d.k = p->inter;
+            if (a.x_f32) {
+                // f32 rows take two row slots each (high and low f16 plane): groups of one or two rows, one launch
+                a.mt = 4, a.gcount = counts + 2, a.gpos = gd, a.grows = gdrows, a.max_groups = combos;
+                if (int rc = cn_routed_launch(a, stream, "cn_moe_nvfp4 (gate/up, grouped)")) return rc;
+            } else {
+                for (int cls = 0; cls < 2; cls++) {
+                    a.mt = cls ? 4 : 1, a.gcount = counts + cls, a.gpos = cls ? gb : ga, a.grows = cls ? gbrows : nullptr, a.max_groups = cls ? combos / 2 : combos;
+                    if (int rc = cn_routed_launch(a, stream, "cn_moe_nvfp4 (gate/up, grouped)")) return rc;
+                }
+            }
+            // the intermediate rows are f32
+            d.mt = 4, d.gcount = counts + 2, d.gpos = gd, d.grows = gdrows, d.max_groups = combos;
+            if (int rc = cn_routed_launch(d, stream, "cn_moe_nvfp4 (down, grouped)")) return rc;
+            return CN_OK;
+        }
     }
+    // Few combos: one launch each for gate|up and down over the combos as they come (nearly every CTA of the step is
+    // resident at once and L2 serves an expert's second reader).
     GemvCall a = {};
     a.gs0 = gs_gu, a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.y = p->h, a.rows = p->inter, a.k = p->hidden, a.m = 1, a.ldy = p->inter;
-    a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = order, a.tab0 = table_gu, a.tab1 = table_up;
+    a.limit = limit, a.dtype = dtype, a.out_f32 = 1, a.ids = ids, a.order = nullptr, a.tab0 = table_gu, a.tab1 = table_up;
     a.fused_up_rows = table_up ? 0 : p->inter, a.x_div = x_div, a.combos = combos, a.experts = p->experts;
     if (int rc = cn_gemv_launch(a, stream, "cn_moe_nvfp4 (gate/up)")) return rc;
     GemvCall d = {};
     d.gs0 = gs_dn, d.x = p->h, d.y = eo, d.yptrs = eo_ptrs, d.rows = p->hidden, d.k = p->inter, d.m = 1, d.ldy = p->hidden, d.dtype = CN_F32, d.out_f32 = 1;
-    d.x_f16_ok = 0, d.ids = ids, d.order = order, d.tab0 = table_dn, d.x_div = 1, d.combos = combos, d.experts = p->experts;
+    d.x_f16_ok = 0, d.ids = ids, d.order = nullptr, d.tab0 = table_dn, d.x_div = 1, d.combos = combos, d.experts = p->experts;
     return cn_gemv_launch(d, stream, "cn_moe_nvfp4 (down)");
 }
 

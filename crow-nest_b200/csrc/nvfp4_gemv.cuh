@@ -27,6 +27,29 @@ struct GemvCall {
 
 int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who);
 
+// One class of routed-expert groups (nvfp4_routed.cu): combos sorted by expert (order), groups of `mt` = 1 or up to 4
+// consecutive positions of one expert (gpos, grows; grows null for one-row groups), their number on the device (gcount).
+struct RoutedCall {
+    const int32_t* ids;
+    const int32_t* order;
+    const int* gcount;
+    const int* gpos;
+    const int* grows;
+    const unsigned long long* tab0;
+    const unsigned long long* tab1;
+    int fused_up_rows;
+    const float* gs0;
+    const float* gs1;
+    const void* x;  // activation row of combo c: row c / x_div, bf16 (or f32 when x_f32)
+    int x_div, x_f32;
+    float* y;  // f32 row of combo c at y + c * ldy, or at yptrs[c]
+    const unsigned long long* yptrs;
+    int ldy, rows, k;
+    float limit;
+    int mt, max_groups;
+};
+int cn_routed_launch(const RoutedCall& a, cudaStream_t stream, const char* who);
+
 // Kernel-side parameters shared by the CUDA-core and the tensor-core GEMV kernels.
 struct GemvParams {
     const uint8_t* w0;  // plain: the matrix; gate/up: gate

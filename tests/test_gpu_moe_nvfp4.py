@@ -132,3 +132,30 @@ def test_moe_f32_separate_gate_up_clamp_and_missing_experts():
     ref2 = cpu_moe(x, rids, rw2, gu, dn, hidden, inter, np.float32(0.2), np.float32(0.3), limit=10.0)
     check_close(y2.cpu().numpy(), ref2, "moe partial residency", bf16_out=False)
     plan.free()
+
+
+@pytest.mark.parametrize("hidden,inter,experts,k,tokens", [(1024, 256, 24, 4, 40), (2048, 512, 16, 6, 33), (768, 1280, 9, 3, 50)])
+def test_grouped_experts_with_f32_rows_and_short_rows(hidden, inter, experts, k, tokens):
+    """More than 96 combos: the experts run over groups of rows that share an expert. f32 activations ride as two f16
+    planes; k = 256 / 512 / 768 / 1280 cover the stage shapes for short and ragged rows; several rows per expert."""
+    rng = np.random.default_rng(hidden + tokens)
+    gu, dn = make_experts(hidden, inter, experts, rng)
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    logits = rng.standard_normal((tokens, experts)).astype(np.float32)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    rids, rw = oracle.route_softmax_topk(logits, k)
+    w = moe.GpuMoeWeights(hidden, inter, experts, 0.2, 0.3, gate_up=[dev(a) for a in gu], down=[dev(a) for a in dn])
+    plan = moe.GpuMoePlan(hidden, inter, experts, k, max_tokens=tokens)
+    y = plan.run(w, dev(logits), dev(x))
+    ref = cpu_moe(x, rids, rw, gu, dn, hidden, inter, np.float32(0.2), np.float32(0.3))
+    check_close(y.cpu().numpy(), ref, "grouped moe f32", bf16_out=False)
+    # bf16 rows through the one-row and four-row group kernels, against the same reference fed the rounded rows
+    xb = synth.bf16_bits(x)
+    yb = plan.run(w, dev(logits), to_dev_bf16(xb))
+    refb = cpu_moe(synth.bf16_to_f32(xb), rids, rw, gu, dn, hidden, inter, np.float32(0.2), np.float32(0.3))
+    check_close(from_dev_bf16(yb), refb, "grouped moe bf16", ulp_floor=1.0 / 64)
+    yb2 = plan.run(w, dev(logits), to_dev_bf16(xb))
+    assert torch.equal(yb.view(torch.int16), yb2.view(torch.int16))
+    from crownest_b200 import device_status
+    assert device_status() == 0
+    plan.free()
