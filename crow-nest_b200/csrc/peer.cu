@@ -38,33 +38,34 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
     return v;
 }
 
+// The block's 512 threads are dealt to the peers in equal groups of whole warps (world 2: 512 threads for the one peer,
+// world 8: two warps for each of the seven): a group stores this rank's slice into its peer's buffer, makes it visible
+// system-wide, meets on its own named barrier, and its first thread publishes the sequence number right behind the data and
+// waits for that peer's slice of the same exchange. The peers are served side by side.
 __global__ void __launch_bounds__(512) tp_allgather_kernel(PeerPtrs peers, int rank, int world, size_t data_off, size_t slice_bytes,
                                                            size_t flag_off) {
-    __shared__ unsigned int seq_s;
     pdl_wait();  // the slice comes from the kernel before this one
     unsigned char* mine = peers.base[rank];
     unsigned int* my_flags = (unsigned int*)(mine + flag_off);
-    if (threadIdx.x == 0) seq_s = my_flags[MAX_WORLD] + 1u;
-    __syncthreads();
-    const unsigned int seq = seq_s;
-    const uint4* src = (const uint4*)(mine + data_off + (size_t)rank * slice_bytes);
-    const size_t n16 = slice_bytes >> 4;
-    for (int p = 0; p < world; p++) {
-        if (p == rank) continue;
+    const unsigned int seq = my_flags[MAX_WORLD] + 1u;  // read by everybody before anybody can advance it (barrier below)
+    const int gsz = (512 / (world - 1)) & ~31;          // threads per peer
+    const int gi = threadIdx.x / gsz, gt = threadIdx.x - gi * gsz;
+    if (gi < world - 1) {
+        const int p = gi < rank ? gi : gi + 1;  // the peers in rank order, this rank left out
+        const uint4* src = (const uint4*)(mine + data_off + (size_t)rank * slice_bytes);
         uint4* dst = (uint4*)(peers.base[p] + data_off + (size_t)rank * slice_bytes);
-        for (size_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < world && (int)threadIdx.x != rank) {
-        const int p = threadIdx.x;
-        st_release_sys((unsigned int*)(peers.base[p] + flag_off) + rank, seq);
-        // and wait for rank p's slice of the same exchange
-        const long long t0 = clock64();
-        while ((int)(ld_acquire_sys(my_flags + p) - seq) < 0) {
-            if (clock64() - t0 > 2000000000LL) {
-                cn_dev_fail(CN_DEV_WAIT_FULL);
-                break;
+        const size_t n16 = slice_bytes >> 4;
+        for (size_t i = gt; i < n16; i += gsz) dst[i] = src[i];
+        __threadfence_system();
+        asm volatile("bar.sync %0, %1;" ::"r"(gi + 1), "r"(gsz) : "memory");
+        if (gt == 0) {
+            st_release_sys((unsigned int*)(peers.base[p] + flag_off) + rank, seq);
+            const long long t0 = clock64();
+            while ((int)(ld_acquire_sys(my_flags + p) - seq) < 0) {
+                if (clock64() - t0 > 2000000000LL) {
+                    cn_dev_fail(CN_DEV_WAIT_FULL);
+                    break;
+                }
             }
         }
     }
