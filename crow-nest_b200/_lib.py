@@ -58,6 +58,11 @@ _SIGS = {
     "cn_ep_return": [C.POINTER(C.c_void_p), _i, _i, _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _vp, _vp, _vp, _vp],
     "cn_nvfp4_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
     "cn_nvfp4_gemm_workspace_bytes": [_i, _i],
+    "cn_nvfp4_bs_packed_bytes": [_i, _i],
+    "cn_nvfp4_bs_repack": [_vp, _vp, _i, _i, _vp],
+    "cn_nvfp4_bs_workspace_bytes": [_i, _i, _i],
+    "cn_nvfp4_bs_gemm": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, C.c_size_t, _vp],
+    "cn_nvfp4_act_cascade": [_vp, _vp, _i, _i, _i, _i, _vp],
     "cn_peer_export": [_vp, _vp, C.POINTER(C.c_size_t)],
     "cn_peer_open": [_vp, C.c_size_t, C.POINTER(C.c_void_p)],
     "cn_peer_close": [_vp, C.c_size_t],
@@ -88,7 +93,8 @@ def exported_symbols():
     return sorted(_SIGS)
 
 
-_RESTYPES_INIT = {"cn_nvfp4_gemm_workspace_bytes": C.c_size_t, "cn_ep_flag_bytes": C.c_size_t}
+_RESTYPES_INIT = {"cn_nvfp4_gemm_workspace_bytes": C.c_size_t, "cn_ep_flag_bytes": C.c_size_t, "cn_nvfp4_bs_packed_bytes": C.c_size_t,
+                  "cn_nvfp4_bs_workspace_bytes": C.c_size_t}
 
 
 def register(name, argtypes, restype=C.c_int):

@@ -82,6 +82,46 @@ def gemm_workspace_bytes(k, m):
     return int(lib().cn_nvfp4_gemm_workspace_bytes(k, m))
 
 
+class Fp4Packed:
+    """An NVFP4 matrix re-laid once at load for the block-scaled FP4 tensor-core GEMM (cn_nvfp4_bs_repack): stage images
+    of 128 rows x 256 columns with their scale bytes (0x7F read as 0x7E, bit 7 cleared - the reference rewrites its slabs
+    the same way at load, engine/src/residency.rs:119-137)."""
+
+    def __init__(self, w: Fp4):
+        n = int(lib().cn_nvfp4_bs_packed_bytes(w.rows, w.cols))
+        if n == 0:
+            raise CrownestError(f"block-scaled GEMM: k = {w.cols} must be a multiple of 256")
+        self.packed = torch.empty(n, dtype=torch.uint8, device=w.w.device)
+        check(lib().cn_nvfp4_bs_repack(w.w.data_ptr(), self.packed.data_ptr(), w.rows, w.cols, _stream()))
+        self.gs, self.rows, self.cols = w.gs, w.rows, w.cols
+
+
+def launch_gemm_fp4(w: Fp4Packed, x, y=None, workspace=None):
+    """Y[t][n] = gs * sum_k X[t][k] W[n][k] on the block-scaled FP4 MMA (tcgen05 kind::mxf4nvf4): gemm_fp4_dense
+    (engine/src/kernels.rs:533) with the activations as a five-level NVFP4 cascade (the reference's act_cascade,
+    engine/src/kernels.rs:5354-5475, has three)."""
+    x2 = x.reshape(-1, w.cols)
+    m = x2.shape[0]
+    if y is None:
+        y = torch.empty((m, w.rows), dtype=x.dtype, device=x.device)
+    need = int(lib().cn_nvfp4_bs_workspace_bytes(w.rows, w.cols, m))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib().cn_nvfp4_bs_gemm(w.packed.data_ptr(), w.gs.data_ptr(), x2.data_ptr(), y.data_ptr(), w.rows, w.cols, m, y.stride(0), _dtype_code(x),
+                                 workspace.data_ptr(), workspace.numel(), _stream()))
+    return y
+
+
+def act_cascade(x, levels=3):
+    """The activation cascade in the reference's byte layout (quant_x_fp4, engine/src/kernels.rs:351): uint8
+    [rows][levels * k/64 * 36 + 4]."""
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, k = x2.shape
+    out = torch.empty((rows, levels * (k // 64) * 36 + 4), dtype=torch.uint8, device=x.device)
+    check(lib().cn_nvfp4_act_cascade(x2.data_ptr(), out.data_ptr(), rows, k, levels, _dtype_code(x), _stream()))
+    return out
+
+
 dense_proj = launch_gemv  # Engine::dense_proj (engine/src/gen.rs:3915): same operator at t == 1 and t <= 4
 
 

@@ -199,6 +199,27 @@ size_t cn_nvfp4_gemm_workspace_bytes(int k, int m);
 int cn_nvfp4_gemm(const void* w, const float* gs, const void* x, void* y, int rows, int k, int m, int ldy, int dtype, void* workspace,
                   size_t workspace_bytes, cn_stream_t stream);
 
+/* The same product on the block-scaled FP4 tensor-core path: tcgen05.mma kind::mxf4nvf4 (both operands E2M1 with one
+ * UE4M3 scale per 16 values, f32 accumulation in tensor memory). Replaces gemm_fp4_dense / gemm_fp4_dense_b
+ * (engine/src/kernels.rs:533, :642) and quant_x_fp4 / quant_row_prescaled (:264-351, host twin act_cascade :5354-5475).
+ * The weights are re-laid once at load (cn_nvfp4_bs_repack into cn_nvfp4_bs_packed_bytes bytes, 16-byte aligned: tiles of
+ * 128 rows x 256 columns in the tensor core's shared-memory layout, scale byte 0x7F -> 0x7E and bit 7 cleared as the
+ * reference does at load, engine/src/residency.rs:119-137). The activations of every call go through the reference's
+ * cascade - a per-row power of two times a sum of NVFP4 levels, each coding the residual of the ones before - with five
+ * levels instead of the reference's three (three leave 8e-4 relative L2, inside 1e-3 but tens of bf16 ulp on small outputs;
+ * each level buys a factor of about 16). The levels of a token ride as columns of the MMA and are added in the epilogue.
+ * k a multiple of 256; workspace (256-byte aligned, cn_nvfp4_bs_workspace_bytes) holds the cascade and, for few rows, the
+ * partial sums of a split K range. Meant for 16 < m <= a few hundred rows, where it streams the weights near HBM speed;
+ * for thousands of rows cn_nvfp4_gemm is as fast. cn_nvfp4_act_cascade exposes the cascade alone in the reference's byte
+ * layout ([rows][levels * k/64 * 36 + 4]; level L at L * k/64 * 36, then the f32 factor 2^-k), bit-identical to the
+ * reference's host twin; levels 1..8. */
+size_t cn_nvfp4_bs_packed_bytes(int rows, int k);
+int cn_nvfp4_bs_repack(const void* w, void* packed, int rows, int k, cn_stream_t stream);
+size_t cn_nvfp4_bs_workspace_bytes(int rows, int k, int m);
+int cn_nvfp4_bs_gemm(const void* packed, const float* gs, const void* x, void* y, int rows, int k, int m, int ldy, int dtype, void* workspace,
+                     size_t workspace_bytes, cn_stream_t stream);
+int cn_nvfp4_act_cascade(const void* x, void* out, int rows, int k, int levels, int dtype, cn_stream_t stream);
+
 /* ---------------------------------------------------------------- EXL3 "MUL1" trellis experts
  * A record holds one expert (converter/src/mul1.rs:30-34, engine/src/cpu_mul1.rs:7-12):
  * [gate.trellis][up.trellis][down.trellis][gate.suh][gate.svh][up.suh][up.svh][down.suh][down.svh],
