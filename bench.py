@@ -471,16 +471,27 @@ def gemm_arm(args, rank, world, local):
     hp = torch.empty((m, inter // world), dtype=torch.bfloat16, device=dev) if world > 1 else h
     yp = torch.empty((m, hidden // world), dtype=torch.bfloat16, device=dev) if world > 1 else y
     y_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
-    ws = torch.empty(ops.gemm_workspace_bytes(inter, m), dtype=torch.uint8, device=dev)
+    # engine: the block-scaled FP4 MMA (kind::mxf4nvf4 + five-level activation cascade) up to 128 rows, where one pass over
+    # the weights serves every token; beyond that its operand traffic (five cascade columns per token) binds on L2 and the f16
+    # MMA on losslessly widened weights is faster (both are tcgen05)
+    fp4 = args.engine == "fp4" or (args.engine == "auto" and m <= 128)
+    if fp4:
+        ups, downs = [ops.Fp4Packed(w) for w in ups], [ops.Fp4Packed(w) for w in downs]
+        nws = max(int(_lib.lib().cn_nvfp4_bs_workspace_bytes(inter // world, hidden, m)), int(_lib.lib().cn_nvfp4_bs_workspace_bytes(hidden // world, inter, m)))
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+        gemm = ops.launch_gemm_fp4
+    else:
+        ws = torch.empty(ops.gemm_workspace_bytes(inter, m), dtype=torch.uint8, device=dev)
+        gemm = ops.launch_gemm
     it = [0]
 
     def step():
         i = it[0]
         it[0] += 1
-        ops.launch_gemm(ups[i % ncopy], x, hp, workspace=ws)
+        gemm(ups[i % ncopy], x, hp, workspace=ws)
         if world > 1:
             dense.gather_rows(hp, h, m, world)
-        ops.launch_gemm(downs[i % ncopy], h, yp, workspace=ws)
+        gemm(downs[i % ncopy], h, yp, workspace=ws)
         if world > 1:
             dense.gather_rows(yp, y, m, world)
 
@@ -503,12 +514,13 @@ def gemm_arm(args, rank, world, local):
         tf = flops / (ms_step * 1e-3) / 1e12
         peak, kind = measured_peak("bf16_tflops", 1590.0)
         line = {"metric": "nvfp4_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 x f16 -> f32", "data": "synthetic",
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "e2m1 x e2m1 block-scaled -> f32" if fp4 else "f16 x f16 -> f32", "data": "synthetic",
                 "config": {"workload": f"nvfp4 GEMM pair [17408 x 5120] and [5120 x 17408], M={m}", "parallelism": f"tp{world} column split + all-gather" if world > 1 else "none",
                            "l2": "three weight copies rotated (300 MB per rank) plus the activations: larger than L2", "launch": "plain launches"},
                 "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s", "frac": tf / world / peak, "traffic": None,
                              "peak_kind": kind + " (bf16 GEMM, burst)", "scope": "per GPU",
-                             "kernel": "nvfp4_gemm_tc5_kernel", "flops_per_launch": flops / 2 / world, "us_per_launch": ms_step * 1e3 / 2,
+                             "kernel": "nvfp4_gemm_bs_kernel (tcgen05 kind::mxf4nvf4)" if fp4 else "nvfp4_gemm_tc5_kernel (tcgen05 kind::f16)", "flops_per_launch": flops / 2 / world, "us_per_launch": ms_step * 1e3 / 2,
                              "hbm_gbs": (2 * hidden * inter // 64 * 36 / world + 2.0 * m * (hidden + inter) * 2) / (ms_step * 1e-3) / 1e9},
                 "blocks": t["blocks"], "ms_per_step_min": t["ms_per_step_min"], "ms_per_step_max": t["ms_per_step_max"],
                 "e2e": {"value": flops / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
@@ -592,6 +604,7 @@ def main():
     ap.add_argument("--workload", default="dense", choices=["dense", "gemv", "moe", "mul1", "gemm"],
                     help="dense = the headline (layer stack); gemv = one matrix (default 4096 x 4096); moe / mul1 = routed experts; gemm = batched rows")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
+    ap.add_argument("--engine", default="auto", choices=["auto", "fp4", "f16"], help="gemm: block-scaled FP4 MMA, f16 MMA on widened weights, or by row count")
     ap.add_argument("--rows", type=int, default=4096, help="gemv: output rows")
     ap.add_argument("--cols", type=int, default=4096, help="gemv: k")
     args = ap.parse_args()

@@ -37,34 +37,39 @@ __host__ __device__ constexpr int stages_of(int nb) { return nb == 2 ? 3 : 5; }
 __host__ __device__ constexpr int smem_of(int nb) { return 2048 + 1024 + stages_of(nb) * stage_bytes(nb); }
 
 // ---------------------------------------------------------------- the reference's quantiser, operation for operation
-// engine/src/kernels.rs:238-249
+// engine/src/kernels.rs:238-249 (round to nearest onto {0,.5,1,1.5,2,3,4,6}, ties to the even mantissa): the if-chain of the
+// reference as a count of passed thresholds
 __device__ __forceinline__ uint32_t q_e2m1(float v) {
-    const uint32_t s = v < 0.0f ? 8u : 0u;
     const float r = fabsf(v);
-    if (r <= 0.25f) return s;
-    if (r < 0.75f) return s | 1;
-    if (r <= 1.25f) return s | 2;
-    if (r < 1.75f) return s | 3;
-    if (r <= 2.5f) return s | 4;
-    if (r < 3.5f) return s | 5;
-    if (r <= 5.0f) return s | 6;
-    return s | 7;
+    const uint32_t c = (uint32_t)(r > 0.25f) + (uint32_t)(r >= 0.75f) + (uint32_t)(r > 1.25f) + (uint32_t)(r >= 1.75f) + (uint32_t)(r > 2.5f) +
+                       (uint32_t)(r >= 3.5f) + (uint32_t)(r > 5.0f);
+    // an all-zero sub-block has scale 0 and v = 0 * inf = NaN here: the reference's chain of comparisons then falls through
+    // to its last code (6 x scale 0 = 0), and so does this
+    return (r != r ? 7u : c) | (v < 0.0f ? 8u : 0u);
 }
 __device__ __forceinline__ float e2m1_f32(uint32_t n) {
-    const float t[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
-    const float v = t[n & 7];
-    return (n & 8) ? -v : v;
+    const uint32_t c = n & 7u;
+    const float v = c < 2u ? 0.5f * (float)c : __uint_as_float(((126u + (c >> 1)) << 23) | ((c & 1u) << 22));
+    return (n & 8u) ? -v : v;
 }
-// engine/src/kernels.rs:254-263: the smallest UE4M3 value >= s, saturating at 0x7E
+// engine/src/kernels.rs:254-263: the smallest UE4M3 value >= s, saturating at 0x7E. The reference tries the exponents
+// e = 0 .. 15 in turn and takes the first whose mantissa ceil(s * 2^(10 - e)) - 8 fits (ceil(s * 512) at e = 0); with
+// t = s * 512 = f * 2^x that first exponent is 0 for t <= 7, else 1 + max(0, x - 3 + (8 f > 15)). All products are by powers
+// of two, hence exact, and the result is the reference's byte for every s (checked against its host twin).
 __device__ __forceinline__ uint32_t enc_ue4m3_up(float s) {
     if (!(s > 0.0f)) return 0;
-    for (int e = 0; e < 16; e++) {
-        const float mul = e == 0 ? 512.0f : __uint_as_float((uint32_t)(127 + 10 - e) << 23);
-        const float m = ceilf(s * mul) - (e == 0 ? 0.0f : 8.0f);
-        const float m_max = e == 15 ? 6.0f : 7.0f;
-        if (m >= 0.0f && m <= m_max) return (uint32_t)((e << 3) | (int)m);
-    }
-    return 0x7E;
+    const float t = s * 512.0f;
+    if (t <= 7.0f) return (uint32_t)ceilf(t);
+    if (!(t < 3.0e38f)) return 0x7E;
+    const int x = (int)((__float_as_uint(t) >> 23) & 0xFFu) - 127;
+    const float f8 = t * __uint_as_float((uint32_t)(127 + 3 - x) << 23);  // in [8, 16)
+    int j = x - 3 + (f8 > 15.0f ? 1 : 0);
+    j = j < 0 ? 0 : j;
+    if (j > 14) return 0x7E;
+    const int m = (int)ceilf(t * __uint_as_float((uint32_t)(127 - j) << 23)) - 8;
+    const int e = 1 + j;
+    if (e == 15 && m > 6) return 0x7E;
+    return (uint32_t)((e << 3) | m);
 }
 // engine/src/kernels.rs:298-304
 __device__ __forceinline__ int row_prescale_k(float amax) {
@@ -139,37 +144,59 @@ __global__ void act_cascade_kernel(const void* __restrict__ x, uint8_t* __restri
     }
 }
 
-// The same cascade (LEVELS levels) written as the stage images of the GEMM. grid (m rounded up to whole token blocks),
-// block 128; rows beyond m are zero rows.
+// rs[tok] = 2^-k of every activation row (1 for rows beyond m). grid (token blocks * TB), block 256.
 template <int XT>
-__global__ void bs_cascade_kernel(const void* __restrict__ x, uint8_t* __restrict__ ws, float* __restrict__ rs, int k, int m) {
+__global__ void bs_rowscale_kernel(const void* __restrict__ x, float* __restrict__ rs, int k, int m) {
     __shared__ float amax_w[32];
-    const int tok = blockIdx.x, tb = tok / TB, tt = tok % TB;
-    const int kts = k / KT;
-    const bool live = tok < m;
+    const int tok = blockIdx.x;
     float amax = 0.0f;
-    if (live)
+    if (tok < m)
         for (int i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(load_act<XT>(x, (size_t)tok * k + i)));
     amax = block_amax(amax, amax_w);
-    const int kk = row_prescale_k(amax);
-    const float up = __uint_as_float((uint32_t)(127 + kk) << 23);
-    for (int sb = threadIdx.x; sb < k / 16; sb += blockDim.x) {
-        const int kt = sb >> 4, sub = sb & 15;  // column tile, sub-block inside it: MMA sub >> 2, scale slot sub & 3
-        float v[16];
+    if (threadIdx.x == 0) rs[tok] = __uint_as_float((uint32_t)(127 - row_prescale_k(amax)) << 23);
+}
+
+// The same cascade (LEVELS levels) written as the stage images of the GEMM: one thread per 16-value sub-block of a row.
+// grid (tokens rounded up to whole token blocks, k / 16 / 128 rounded up), block 128; rows beyond m are zero rows.
+template <int XT>
+__global__ void bs_cascade_kernel(const void* __restrict__ x, uint8_t* __restrict__ ws, const float* __restrict__ rs, int k, int m) {
+    const int tok = blockIdx.x, tb = tok / TB, tt = tok % TB;
+    const int kts = k / KT;
+    const int sb = blockIdx.y * blockDim.x + threadIdx.x;
+    if (sb >= k / 16) return;
+    const bool live = tok < m;
+    const float up = 1.0f / rs[tok];  // a power of two: exact
+    const int kt = sb >> 4, sub = sb & 15;  // column tile, sub-block inside it: MMA sub >> 2, scale slot sub & 3
+    float v[16];
+    if (live) {
+        if (XT == 1) {
+            const uint4* src = (const uint4*)((const char*)x + ((size_t)tok * k + (size_t)sb * 16) * 2);
+            const uint4 a = src[0], b = src[1];
+            const uint32_t u[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int j = 0; j < 16; j++) v[j] = live ? load_act<XT>(x, (size_t)tok * k + (size_t)sb * 16 + j) * up : 0.0f;
-        uint8_t* img = ws + ((size_t)tb * kts + kt) * B_STAGE;
+            for (int j = 0; j < 8; j++) v[2 * j] = __uint_as_float(u[j] << 16) * up, v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u) * up;
+        } else {
+            const float4* src = (const float4*)((const char*)x + ((size_t)tok * k + (size_t)sb * 16) * 4);
 #pragma unroll
-        for (int lv = 0; lv < LEVELS; lv++) {
-            uint32_t sc, code[2];
-            quant_level(v, sc, code);
-            const int n = lv * TB + tt;
-            const int c = sub >> 1;
-            *(uint2*)(img + (size_t)n * 128 + ((c ^ (n & 7)) << 4) + (sub & 1) * 8) = make_uint2(code[0], code[1]);
-            img[B_IMG + ((sub >> 2) * 2 + (n >> 7)) * 512 + ((n & 127) & 31) * 16 + ((n & 127) >> 5) * 4 + (sub & 3)] = (uint8_t)sc;
+            for (int j = 0; j < 4; j++) {
+                const float4 a = src[j];
+                v[4 * j] = a.x * up, v[4 * j + 1] = a.y * up, v[4 * j + 2] = a.z * up, v[4 * j + 3] = a.w * up;
+            }
         }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = 0.0f;
     }
-    if (threadIdx.x == 0) rs[tok] = __uint_as_float((uint32_t)(127 - kk) << 23);
+    uint8_t* img = ws + ((size_t)tb * kts + kt) * B_STAGE;
+#pragma unroll
+    for (int lv = 0; lv < LEVELS; lv++) {
+        uint32_t sc, code[2];
+        quant_level(v, sc, code);
+        const int n = lv * TB + tt;
+        const int c = sub >> 1;
+        *(uint2*)(img + (size_t)n * 128 + ((c ^ (n & 7)) << 4) + (sub & 1) * 8) = make_uint2(code[0], code[1]);
+        img[B_IMG + ((sub >> 2) * 2 + (n >> 7)) * 512 + ((n & 127) & 31) * 16 + ((n & 127) >> 5) * 4 + (sub & 3)] = (uint8_t)sc;
+    }
 }
 
 // container -> stage images of the weights. One thread per 16-byte chunk of the image (32 codes = half a container block)
@@ -460,10 +487,15 @@ extern "C" int cn_nvfp4_bs_gemm(const void* packed, const float* gs, const void*
     uint8_t* xq = (uint8_t*)workspace;
     float* rs = (float*)(xq + (size_t)ntb * kts * B_STAGE);
     float* part = rs + (size_t)ntb * TB + 64;
-    if (dtype == CN_BF16)
-        bs_cascade_kernel<1><<<ntb * TB, 128, 0, stream>>>(x, xq, rs, k, m);
-    else
-        bs_cascade_kernel<0><<<ntb * TB, 128, 0, stream>>>(x, xq, rs, k, m);
+    if (((uintptr_t)x & 15)) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_bs_gemm: x must be 16-byte aligned");
+    const dim3 cgrid(ntb * TB, (k / 16 + 127) / 128);
+    if (dtype == CN_BF16) {
+        bs_rowscale_kernel<1><<<ntb * TB, 256, 0, stream>>>(x, rs, k, m);
+        bs_cascade_kernel<1><<<cgrid, 128, 0, stream>>>(x, xq, rs, k, m);
+    } else {
+        bs_rowscale_kernel<0><<<ntb * TB, 256, 0, stream>>>(x, rs, k, m);
+        bs_cascade_kernel<0><<<cgrid, 128, 0, stream>>>(x, xq, rs, k, m);
+    }
     CN_CUDA(cudaGetLastError());
     BsParams p;
     p.wp = (const uint8_t*)packed, p.xq = xq, p.gs = gs, p.rs = rs, p.y = y, p.rows = rows, p.k = k, p.m = m, p.ldy = ldy, p.out_bf16 = dtype == CN_BF16;
