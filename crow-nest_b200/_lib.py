@@ -39,6 +39,9 @@ _SIGS = {
     "cn_nvfp4_gemv": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cn_nvfp4_gemv_gu": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "cn_nvfp4_dequant": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "cn_add_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "cn_argmax": [_vp, _vp, _i, _i, _i, _i, _vp],
+    "cn_lm_head_argmax": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "cn_nvfp4_seq_create": [C.POINTER(C.c_void_p), _vp, _i],
     "cn_nvfp4_seq_run": [_vp, _vp],
     "cn_nvfp4_seq_destroy": [_vp],

@@ -198,6 +198,36 @@ class GemvSeq:
             pass
 
 
+def add_norm(h, y, w, out=None, eps=1e-6):
+    """h += y (y may be None), out = h * rsqrt(mean(h^2) + eps) * (1 + w): Engine::add_norm / add_rms_1k
+    (engine/src/kernels_p2.rs:609). h, y, out f32 [rows][hidden], w f32 [hidden]; h is updated in place."""
+    rows, hidden = h.shape
+    if out is None:
+        out = torch.empty_like(h)
+    check(lib().cn_add_rmsnorm(h.data_ptr(), None if y is None else y.data_ptr(), w.data_ptr(), out.data_ptr(), rows, hidden, float(eps), _stream()))
+    return out
+
+
+def argmax(logits):
+    """Token id per row with the tie rule of argmax_k (engine/src/kernels.rs:4238)."""
+    rows, n = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    check(lib().cn_argmax(logits.data_ptr(), out.data_ptr(), rows, n, logits.stride(0), _dtype_code(logits), _stream()))
+    return out
+
+
+def lm_head_argmax(w: Fp4, x, logits=None):
+    """logits = lm_head x and their argmax per row (engine/src/gen.rs:5638-5641): returns (tokens int32 [m], logits [m][vocab])."""
+    x2 = x.reshape(-1, w.cols)
+    m = x2.shape[0]
+    if logits is None:
+        logits = torch.empty((m, w.rows), dtype=x.dtype, device=x.device)
+    tokens = torch.empty(m, dtype=torch.int32, device=x.device)
+    check(lib().cn_lm_head_argmax(w.w.data_ptr(), w.gs.data_ptr(), x2.data_ptr(), logits.data_ptr(), tokens.data_ptr(), w.rows, w.cols, m,
+                                  _dtype_code(x), _stream()))
+    return tokens, logits
+
+
 def dequant(w: Fp4, rule=False):
     """f32 [rows][cols] = e2m1(code) * (ue4m3(byte) * gs): dequant_fp4_flat (engine/src/kernels.rs:1460)."""
     out = torch.empty((w.rows, w.cols), dtype=torch.float32, device=w.w.device)

@@ -108,6 +108,18 @@ int cn_nvfp4_seq_create(void** plan_out, const cn_gemv_step* steps, int nsteps);
 int cn_nvfp4_seq_run(void* plan, cn_stream_t stream);
 int cn_nvfp4_seq_destroy(void* plan);
 
+/* Residual add + RMSNorm between the projections: h[r] += y[r] (y may be null), out[r] = h[r] * rsqrt(mean(h[r]^2) + eps) *
+ * (1 + w). Replaces add_rms_1k (engine/src/kernels_p2.rs:609-633, Engine::add_norm). All f32; h is updated in place. */
+int cn_add_rmsnorm(float* h, const float* y, const float* w, float* out, int rows, int hidden, float eps, cn_stream_t stream);
+
+/* Token id of the largest logit per row, with the tie rule of argmax_k (engine/src/kernels.rs:4238-4261): 1024 strided
+ * scanners keeping their first strict maximum, then a tree in which the lower scanner wins ties. logits [rows][ld >= n] in
+ * `dtype`. cn_lm_head_argmax: the vocabulary GEMV (cn_nvfp4_gemv over w [vocab][k], m <= CN_MAX_M rows, logits [m][vocab] in
+ * `dtype` kept for the caller's sampler) followed by that argmax (engine/src/gen.rs:5638-5641). */
+int cn_argmax(const void* logits, int32_t* out, int rows, int n, int ld, int dtype, cn_stream_t stream);
+int cn_lm_head_argmax(const void* w, const float* gs, const void* x, void* logits, int32_t* tokens, int vocab, int k, int m, int dtype,
+                      cn_stream_t stream);
+
 /* Bit-exact dequantisation self-check: out[r][c] f32 = e2m1(code) * (ue4m3(scale byte) * gs).
  * Replaces dequant_fp4_flat (engine/src/kernels.rs:1460), host twin cnq::dequant_block
  * (engine/src/cnq.rs:1298). rule != 0 reads 0x7F as 0x7E first (the GEMV's reading). */

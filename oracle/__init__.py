@@ -78,6 +78,10 @@ def _declare(L):
     L.cn_o_f32_to_f16.restype = C.c_uint16
     L.cn_o_f32_to_f16.argtypes = [C.c_float]
     L.cn_o_mul1_reconstruct.argtypes = [_u16p, _i64, _i64, C.c_int, C.c_int, _u16p]
+    L.cn_o_argmax.restype = C.c_int32
+    L.cn_o_argmax.argtypes = [_f32p, _i64]
+    L.cn_o_add_rmsnorm.argtypes = [_f32p, _f32p, _f32p, _f32p, _i64, _i64, C.c_float]
+    L.cn_o_add_rmsnorm.restype = None
     L.cn_o_q_e2m1.restype = C.c_uint32
     L.cn_o_q_e2m1.argtypes = [C.c_float]
     L.cn_o_enc_ue4m3_up.restype = C.c_uint8
@@ -171,6 +175,23 @@ def act_cascade_dequant(q, k, levels=3, level_shift=0):
     out = np.empty(k, np.float32)
     lib().cn_o_act_cascade_dequant(_p(q, _u8p), k, levels, level_shift, _p(out, _f32p))
     return out
+
+
+def argmax(logits):
+    """argmax_k's token per row (engine/src/kernels.rs:4238-4261), ties as the kernel breaks them."""
+    x = _c(logits, np.float32)
+    x = x.reshape(-1, x.shape[-1])
+    return np.array([lib().cn_o_argmax(_p(np.ascontiguousarray(r), _f32p), r.size) for r in x], np.int32)
+
+
+def add_rmsnorm(h, y, w, eps=1e-6):
+    """add_rms_1k (engine/src/kernels_p2.rs:609-633): returns (h + y, normalised output)."""
+    h = _c(h, np.float32).copy()
+    rows, hidden = h.shape
+    out = np.empty_like(h)
+    yy = None if y is None else _c(y, np.float32)
+    lib().cn_o_add_rmsnorm(_p(h, _f32p), None if yy is None else _p(yy, _f32p), _p(_c(w, np.float32), _f32p), _p(out, _f32p), rows, hidden, eps)
+    return h, out
 
 
 def e4m3_table():

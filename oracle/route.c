@@ -132,3 +132,59 @@ void cn_o_moe_acc_combo(int topk, int64_t tokens, int64_t hidden, const float* e
             y[t * hidden + j] = base + acc;
         }
 }
+
+/* engine/src/kernels.rs:4238-4261 (`argmax_k`): 1024 workers, worker t scans i = t, t + 1024, .. keeping the first strict
+ * maximum (start -3e38 at index 0), then a stride-halving tree where the upper worker's candidate replaces the lower one
+ * only when strictly larger. NaN never compares larger. */
+int32_t cn_o_argmax(const float* logits, int64_t n) {
+    float rb[1024];
+    int32_t ri[1024];
+    for (int t = 0; t < 1024; t++) {
+        float best = -3.0e38f;
+        int32_t bi = 0;
+        for (int64_t i = t; i < n; i += 1024)
+            if (logits[i] > best) best = logits[i], bi = (int32_t)i;
+        rb[t] = best, ri[t] = bi;
+    }
+    for (int st = 512; st > 0; st >>= 1)
+        for (int t = 0; t < st; t++)
+            if (rb[t + st] > rb[t]) rb[t] = rb[t + st], ri[t] = ri[t + st];
+    return ri[0];
+}
+
+/* engine/src/kernels_p2.rs:609-633 (`add_rms_1k`): h += y (y may be null), out = h * rsqrt(mean(h^2) + eps) * (1 + w); the sum
+ * of squares in the kernel's order: 1024 strided partial sums, xor-shuffle tree inside each group of 32, the 32 group sums
+ * left to right. 1 / sqrtf stands in for the device's rsqrtf (2 ulp apart at most). */
+void cn_o_add_rmsnorm(float* h, const float* y, const float* w, float* out, int64_t rows, int64_t hidden, float eps) {
+    for (int64_t r = 0; r < rows; r++) {
+        float* hp = h + r * hidden;
+        float part[1024];
+        for (int t = 0; t < 1024; t++) {
+            float ss = 0.0f;
+            for (int64_t i = t; i < hidden; i += 1024) {
+                float v = hp[i];
+                if (y) {
+                    v = v + y[r * hidden + i];
+                    hp[i] = v;
+                }
+                ss = ss + v * v;
+            }
+            part[t] = ss;
+        }
+        float red[32];
+        for (int g = 0; g < 32; g++) {
+            float v[32];
+            for (int l = 0; l < 32; l++) v[l] = part[g * 32 + l];
+            for (int o = 16; o > 0; o >>= 1) {
+                float nv[32];
+                for (int l = 0; l < 32; l++) nv[l] = v[l] + v[l ^ o];
+                for (int l = 0; l < 32; l++) v[l] = nv[l];
+            }
+            red[g] = v[0];
+        }
+        float ss = 0.0f;
+        for (int g = 0; g < 32; g++) ss = ss + red[g];
+        const float rms = 1.0f / sqrtf(ss / (float)hidden + eps);
+        for (int64_t i = 0; i < hidden; i++) out[r * hidden + i] = (hp[i] * rms) * (1.0f + w[i]);
+    }
+}

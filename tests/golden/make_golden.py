@@ -7,6 +7,7 @@ What it writes, and where it comes from:
   (oracle/cnq_weights.py, imported and run): the six NVFP4 tensors of the reference's container
   fixture engine/tests/fixtures/synthetic-v2/synthetic-v2.cnq, plus one seeded matrix that holds
   every scale byte (0x7F and bit 7 among them) decoded with and without the 0x7F -> 0x7E rule.
+- synthetic-v2.cnq: the reference's container fixture itself, byte for byte (data, not source), for the container reader.
 - exl3-mul1-*.{tsv,bin}, fp8-*.tsv: the reference's golden vectors for the MUL1 codec and the
   FP8 codec, copied byte for byte (data, not source).
 - glm5_moe/*: the HF-computed goldens of the sigmoid router, the NVFP4 dense FFN and the MUL1
@@ -50,6 +51,9 @@ def main(ref):
     out["all_raw"] = raw.reshape(-1)
     out["all_gs"] = np.array(gs, np.float32)
     np.savez_compressed(os.path.join(here, "nvfp4_dequant.npz"), **out)
+
+    # the container fixture itself (data: 66 KB), for the container reader's test
+    shutil.copyfile(os.path.join(ref, "engine/tests/fixtures/synthetic-v2/synthetic-v2.cnq"), os.path.join(here, "synthetic-v2.cnq"))
 
     fx = os.path.join(ref, "converter/tests/fixtures")
     for f in ("exl3-mul1-decode.tsv", "exl3-mul1-glm-sizes.tsv", "exl3-mul1-q-k2.bin", "exl3-mul1-q-k3.bin",
