@@ -600,7 +600,8 @@ def main():
     ap.add_argument("--no-moe", action="store_true", help="dense workload: leave the MoE block out of the line")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="tensor parallel: slices pushed over peer memory, or NCCL all-gather")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
-    ap.add_argument("--fuse", default="none", choices=["none", "layer", "token"], help="dense, one GPU, M = 1: projections as persistent chains (one launch per layer / token)")
+    ap.add_argument("--fuse", default="none", choices=["none", "gemv", "layer", "token"],
+                    help="dense, one GPU, M = 1: projections through the balanced-share kernel, one launch per projection / layer / token")
     ap.add_argument("--workload", default="dense", choices=["dense", "gemv", "moe", "mul1", "gemm"],
                     help="dense = the headline (layer stack); gemv = one matrix (default 4096 x 4096); moe / mul1 = routed experts; gemm = batched rows")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")

@@ -63,6 +63,7 @@ struct SeqParams {
     int nsteps;
     int stages;
     uint32_t stage_off;   // byte offset of the weight ring in shared memory (behind the longest activation row)
+    int pdl;              // launched with programmatic dependent launch (a single step): wait for the predecessor grid before x is read
     unsigned int* done;   // [nsteps] arrivals: after run r every entry is (r + 1) * gridDim.x
     unsigned int* pflag;  // [nsteps][grid] run number + 1 of the last partial posted by that CTA in that step
     float* part;          // [nsteps][grid][16]
@@ -124,7 +125,6 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
     const int S = p.stages;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cid = blockIdx.x, ncta = gridDim.x;
-    const unsigned int run = *(volatile const unsigned int*)p.runs;  // completed runs before this one (stable until every CTA has left)
 
     if (warp == NW) {
         if (lane == 0) {
@@ -137,6 +137,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
         }
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
+        pdl_launch_dependents();
         // ------------------------------------------------------------ weight producer: every step, back to back
         const uint64_t pol = l2_policy_evict_first();
         int s = 0;
@@ -145,20 +146,21 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
         for (int st = 0; st < p.nsteps; st++) {
             const SeqStepDev d = p.steps[st];
             const bool gu = d.w1 != nullptr;
-            const int bpr = d.k >> 6, C = (bpr + TX - 1) / TX;
+            const int bpr = d.k >> 6, HC = (bpr + 15) >> 4;  // half chunks (16 blocks, the last may be shorter) per row: the unit the shares are dealt in
             const size_t row_bytes = (size_t)bpr * 36;
             const int per_cta = gu ? ROWS / 2 : ROWS;
-            const int T = (d.rows + per_cta - 1) / per_cta, U = T * C;
+            const int T = (d.rows + per_cta - 1) / per_cta, U = T * HC;
             const int u0 = share_start(cid, U, ncta), u1 = share_start(cid + 1, U, ncta);
-            int tile = u0 / C, c = u0 - tile * C;
-            for (int u = u0; u < u1; u++) {
+            int tile = u0 / HC, hc = u0 - tile * HC;
+            for (int u = u0; u < u1;) {
+                // a stage: one or two half chunks of one tile (two when the tile and the share both go on)
+                const int nh = min(2, min(HC - hc, u1 - u));
                 const int row0 = tile * per_cta;
                 const int row = gu ? row0 + (lane & 7) : row0 + lane;
                 const uint8_t* base = (gu && ((lane >> 3) & 1)) ? d.w1 : d.w0;
                 const uint8_t* src = (lane < ROWS && row < d.rows) ? base + (size_t)row * row_bytes : nullptr;
                 const uint32_t nvalid = (uint32_t)__popc(__ballot_sync(0xffffffffu, src != nullptr));
-                const int nblk = min(TX, bpr - c * TX);
-                const uint32_t piece = (uint32_t)nblk * 36u;
+                const uint32_t piece = (uint32_t)min(nh * 16, bpr - hc * 16) * 36u;
                 if (!first_round && !mbar_wait(&empty[s], par ^ 1u)) {
                     cn_dev_fail(CN_DEV_WAIT_EMPTY);
                     return;
@@ -169,19 +171,23 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
                     mbar_arrive(&full[s]);
                 }
                 __syncwarp();
-                if (src) bulk_g2s_stream(dst + (size_t)lane * PSTRIDE, src + (size_t)c * TX * 36, piece, &full[s], pol);
+                if (src) bulk_g2s_stream(dst + (size_t)lane * PSTRIDE, src + (size_t)hc * 16 * 36, piece, &full[s], pol);
                 if (++s == S) {
                     s = 0;
                     par ^= 1u;
                     first_round = false;
                 }
-                if (++c == C) c = 0, tile++;
+                u += nh, hc += nh;
+                if (hc == HC) hc = 0, tile++;
             }
         }
         return;
     }
 
     // ---------------------------------------------------------------- consumer warps
+    pdl_launch_dependents();
+    if (p.pdl) pdl_wait();  // the activation row (and this plan's run counter) may come from the kernel just before this one
+    const unsigned int run = *(volatile const unsigned int*)p.runs;  // completed runs before this one (stable until every CTA has left)
     const int g = lane >> 2, t = lane & 3;
     const int myq = ((g & 1) == (t >> 1)) ? (g >> 1) : -1;
     const int xb0 = 2 * warp + (g >> 2);
@@ -201,9 +207,9 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
     for (int st = 0; st < p.nsteps && ok; st++) {
         const SeqStepDev d = p.steps[st];
         const bool gu = d.w1 != nullptr;
-        const int bpr = d.k >> 6, C = (bpr + TX - 1) / TX;
+        const int bpr = d.k >> 6, HC = (bpr + 15) >> 4;
         const int per_cta = gu ? ROWS / 2 : ROWS;
-        const int T = (d.rows + per_cta - 1) / per_cta, U = T * C;
+        const int T = (d.rows + per_cta - 1) / per_cta, U = T * HC;
         const int u0 = share_start(cid, U, ncta), u1 = share_start(cid + 1, U, ncta);
         uint8_t* xs0 = smem + XS_OFF;
         float* xinv0 = (float*)(xs0 + (size_t)bpr * XB);
@@ -276,11 +282,12 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
         // ---- this CTA's share of the step's units
         const float* xinv_lane = xinv0 + 2 * warp + (t >> 1);
         const float* lut_b = lut + (gu ? 256 : 0);
-        int tile = u0 / C, c = u0 - tile * C;
+        int tile = u0 / HC, hc = u0 - tile * HC;
         float acc0 = 0.0f, acc1 = 0.0f;
-        int c_first = c;
-        for (int u = u0; u < u1 && ok; u++) {
-            const int ng = min(TX, bpr - c * TX) >> 1;
+        int c_first = hc;
+        for (int u = u0; u < u1 && ok;) {
+            const int nh = min(2, min(HC - hc, u1 - u));
+            const int ng = min(nh * 16, bpr - hc * 16) >> 1;  // groups of two blocks in this stage
             if (!mbar_wait(&full[s], par)) {
                 cn_dev_fail(CN_DEV_WAIT_FULL);
                 ok = false;
@@ -290,11 +297,11 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
             if (u == u0) CN_STAMP(3);
 #endif
             const uint8_t* pa0 = smem + stage_off + (size_t)s * STAGE_BYTES + aoff;
-            const uint32_t xoff = xoff_lane + (uint32_t)(c * TX * XB);
+            const uint32_t xoff = xoff_lane + (uint32_t)(hc * 16 * XB);
             uint32_t bq[4];
 #pragma unroll
             for (int q = 0; q < 4; q++) bq[q] = myq == q ? xoff : (uint32_t)ZERO_OFF;
-            const float* xip = xinv_lane + c * TX;
+            const float* xip = xinv_lane + hc * 16;
             auto group = [&](int j) {
                 const uint8_t* pa = pa0 + j * (NW * 72);
                 const uint8_t* pb = pa + 8 * PSTRIDE;
@@ -328,7 +335,8 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
                 s = 0;
                 par ^= 1u;
             }
-            const bool tile_ends = c == C - 1, share_ends = u == u1 - 1;
+            u += nh, hc += nh;
+            const bool tile_ends = hc == HC, share_ends = u == u1;
             if (tile_ends || share_ends) {
                 // the quad's four lanes hold two columns each; then the eight warps' K ranges meet in shared memory
                 float a = acc0, b = acc1;
@@ -365,7 +373,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
                         } else {
                             if (!tile_ends) {
                                 // the tile goes on in the following CTAs, which took it first and have posted by now
-                                const int tile_end_u = (tile + 1) * C;
+                                const int tile_end_u = (tile + 1) * HC;
                                 for (int cc2 = cid + 1; cc2 < ncta; cc2++) {
                                     const int a2 = share_start(cc2, U, ncta), b2 = share_start(cc2 + 1, U, ncta);
                                     if (a2 >= tile_end_u) break;
@@ -402,7 +410,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_seq_kernel(const Seq
                 acc0 = acc1 = 0.0f;
                 c_first = 0;
             }
-            if (++c == C) c = 0, tile++;
+            if (hc == HC) hc = 0, tile++;
         }
         // this CTA's outputs of the step are written: arrive (warp 0 wrote them, lane 0 of it publishes)
         if (warp == 0) {
@@ -431,7 +439,7 @@ struct SeqPlan {
     SeqStepDev* steps;
     unsigned int *done, *pflag, *runs;
     float* part;
-    int nsteps, grid, stages;
+    int nsteps, grid, stages, cps, pdl;
     uint32_t stage_off;
     size_t smem;
     int device;
@@ -453,7 +461,7 @@ extern "C" int cn_nvfp4_seq_create(void** plan_out, const cn_gemv_step* steps, i
     int kmax = 0;
     for (int i = 0; i < nsteps; i++) {
         const cn_gemv_step& a = steps[i];
-        if (a.rows <= 0 || a.k < 2048 || a.k % 256 != 0)
+        if (a.rows <= 0 || a.k < 2048 || a.k % 256 != 0 || a.k > 32768)
             CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_seq_create: step %d: k = %d must be a multiple of 256 and at least 2048, rows %d positive", i, a.k, a.rows);
         if (!a.w || !a.gs || !a.x || !a.y) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_seq_create: step %d: null pointer", i);
         if (((uintptr_t)a.w & 15) || ((uintptr_t)a.w_up & 15) || ((uintptr_t)a.x & 15))
@@ -470,16 +478,23 @@ extern "C" int cn_nvfp4_seq_create(void** plan_out, const cn_gemv_step* steps, i
     cudaError_t e = cudaGetDevice(&p->device);
     int sms = 0;
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
-    // two CTAs per SM; the ring takes what the longest activation row leaves
-    const int cps = 2;
+    // three CTAs per SM when the longest activation row leaves each of them a ring of three stages, else two
     const int bprmax = kmax / 64;
     p->stage_off = (uint32_t)((XS_OFF + bprmax * XB + bprmax * 4 + 127) & ~127);
+    int cps = 3;
     int stages = (int)(((227 * 1024) / cps - 1024 - (long long)p->stage_off) / STAGE_BYTES);
+    if (stages < 3) {
+        cps = 2;
+        stages = (int)(((227 * 1024) / cps - 1024 - (long long)p->stage_off) / STAGE_BYTES);
+    }
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) {
         delete p;
         CN_FAIL(CN_ERR_LIMIT, "cn_nvfp4_seq_create: k = %d leaves no room for a weight ring beside the activation row", kmax);
     }
+    // one step that waits for nothing: a plain launch that may overlap its predecessor's tail (the CTAs still hand partial
+    // sums to one another, which a grid no larger than the machine allows); chains need every CTA resident: cooperative
+    p->cps = cps, p->pdl = (nsteps == 1 && host[0].after < 0) ? 1 : 0;
     p->stages = stages, p->grid = sms * cps, p->smem = p->stage_off + (size_t)stages * STAGE_BYTES;
     auto step = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
     const size_t n = (size_t)nsteps, g = (size_t)p->grid;
@@ -508,20 +523,30 @@ extern "C" void cn_nvfp4_seq_trace(unsigned long long* buf) { g_seq_trace = buf;
 extern "C" int cn_nvfp4_seq_run(void* plan, cn_stream_t stream) {
     SeqPlan* p = (SeqPlan*)plan;
     if (!p) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_seq_run: null plan");
-    CN_ALLOW_SMEM(nvfp4_gemv_seq_kernel<2>, 113 * 1024);
     SeqParams a;
     a.steps = p->steps, a.nsteps = p->nsteps, a.stages = p->stages, a.stage_off = p->stage_off, a.done = p->done, a.pflag = p->pflag, a.part = p->part,
-    a.runs = p->runs;
+    a.runs = p->runs, a.pdl = p->pdl;
 #ifdef CN_SEQ_TRACE
     a.trace = g_seq_trace;
 #endif
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p->grid), cfg.blockDim = dim3(NTHREADS), cfg.dynamicSmemBytes = p->smem, cfg.stream = (cudaStream_t)stream;
-    // cooperative: the CTAs wait on one another, so all of them must be resident (the launch fails otherwise)
     cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeCooperative;
-    at[0].val.cooperative = 1;
+    if (p->pdl) {
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+    } else {
+        // cooperative: the CTAs wait on one another across steps, so all of them must be resident (the launch fails otherwise)
+        at[0].id = cudaLaunchAttributeCooperative;
+        at[0].val.cooperative = 1;
+    }
     cfg.attrs = at, cfg.numAttrs = 1;
-    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_seq_kernel<2>, a));
+    if (p->cps == 3) {
+        CN_ALLOW_SMEM(nvfp4_gemv_seq_kernel<3>, 75 * 1024);
+        CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_seq_kernel<3>, a));
+    } else {
+        CN_ALLOW_SMEM(nvfp4_gemv_seq_kernel<2>, 113 * 1024);
+        CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_seq_kernel<2>, a));
+    }
     return CN_OK;
 }

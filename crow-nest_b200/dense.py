@@ -127,15 +127,23 @@ class DenseStack:
         self.chains = None
 
     def fuse(self, per_launch="token"):
-        """Run the stack's projections as persistent chains (`ops.GemvSeq`): "token" = the whole stack in one launch,
-        "layer" = one launch per layer. One activation row, one GPU. Every step waits for its predecessor, as the
-        projections of a real decode step do."""
+        """Run the stack's projections through the balanced-share kernel (`ops.GemvSeq`): "gemv" = one launch per projection
+        (every CTA an equal share of the matrix whatever its row count), "layer" = one persistent launch per layer, "token" =
+        the whole stack in one. One activation row, one GPU. Every step waits for its predecessor, as the projections of a real
+        decode step do."""
         if self.world != 1 or self.dtype != torch.bfloat16:
             raise CrownestError("the fused chain takes one bf16 row on one GPU")
         self.chains = []
         seq, prev = ops.GemvSeq(), None
         x = self.x[:1]
         for i, mats in enumerate(self.w):
+            if per_launch == "gemv":
+                for add in (lambda s: s.gemv(mats["qkv"], x, self.q[:1]), lambda s: s.gemv(mats["o"], x, self.o[:1]),
+                            lambda s: s.gemv_gu(mats["gate"], mats["up"], x, self.h[:1]), lambda s: s.gemv(mats["down"], self.h[:1], self.y[:1])):
+                    one = ops.GemvSeq()
+                    add(one)
+                    self.chains.append(one.build())
+                continue
             prev = seq.gemv(mats["qkv"], x, self.q[:1], after=prev)
             prev = seq.gemv(mats["o"], x, self.o[:1], after=prev)
             prev = seq.gemv_gu(mats["gate"], mats["up"], x, self.h[:1], after=prev)

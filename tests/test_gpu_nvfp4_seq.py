@@ -64,19 +64,26 @@ def test_fused_stack_matches_the_per_projection_launches():
     a = dense.DenseStack(cfg=cfg, seed=3)
     b = dense.DenseStack(cfg=cfg, seed=3).fuse("token")
     c = dense.DenseStack(cfg=cfg, seed=3).fuse("layer")
+    d = dense.DenseStack(cfg=cfg, seed=3).fuse("gemv")
     x = torch.randn((1, 5120), generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).cuda()
-    for st in (a, b, c):
+    for st in (a, b, c, d):
         st.x.copy_(x)
         st.run_layers(1)
     torch.cuda.synchronize()
     assert device_status() == 0
     for name in ("q", "o", "h", "y"):
         ra = from_dev_bf16(getattr(a, name))
-        for other in (b, c):
+        for other in (b, c, d):
             rb = from_dev_bf16(getattr(other, name))
             # two summation orders of the same f32 products: a bf16 ulp apart at most
             assert np.max(np.abs(ra - rb) / np.maximum(np.abs(ra), np.sqrt(np.mean(ra * ra)) / 64)) <= 2.0 ** -7, name
     assert torch.equal(b.y.view(torch.int16), c.y.view(torch.int16))  # same shares per step -> same bits
+    g2 = d.capture(1)  # one launch per projection, replayed: the same bits every time
+    y1 = d.y.clone()
+    for _ in range(3):
+        g2.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(d.y.view(torch.int16), y1.view(torch.int16))
     # under graph capture, replayed
     g = b.capture(1)
     y0 = b.y.clone()
