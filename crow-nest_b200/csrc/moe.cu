@@ -224,6 +224,16 @@ struct MoePlan {
 
 }  // namespace
 
+// the grouping step for other operators of the library (declared in nvfp4_gemv.cuh): lists of `combos` ints each, counts of 3
+int cn_moe_group_launch(const int32_t* ids, const unsigned long long* tab, int combos, int experts, int32_t* order, int* ga, int* gb, int* gbrows,
+                        int* gd, int* gdrows, int* counts, cudaStream_t stream) {
+    const size_t smem = (size_t)(3 * (experts + 1) + combos) * sizeof(int);
+    if (smem > 160 * 1024) CN_FAIL(CN_ERR_LIMIT, "grouping %d combos over %d experts needs %zu B of shared memory", combos, experts, smem);
+    CN_ALLOW_SMEM(moe_group_kernel, 160 * 1024);
+    CN_CUDA(cn_launch_pdl(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, tab, combos, experts, order, ga, gb, gbrows, gd, gdrows, counts));
+    return CN_OK;
+}
+
 extern "C" int cn_moe_sort(const int32_t* ids, int32_t* order, int combos, int experts, cn_stream_t stream) {
     if (combos < 1 || experts < 1 || experts > 8192) CN_FAIL(CN_ERR_SHAPE, "cn_moe_sort: %d combos over %d experts", combos, experts);
     const size_t smem = (size_t)(experts + 2 + combos) * sizeof(int);
@@ -331,9 +341,7 @@ int routed_experts(MoePlan* p, const unsigned long long* table_gu, const unsigne
             int* gd = gbrows + combos;
             int* gdrows = gd + combos;
             int* counts = gdrows + combos;
-            CN_ALLOW_SMEM(moe_group_kernel, 160 * 1024);
-            CN_CUDA(cn_launch_pdl(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, table_gu, combos, p->experts, p->order, ga, gb, gbrows, gd,
-                                  gdrows, counts));
+            if (int rc = cn_moe_group_launch(ids, table_gu, combos, p->experts, p->order, ga, gb, gbrows, gd, gdrows, counts, stream)) return rc;
             RoutedCall a = {};
             a.ids = ids, a.order = p->order, a.tab0 = table_gu, a.tab1 = table_up, a.fused_up_rows = table_up ? 0 : p->inter, a.gs0 = gs_gu;
             a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.x_div = x_div, a.x_f32 = dtype == CN_F32, a.y = p->h, a.ldy = p->inter, a.rows = p->inter, a.k = p->hidden;

@@ -17,11 +17,17 @@
 //            mixed FMAs; partial sums of the k-split go to scratch
 //   had_out  y = H128(sum of partials) / 128 * svh
 // The inner loop is instruction-bound, not HBM-bound: about 7 issue slots per 3-bit weight.
+// Three helpers restate reference text because their operation order defines the bits the parity contract asks for:
+// fwht128 follows mul1_fwht128 (engine/src/kernels_mul1.cu:74-88: the stage order and the a+b / a-b pairing), out_block
+// follows mul1_out_block (:98-110: partial sums left to right, then the transform, 1/128 and the scale), mul1_pair follows
+// the first half of mul1_w2 (:500-510: the multiply-hash byte sum and the f16 FMA constants of the codec).
 #include "common.cuh"
+#include "nvfp4_gemv.cuh"
 
 namespace {
 
 constexpr int MUL1_MAXT = CN_MAX_M;  // activation rows per slot
+constexpr int MUL1_GT = 4;           // rows of a group when the MoE step bundles the combos of an expert
 constexpr int RING = 4;              // stages of the tile ring
 constexpr int UROWS = 4;             // tile rows per stage
 
@@ -75,20 +81,24 @@ __device__ __forceinline__ void store_hi_lo(uint16_t* xh, size_t plane, size_t a
 
 // xh16[slot][t][k] = the hi / lo planes of H128(x * suh) * mul, xinv[slot][t][k/128] = 1/mul.
 // grid (k/128, T, slots), block 32. XT: 0 f32, 1 bf16 input. x row of slot: x + (slot / x_div) * T * k.
+// rowsrc (optional): the x row of (slot, t) as an index into x [rows][k], negative = an unused row slot (stored as zeros)
 template <int XT>
 __global__ void mul1_had_in_kernel(const unsigned long long* __restrict__ ptrs, const void* __restrict__ x, uint16_t* __restrict__ xh,
-                                   float* __restrict__ xinv, int k, int T, long long suh_off, int x_div, size_t plane) {
+                                   float* __restrict__ xinv, int k, int T, long long suh_off, int x_div, size_t plane,
+                                   const int* __restrict__ rowsrc) {
     pdl_launch_dependents();
     pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
     if (ptrs[slot] == 0ull) return;  // a null record: nothing to read or write
     const uint16_t* suh = (const uint16_t*)(ptrs[slot] + (unsigned long long)suh_off);
-    const size_t xrow = ((size_t)(slot / x_div) * T + t) * k, row = ((size_t)slot * T + t) * k;
+    const int src = rowsrc ? rowsrc[slot * T + t] : 0;
+    const size_t xrow = rowsrc ? (size_t)(src < 0 ? 0 : src) * k : ((size_t)(slot / x_div) * T + t) * k, row = ((size_t)slot * T + t) * k;
     const int c0 = blk * 128 + 4 * lane;
     float v[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        const float xv = XT == 1 ? __bfloat162float(((const __nv_bfloat16*)x)[xrow + c0 + j]) : ((const float*)x)[xrow + c0 + j];
+        float xv = XT == 1 ? __bfloat162float(((const __nv_bfloat16*)x)[xrow + c0 + j]) : ((const float*)x)[xrow + c0 + j];
+        if (src < 0) xv = 0.0f;
         v[j] = __fmul_rn(xv, h2f(suh[c0 + j]));
     }
     fwht128(v, lane);
@@ -314,16 +324,19 @@ __device__ __forceinline__ void out_block(float v[4], const float* __restrict__ 
 }
 
 // grid (n/128, T, slots), block 32. YT: 0 f32, 1 bf16 output; y row = slot * T + t
+// rowdst (optional): the y row of (slot, t) as an index into y [rows][n], negative = nothing to store
 template <int YT>
 __global__ void mul1_had_out_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part, void* __restrict__ y, int n,
-                                    int S, int T, long long svh_off) {
+                                    int S, int T, long long svh_off, const int* __restrict__ rowdst) {
     pdl_launch_dependents();
     pdl_wait();  // everything below may read what earlier kernels of the stream wrote
     const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
     if (ptrs[slot] == 0ull) return;
+    const int dst = rowdst ? rowdst[slot * T + t] : 0;
+    if (dst < 0) return;
     float v[4];
     out_block(v, part, (const uint16_t*)(ptrs[slot] + (unsigned long long)svh_off), slot, S, T, t, n, blk, lane);
-    const size_t at = ((size_t)slot * T + t) * n + blk * 128 + 4 * lane;
+    const size_t at = (rowdst ? (size_t)dst : (size_t)slot * T + t) * n + blk * 128 + 4 * lane;
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         if (YT == 1)
@@ -402,6 +415,11 @@ struct Mul1Plan {
     float *xinv_a, *xinv_b;  // [slots][T][kmax/128]
     float *part_a, *part_b;  // [slots][16][T][kmax]
     unsigned long long* ptrs;  // [slots] gathered record addresses (MoE form)
+    int32_t* order;            // [slots] combos sorted by expert (grouped MoE form)
+    int* groups;               // [5 * slots + 8] the group lists and counts of cn_moe_group_launch
+    int* rowsrc;               // [slots * MUL1_GT] x row of every (group slot, row), -1 = unused
+    int* rowdst;               // [slots * MUL1_GT] combo (output row) of every (group slot, row), -1 = unused
+    int grp_rows;              // rows the scratch holds per slot: max(max_t, MUL1_GT)
     float* eo;                 // [slots][T][hidden] expert outputs (MoE form)
     // the up projection does not depend on the gate projection: it runs on a side stream between two events
     cudaStream_t side;
@@ -429,12 +447,12 @@ Mul1Spec spec_of(const Mul1Plan* p, int which) {
 }
 
 int launch_had_in(const unsigned long long* ptrs, const void* x, uint16_t* xh, float* xinv, const Mul1Spec& s, int slots, int T, int x_div,
-                  int dtype, size_t plane, cudaStream_t st) {
+                  int dtype, size_t plane, cudaStream_t st, const int* rowsrc = nullptr) {
     dim3 grid(s.k / 128, T, slots);
     if (dtype == CN_BF16)
-        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane));
+        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane, rowsrc));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane));
+        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane, rowsrc));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
@@ -487,6 +505,27 @@ __global__ void mul1_gather_kernel(const unsigned long long* __restrict__ table,
     if (c < n) ptrs[c] = (ids[c] < 0 || (experts > 0 && ids[c] >= experts)) ? 0ull : table[ids[c]];
 }
 
+// Slot s of the grouped MoE form: the groups of two to four rows first, then the one-row groups, then empty slots (null
+// record). Fills the slot's record address and, per row, where its x row comes from and which combo's output row it is.
+__global__ void mul1_slots_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ ids, const int32_t* __restrict__ order,
+                                  const int* __restrict__ ga, const int* __restrict__ gb, const int* __restrict__ gbrows, const int* __restrict__ counts,
+                                  unsigned long long* __restrict__ ptrs, int* __restrict__ rowsrc, int* __restrict__ rowdst, int slots, int x_div) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= slots) return;
+    const int na = counts[0], nb = counts[1];
+    int pos = -1, rows = 0;
+    if (s < nb) pos = gb[s], rows = gbrows[s];
+    else if (s < nb + na) pos = ga[s - nb], rows = 1;
+    ptrs[s] = pos < 0 ? 0ull : table[ids[order[pos]]];
+    for (int t = 0; t < MUL1_GT; t++) {
+        const int c = t < rows ? order[pos + t] : -1;
+        rowsrc[s * MUL1_GT + t] = c < 0 ? -1 : c / x_div;
+        rowdst[s * MUL1_GT + t] = c;
+    }
+}
+
 }  // namespace
 
 extern "C" int cn_mul1_plan_destroy(void* plan);
@@ -499,7 +538,9 @@ extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int b
     Mul1Plan* p = new Mul1Plan();
     p->hidden = hidden, p->inter = inter, p->bits = bits, p->half = half, p->n32 = 8 * bits + (half ? 4 : 0), p->max_slots = max_slots, p->max_t = max_t;
     p->kmax = hidden > inter ? hidden : inter;
-    const size_t rows = (size_t)max_slots * max_t;
+    // the grouped MoE form runs every slot with MUL1_GT rows: the scratch is sized for that
+    p->grp_rows = max_t > MUL1_GT ? max_t : MUL1_GT;
+    const size_t rows = (size_t)max_slots * p->grp_rows;
     p->plane = rows * p->kmax;
     // a failure part-way frees what the earlier steps got (the destroy call takes a half-built plan)
     cudaError_t e = cudaSuccess;
@@ -511,6 +552,10 @@ extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int b
     step(cudaMalloc(&p->part_a, rows * 16 * p->kmax * 4));
     step(cudaMalloc(&p->part_b, rows * 16 * p->kmax * 4));
     step(cudaMalloc(&p->ptrs, (size_t)max_slots * 8));
+    step(cudaMalloc(&p->order, (size_t)max_slots * 4));
+    step(cudaMalloc(&p->groups, ((size_t)5 * max_slots + 8) * 4));
+    step(cudaMalloc(&p->rowsrc, (size_t)max_slots * MUL1_GT * 4));
+    step(cudaMalloc(&p->rowdst, (size_t)max_slots * MUL1_GT * 4));
     step(cudaMalloc(&p->eo, rows * hidden * 4));
     step(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
     step(cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming));
@@ -527,7 +572,7 @@ extern "C" int cn_mul1_plan_destroy(void* plan) {
     Mul1Plan* p = (Mul1Plan*)plan;
     if (!p) return CN_OK;
     cudaFree(p->xh_a), cudaFree(p->xh_b), cudaFree(p->xinv_a), cudaFree(p->xinv_b), cudaFree(p->part_a), cudaFree(p->part_b), cudaFree(p->ptrs),
-        cudaFree(p->eo);
+        cudaFree(p->eo), cudaFree(p->order), cudaFree(p->groups), cudaFree(p->rowsrc), cudaFree(p->rowdst);
     if (p->side) cudaStreamDestroy(p->side);
     if (p->fork) cudaEventDestroy(p->fork);
     if (p->join) cudaEventDestroy(p->join);
@@ -547,24 +592,24 @@ extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptr
     if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, s, slots, t, p->plane, st)) return rc;
     dim3 grid(s.n / 128, t, slots);
     if (dtype == CN_BF16)
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
 
 // y[slot][t] = down(act(gate x, up x)) as f32 when out_f32, else in `dtype`
 static int mul1_ffn(Mul1Plan* p, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, float limit, int dtype,
-                    int out_f32, cudaStream_t st) {
+                    int out_f32, cudaStream_t st, const int* rowsrc = nullptr, const int* rowdst = nullptr) {
     const Mul1Spec g = spec_of(p, 0), u = spec_of(p, 1), d = spec_of(p, 2);
     // up branch on the side stream; it is joined again on every path, so a capture of `st` stays valid
     CN_CUDA(cudaEventRecord(p->fork, st));
     CN_CUDA(cudaStreamWaitEvent(p->side, p->fork, 0));
-    int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, p->plane, p->side);
+    int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, p->plane, p->side, rowsrc);
     if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, p->plane, p->side);
     CN_CUDA(cudaEventRecord(p->join, p->side));
-    if (rc == CN_OK) rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, p->plane, st);
+    if (rc == CN_OK) rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, p->plane, st, rowsrc);
     if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, p->plane, st);
     CN_CUDA(cudaStreamWaitEvent(st, p->join, 0));
     if (rc != CN_OK) return rc;
@@ -574,9 +619,9 @@ static int mul1_ffn(Mul1Plan* p, const unsigned long long* ptrs, const void* x, 
     if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, d, slots, t, p->plane, st)) return rc;
     dim3 grid(d.n / 128, t, slots);
     if (dtype == CN_BF16 && !out_f32)
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off, rowdst));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off, rowdst));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
@@ -600,6 +645,22 @@ extern "C" int cn_moe_mul1_experts(void* plan, const unsigned long long* table, 
     if (x_div < 1 || !eo) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_experts: x_div %d, eo %p", x_div, (void*)eo);
     if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_experts: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     cudaStream_t st = (cudaStream_t)stream;
+    if (experts > 0 && combos >= 16 * experts && p->max_t <= MUL1_GT) {
+        // A long batch (sixteen combo slots per expert or more; measured: with four rows per expert the four-row kernel at two CTAs per
+        // SM is no faster than four one-row slots at four CTAs per SM): the combos are sorted by
+        // expert and bundled into groups of up to four rows that share one decode of the expert's trellis
+        int* ga = p->groups;
+        int* gb = ga + combos;
+        int* gbrows = gb + combos;
+        int* gd = gbrows + combos;
+        int* gdrows = gd + combos;
+        int* counts = gdrows + combos;
+        if (int rc = cn_moe_group_launch(ids, table, combos, experts, p->order, ga, gb, gbrows, gd, gdrows, counts, st)) return rc;
+        CN_CUDA(cn_launch_pdl(mul1_slots_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->order, ga, gb, gbrows, counts, p->ptrs, p->rowsrc,
+                              p->rowdst, combos, x_div));
+        // every slot beyond the groups is a null record, which all kernels skip; a group's unused rows are zero rows
+        return mul1_ffn(p, p->ptrs, x, eo, combos, MUL1_GT, 1, limit, dtype, 1, st, p->rowsrc, p->rowdst);
+    }
     CN_CUDA(cn_launch_pdl(mul1_gather_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->ptrs, combos, experts));
     CN_CUDA(cudaGetLastError());
     return mul1_ffn(p, p->ptrs, x, eo, combos, 1, x_div, limit, dtype, 1, st);
@@ -691,9 +752,9 @@ extern "C" int cn_mul1_gemv_noalloc(int which, int hidden, int inter, int bits, 
     if (int rc = launch_gemv(ptrs, xh, xinv, part, s, slots, t, plane, st)) return rc;
     dim3 grid(s.n / 128, t, slots);
     if (dtype == CN_BF16)
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }

@@ -132,3 +132,29 @@ def test_moe_step_over_mul1_experts_matches_the_cpu_reference(tokens):
     # bf16 in / out (ulp taken no lower than rms / 64: the combine cancels)
     check_close(from_dev_bf16(y), ref, f"mul1 moe tokens={tokens}", ulp_floor=1.0 / 64)
     plan.free()
+
+
+@pytest.mark.parametrize("tokens,experts,topk", [(32, 6, 3), (40, 5, 4), (10, 6, 3)])
+def test_moe_step_with_bundled_rows_matches_the_cpu_reference(tokens, experts, topk):
+    """At least two combo slots per expert: the combos are sorted by expert and run as groups of up to four rows that share
+    one decode of the expert (one, two, three and four-row groups and unused row slots all occur)."""
+    hidden, inter, K = 1024, 512, 3.0
+    rng = np.random.default_rng(7 + tokens)
+    recs = [tk.mul1_record(0x2000 + 5 * e, hidden, inter, K) for e in range(experts)]
+    d = [dev(r) for r in recs]
+    table = torch.tensor([r.data_ptr() for r in d], dtype=torch.int64, device="cuda")
+    x = (rng.standard_normal((tokens, hidden)) * 0.25).astype(np.float32)
+    logits = rng.standard_normal((tokens, experts)).astype(np.float32)
+    ids, wts = moe.route_softmax_topk(dev(logits), topk)
+    rids, rw = oracle.route_softmax_topk(logits, topk)
+    assert np.array_equal(ids.cpu().numpy(), rids)
+    plan = mul1.Mul1Plan(hidden, inter, K, slots=tokens * topk, tokens=1)
+    y = plan.moe(table, ids, wts, dev(x), limit=10.0)
+    ye = np.zeros((tokens * topk, hidden), np.float32)
+    for c in range(tokens * topk):
+        ye[c] = oracle.mul1_expert_ffn(recs[rids.reshape(-1)[c]], hidden, inter, K, x[c // topk: c // topk + 1], limit=10.0, threads=8)[0]
+    ref = oracle.moe_combine(ye, rw, None)
+    check_close(y.cpu().numpy(), ref, f"mul1 moe bundled tokens={tokens}", bf16_out=False)
+    y2 = plan.moe(table, ids, wts, dev(x), limit=10.0)
+    assert torch.equal(y.view(torch.int32), y2.view(torch.int32))
+    plan.free()
