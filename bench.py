@@ -385,19 +385,36 @@ def gemv_arm(args, rank, world, local):
     gen = torch.Generator(device=dev)
     gen.manual_seed(0)
     one = torch.ones(1, device=dev)
-    ws = [ops.Fp4(dense._rand_nvfp4_device(rows, k, gen, dev), one, rows, k) for _ in range(copies)]
+    op = args.op
+    if op == "fp8":
+        nb = rows * k
+        copies = max(2, int(math.ceil(512 * 2 ** 20 / nb)))
+        per_graph = max(64, copies)
+        ws = [torch.randint(0, 120, (rows * k,), dtype=torch.uint8, device=dev, generator=gen) for _ in range(copies)]
+        sc = torch.rand(((rows + 127) // 128) * ((k + 127) // 128), device=dev, generator=gen) * 0.01 + 0.005
+        launch = lambda w, xx, yy: ops.fp8_gemv(w, sc, xx, rows, k, yy)
+    elif op == "gu":  # fused gate/up: `rows` outputs from two [rows][k] matrices
+        nb *= 2
+        copies = max(2, int(math.ceil(512 * 2 ** 20 / nb)))
+        per_graph = max(64, copies)
+        ws = [(ops.Fp4(dense._rand_nvfp4_device(rows, k, gen, dev), one, rows, k), ops.Fp4(dense._rand_nvfp4_device(rows, k, gen, dev), one, rows, k))
+              for _ in range(copies)]
+        launch = lambda w, xx, yy: ops.launch_gemv_gu(w[0], w[1], xx, yy)
+    else:
+        ws = [ops.Fp4(dense._rand_nvfp4_device(rows, k, gen, dev), one, rows, k) for _ in range(copies)]
+        launch = lambda w, xx, yy: ops.launch_gemv(w, xx, yy)
     x_host = torch.randn((m, k), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
     x = x_host.to(dev)
     y = torch.empty((m, rows), dtype=torch.bfloat16, device=dev)
     y_host = torch.empty((m, rows), dtype=torch.bfloat16).pin_memory()
     st = torch.cuda.Stream()
     with torch.cuda.stream(st):
-        ops.launch_gemv(ws[0], x, y)
+        launch(ws[0], x, y)
         st.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=st):
             for i in range(per_graph):
-                ops.launch_gemv(ws[i % copies], x, y)
+                launch(ws[i % copies], x, y)
     tm = Timer(1)
     sampler = ClockSampler(local)
     sampler.start()
@@ -406,7 +423,7 @@ def gemv_arm(args, rank, world, local):
 
     def host_step():
         x.copy_(x_host, non_blocking=True)
-        ops.launch_gemv(ws[i[0] % copies], x, y)
+        launch(ws[i[0] % copies], x, y)
         i[0] += 1
         y_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
@@ -419,16 +436,17 @@ def gemv_arm(args, rank, world, local):
     peak, peak_kind = measured_peak()
     line = {"metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"single NVFP4 GEMV [{rows} x {k}], M={m}; a step = {per_graph} launches", "activations": "bf16 in/out, f32 accumulate",
+            "config": {"workload": f"single {'FP8' if op == 'fp8' else 'NVFP4'} {'fused gate/up ' if op == 'gu' else ''}GEMV [{rows} x {k}], M={m}; a step = {per_graph} launches",
+                       "activations": "bf16 in/out, f32 accumulate",
                        "l2": f"{copies} distinct weight copies ({copies * nb / 2 ** 20:.0f} MiB) rotated launch by launch: larger than L2",
                        "launch": f"CUDA graph replay of {per_graph} launches"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "nvfp4_gemv_m1_kernel", "bytes_per_launch": bytes_launch, "us_per_launch": us},
+                         "kernel": "fp8_gemv_tc_kernel" if op == "fp8" else "nvfp4_gemv_m1_kernel", "bytes_per_launch": bytes_launch, "us_per_launch": us},
             "blocks": t["blocks"], "ms_per_step_min": t["ms_per_step_min"], "ms_per_step_max": t["ms_per_step_max"],
             "e2e": {"value": bytes_launch / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
                     "note": "one launch per host call"},
             "gpu_launches": args.steps * t["blocks"] * per_graph, "clocks": clocks, "device_status": _lib.device_status()}
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and op == "gemv":
         import oracle
         cores = os.cpu_count() or 1
         hw = [w.w.cpu().numpy() for w in ws[:min(copies, 24)]]
@@ -606,6 +624,7 @@ def main():
                     help="dense = the headline (layer stack); gemv = one matrix (default 4096 x 4096); moe / mul1 = routed experts; gemm = batched rows")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
     ap.add_argument("--engine", default="auto", choices=["auto", "fp4", "f16"], help="gemm: block-scaled FP4 MMA, f16 MMA on widened weights, or by row count")
+    ap.add_argument("--op", default="gemv", choices=["gemv", "gu", "fp8"], help="gemv workload: plain NVFP4 GEMV, fused gate/up, or the FP8 GEMV")
     ap.add_argument("--rows", type=int, default=4096, help="gemv: output rows")
     ap.add_argument("--cols", type=int, default=4096, help="gemv: k")
     args = ap.parse_args()

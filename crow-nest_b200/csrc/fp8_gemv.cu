@@ -13,6 +13,8 @@
 // activation scale are applied to each 16-value partial sum. Lanes are reduced with xor shuffles.
 #include "common.cuh"
 
+int cn_fp8_gemv_tc_launch(const void* w, const float* scale, const void* x, void* y, int rows, int cols, int m, int ldy, int dtype, cudaStream_t st);
+
 namespace {
 
 constexpr int WARPS = 8;
@@ -142,6 +144,12 @@ extern "C" int cn_fp8_gemv(const void* w, const float* scale, const void* x, voi
     if (m < 1 || m > CN_MAX_M) CN_FAIL(CN_ERR_LIMIT, "cn_fp8_gemv: m = %d, the kernel takes 1..%d activation rows", m, CN_MAX_M);
     if (ldy < rows) CN_FAIL(CN_ERR_SHAPE, "cn_fp8_gemv: ldy %d < rows %d", ldy, rows);
     if (((uintptr_t)w & 15) || ((uintptr_t)x & 15)) CN_FAIL(CN_ERR_SHAPE, "cn_fp8_gemv: weight and activation pointers must be 16-byte aligned");
+    if (dtype != CN_BF16 && dtype != CN_F32) CN_FAIL(CN_ERR_SHAPE, "cn_fp8_gemv: dtype %d is neither CN_F32 nor CN_BF16", dtype);
+    // whole 128-column blocks: the tensor-core kernel (fp8_gemv_tc.cu); ragged rows stay on the warp-per-row kernel below
+    {
+        const int rc = cn_fp8_gemv_tc_launch(w, scale, x, y, rows, cols, m, ldy, dtype, (cudaStream_t)stream);
+        if (rc >= 0) return rc;
+    }
     if (dtype == CN_BF16) return launch<1>(w, scale, x, y, rows, cols, m, ldy, (cudaStream_t)stream);
     if (dtype == CN_F32) return launch<0>(w, scale, x, y, rows, cols, m, ldy, (cudaStream_t)stream);
     CN_FAIL(CN_ERR_SHAPE, "cn_fp8_gemv: dtype %d is neither CN_F32 nor CN_BF16", dtype);

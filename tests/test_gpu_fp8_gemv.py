@@ -25,7 +25,9 @@ def test_fp8_gemv_bf16_matches_the_cpu_reference(rows, cols, m):
     xb, xf = synth.activations(m, cols, rng)
     ref = oracle.fp8_gemv(q, rows, cols, s, xf)
     y = ops.fp8_gemv(torch.from_numpy(q).cuda(), torch.from_numpy(s).cuda(), to_dev_bf16(xb), rows, cols)
-    check_close(from_dev_bf16(y), ref, f"fp8 [{rows},{cols}] m={m}")
+    # up to 28,000 outputs: a few cancel to 1e-4 of the row's scale, where the f32 accumulation error of either side is
+    # already several bf16 ulp of the value; the ulp is taken no lower than rms / 256
+    check_close(from_dev_bf16(y), ref, f"fp8 [{rows},{cols}] m={m}", ulp_floor=1.0 / 256)
 
 
 def test_fp8_gemv_f32_and_row_invariance():
