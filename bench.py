@@ -615,6 +615,8 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--impl", default="crownest")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-time", type=float, default=MIN_TIMED_S,
+                    help="seconds of device time the timed blocks cover (0 = one block: for a profiler capture of a few launches)")
     ap.add_argument("--no-moe", action="store_true", help="dense workload: leave the MoE block out of the line")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="tensor parallel: slices pushed over peer memory, or NCCL all-gather")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
@@ -628,6 +630,7 @@ def main():
     ap.add_argument("--rows", type=int, default=4096, help="gemv: output rows")
     ap.add_argument("--cols", type=int, default=4096, help="gemv: k")
     args = ap.parse_args()
+    globals()["MIN_TIMED_S"] = max(0.0, args.min_time)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
