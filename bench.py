@@ -493,6 +493,7 @@ def gemm_arm(args, rank, world, local):
     # the weights serves every token; beyond that its operand traffic (five cascade columns per token) binds on L2 and the f16
     # MMA on losslessly widened weights is faster (both are tcgen05)
     fp4 = args.engine == "fp4" or (args.engine == "auto" and m <= 128)
+    raw_rows = ups[0].w[: 1024 * (hidden // 64 * 36)].cpu().numpy() if world == 1 and not args.no_cpu_baseline else None
     if fp4:
         ups, downs = [ops.Fp4Packed(w) for w in ups], [ops.Fp4Packed(w) for w in downs]
         nws = max(int(_lib.lib().cn_nvfp4_bs_workspace_bytes(inter // world, hidden, m)), int(_lib.lib().cn_nvfp4_bs_workspace_bytes(hidden // world, inter, m)))
@@ -548,7 +549,7 @@ def gemm_arm(args, rank, world, local):
             import oracle
             cores = os.cpu_count() or 1
             rows_s, toks = 1024, min(m, 8)  # a bounded sample: 1024 output rows of the first matrix for 8 tokens
-            wsub = ups[0].w[: rows_s * (hidden // 64 * 36)].cpu().numpy()
+            wsub = raw_rows
             xf = x_host[:toks].float().numpy()
             med, calls = _median_calls(lambda j: oracle.nvfp4_gemv(wsub, rows_s, hidden, 1.0, xf, threads=cores, path=1), 3.0)
             line["cpu_baseline"] = {"value": 2.0 * toks * rows_s * hidden / med / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",

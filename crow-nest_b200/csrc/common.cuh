@@ -144,6 +144,14 @@ __device__ __forceinline__ float fma_f16_f32(uint16_t a, uint16_t b, float c) {
 __device__ __forceinline__ float f16lo_to_f32(uint32_t h2) { return __half2float(__ushort_as_half((uint16_t)(h2 & 0xffff))); }
 __device__ __forceinline__ float f16hi_to_f32(uint32_t h2) { return __half2float(__ushort_as_half((uint16_t)(h2 >> 16))); }
 
+// C (16 x 8, f32) += A (16 x 16, f16, row major) x B (16 x 8, f16, column major) on the warp's tensor cores.
+// not volatile: a pure function of its operands, free to be scheduled between the shared-memory loads
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // four code bytes of one word -> four f16x2 (byte i -> h[i]); the byte split is left to the
 // assembler (vector mov), which measured 1.5x faster than shift-and-mask in front of each cvt
 __device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t word, uint32_t h[4]) {

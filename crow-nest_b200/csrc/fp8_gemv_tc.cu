@@ -38,11 +38,6 @@ struct Fp8Params {
     uint32_t xrow, stage_off;  // bytes of one staged activation row (padded); where the ring starts
 };
 
-__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 // four E4M3 bytes -> two f16x2 (bytes 0,1 and bytes 2,3); every E4M3 value is exact in f16
 __device__ __forceinline__ void e4m3x4_to_f16x2(uint32_t word, uint32_t& lo, uint32_t& hi) {
     asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}" : "=r"(lo), "=r"(hi) : "r"(word));

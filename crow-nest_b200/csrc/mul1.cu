@@ -30,6 +30,7 @@ constexpr int MUL1_MAXT = CN_MAX_M;  // activation rows per slot
 constexpr int MUL1_GT = 4;           // rows of a group when the MoE step bundles the combos of an expert
 constexpr int RING = 4;              // stages of the tile ring
 constexpr int UROWS = 4;             // tile rows per stage
+constexpr int XPAD = 8;              // f16 elements added to the pitch of a staged activation row
 
 struct Mul1Spec {
     int k, n;        // in, out
@@ -151,7 +152,7 @@ __device__ __forceinline__ void lane_states(const uint32_t* tile, int n32, const
 // part[slot][sp][t][n]; xh16 [slot][T][k] f16, xinv [slot][T][k/128].
 // MT: activation rows the register allocation is built for (1, 2, 4 or 8; T <= MT of them live)
 template <bool K3, int MT>
-__global__ void __launch_bounds__(288, MT == 1 ? 4 : (MT == 2 ? 3 : (MT == 4 ? 2 : 1))) mul1_gemv_kernel(const unsigned long long* __restrict__ ptrs, const uint16_t* __restrict__ xh,
+__global__ void __launch_bounds__(288, 4) mul1_gemv_kernel(const unsigned long long* __restrict__ ptrs, const uint16_t* __restrict__ xh,
                                                         const float* __restrict__ xinv, float* __restrict__ part, Mul1Spec sp_, int S, int T,
                                                         size_t plane, int SPC) {
     pdl_launch_dependents();
@@ -170,8 +171,11 @@ __global__ void __launch_bounds__(288, MT == 1 ? 4 : (MT == 2 ? 3 : (MT == 4 ? 2
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + RING;
     uint32_t* ring = (uint32_t*)(smem + 128);                                   // [RING][UROWS][8][n32]
-    uint16_t* xs = (uint16_t*)(smem + 128 + (size_t)RING * UROWS * run_bytes);  // [2][T][rows] f16: hi plane, lo plane
-    float* xi = (float*)(xs + (size_t)2 * T * rows);                            // [T][rows/128]
+    // [2][T][pitch] f16: hi plane, lo plane; a row pitch of 16 bytes more than a multiple of 256 keeps the eight rows
+    // the lanes of a warp read at once on distinct banks
+    const int pitch = rows + XPAD;
+    uint16_t* xs = (uint16_t*)(smem + 128 + (size_t)RING * UROWS * run_bytes);
+    float* xi = (float*)(xs + (size_t)2 * T * pitch);  // [T][rows/128]
     if (threadIdx.x == 0) {
         for (int s = 0; s < RING; s++) {
             mbar_init(&full[s], 1);
@@ -212,8 +216,8 @@ __global__ void __launch_bounds__(288, MT == 1 ? 4 : (MT == 2 ? 3 : (MT == 4 ? 2
     for (int i = threadIdx.x; i < T * rows / 2; i += 256) {
         const int t = i / (rows / 2), r = i - t * (rows / 2);
         const size_t at = ((size_t)slot * T + t) * k + (size_t)kb0 * 16;
-        ((uint32_t*)xs)[i] = ((const uint32_t*)(xh + at))[r];
-        ((uint32_t*)(xs + (size_t)T * rows))[i] = ((const uint32_t*)(xh + plane + at))[r];
+        ((uint32_t*)(xs + (size_t)t * pitch))[r] = ((const uint32_t*)(xh + at))[r];
+        ((uint32_t*)(xs + (size_t)(T + t) * pitch))[r] = ((const uint32_t*)(xh + plane + at))[r];
     }
     const int nblk = rows / 128;
     for (int i = threadIdx.x; i < T * nblk; i += 256) {
@@ -231,79 +235,96 @@ __global__ void __launch_bounds__(288, MT == 1 ? 4 : (MT == 2 ? 3 : (MT == 4 ? 2
         lo[j] = (eb - 16 + sbits) % sbits;
     }
     const int wi0 = lo[0] >> 5, sh0 = lo[0] & 31;
-    const int q2 = 2 * (lane & 3);
-    float tot0[MT], tot1[MT];
+    // Multiply-accumulate on the tensor cores. The eight weights a lane decodes from a tile are the A fragment of one
+    // mma.m16n8k16 as they stand (MMA row = output column g / g + 8 of the tile, MMA k = the tile's k): w01 | w45 | w23 |
+    // w67. Column c of the B operand is activation row c >> 1, plane c & 1 (hi, lo), so one MMA serves four activation
+    // rows and a lane (g, t) ends up with the hi and lo sums of activation row t for outputs g and g + 8: nothing is
+    // exchanged between lanes. Columns of rows beyond T repeat the last live row and are never stored.
+    const int g = lane >> 2, t4 = lane & 3;
+    constexpr int NM = MT > 4 ? 2 : 1;  // MMAs per tile: four activation rows each
+    const uint16_t* xb[NM];
+    const float* xil[NM];
 #pragma unroll
-    for (int t = 0; t < MT; t++) tot0[t] = tot1[t] = 0.0f;
-    float a0e[MT], a0o[MT], a1e[MT], a1o[MT];  // hi plane, even / odd chains
-    float l0e[MT], l0o[MT], l1e[MT], l1o[MT];  // lo plane
+    for (int i = 0; i < NM; i++) {
+        const int rb = min(4 * i + (g >> 1), T - 1), rc = min(4 * i + t4, T - 1);
+        xb[i] = xs + ((size_t)(g & 1) * T + rb) * pitch + 2 * t4;
+        xil[i] = xi + rc * nblk;
+    }
+    float acc[NM][4], tot0[NM], tot1[NM];
 #pragma unroll
-    for (int t = 0; t < MT; t++) a0e[t] = a0o[t] = a1e[t] = a1o[t] = l0e[t] = l0o[t] = l1e[t] = l1o[t] = 0.0f;
+    for (int i = 0; i < NM; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = tot0[i] = tot1[i] = 0.0f;
+    // Everything a tile needs beyond its own words is a constant offset from pointers that move once per stage: at
+    // K = 3 a tile is 24 words, and a split is a whole number of stages and of 128-row blocks (tps % 8 == 0, which
+    // the launcher guarantees), so the loop carries no division, no bounds test and no address arithmetic per tile.
+    constexpr int TW = K3 ? 24 : 0;  // words of a tile when known at compile time
+    const int tw = K3 ? TW : n32;
+    const int o1 = wi0 + 1 >= tw ? wi0 + 1 - tw : wi0 + 1, o2 = wi0 + 2 >= tw ? wi0 + 2 - tw : wi0 + 2;
+    const uint32_t* lane_tile = ring + (size_t)warp * tw;  // this warp's tile of the ring's first tile row
+    int s = 0, cs = 0, spi = 0, blk = 0;
+    uint32_t ph = 0;
     for (int c = 0; c < nst; c++) {
-        const int s = c % RING;
-        if (!mbar_wait(&full[s], (c / RING) & 1)) {
+        if (!mbar_wait(&full[s], ph)) {
             cn_dev_fail(CN_DEV_WAIT_FULL);
             return;
         }
-        const int spi = c / nst1, cs = c - spi * nst1;
-        const int live = min(UROWS, tps - cs * UROWS);
-        for (int u = 0; u < live; u++) {
-            const int kt = spi * tps + cs * UROWS + u;  // tile row within the CTA's splits
-            const uint32_t* tile = ring + ((size_t)(s * UROWS + u) * 8 + warp) * n32;
+        const uint32_t* tb = lane_tile + (size_t)s * (UROWS * 8) * tw;
+        const int kx = (spi * tps + cs * UROWS) * 16;  // first k of the stage within the staged activations
+#pragma unroll
+        for (int u = 0; u < UROWS; u++) {
             uint32_t st[8];
-            lane_states<K3>(tile, n32, lo, wi0, sh0, st);
+            if (K3) {
+                // words wi0, wi0 + 1, wi0 + 2 (circular) hold bits [24 g - 13, 24 g + 24) of the tile; the window is
+                // aligned to the lane's first bit and state j = bits [3 j, 3 j + 16) of it, most significant bit first
+                const uint32_t* tl = tb + u * 8 * TW;
+                const uint32_t w0 = tl[wi0], w1 = tl[o1], w2 = tl[o2];
+                const uint32_t hi = __funnelshift_l(w1, w0, sh0), lw = __funnelshift_l(w2, w1, sh0);
+                st[0] = hi >> 16;
+                st[1] = (hi >> 13) & 0xffffu;
+                st[2] = (hi >> 10) & 0xffffu;
+                st[3] = (hi >> 7) & 0xffffu;
+                st[4] = (hi >> 4) & 0xffffu;
+                st[5] = (hi >> 1) & 0xffffu;
+                st[6] = __funnelshift_l(lw, hi, 18) >> 16;
+                st[7] = __funnelshift_l(lw, hi, 21) >> 16;
+            } else {
+                lane_states<false>(tb + (size_t)u * 8 * tw, n32, lo, wi0, sh0, st);
+            }
             const uint32_t w01 = mul1_pair(st[0], st[1]), w23 = mul1_pair(st[2], st[3]);
             const uint32_t w45 = mul1_pair(st[4], st[5]), w67 = mul1_pair(st[6], st[7]);
 #pragma unroll
-            for (int t = 0; t < MT; t++) {
-                if (t < T) {
-                    const uint32_t* xr = (const uint32_t*)(xs + (size_t)t * rows + kt * 16 + q2);
-                    const uint32_t x01 = xr[0], x89 = xr[4];
-                    fma2_f16_f32(a0e[t], a0o[t], w01, x01);
-                    fma2_f16_f32(a0e[t], a0o[t], w23, x89);
-                    fma2_f16_f32(a1e[t], a1o[t], w45, x01);
-                    fma2_f16_f32(a1e[t], a1o[t], w67, x89);
-                    const uint32_t* xl = xr + (size_t)T * rows / 2;
-                    const uint32_t y01 = xl[0], y89 = xl[4];
-                    fma2_f16_f32(l0e[t], l0o[t], w01, y01);
-                    fma2_f16_f32(l0e[t], l0o[t], w23, y89);
-                    fma2_f16_f32(l1e[t], l1o[t], w45, y01);
-                    fma2_f16_f32(l1e[t], l1o[t], w67, y89);
-                }
-            }
-            if ((kt & 7) == 7) {
-                // end of a 128-row block: undo its activation scale
-#pragma unroll
-                for (int t = 0; t < MT; t++) {
-                    if (t < T) {
-                        const float inv = xi[t * nblk + (kt >> 3)];
-                        tot0[t] = fmaf(fmaf(l0e[t] + l0o[t], 4.8828125e-4f, a0e[t] + a0o[t]), inv, tot0[t]);
-                        tot1[t] = fmaf(fmaf(l1e[t] + l1o[t], 4.8828125e-4f, a1e[t] + a1o[t]), inv, tot1[t]);
-                        a0e[t] = a0o[t] = a1e[t] = a1o[t] = l0e[t] = l0o[t] = l1e[t] = l1o[t] = 0.0f;
-                    }
-                }
+            for (int i = 0; i < NM; i++) {
+                const uint32_t* xr = (const uint32_t*)(xb[i] + kx + u * 16);
+                mma16816(acc[i], w01, w45, w23, w67, xr[0], xr[4]);
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-        if (cs == nst1 - 1) {
-            // end of a split: the four lanes of a column (g % 4) meet with two xor-shuffle adds, one store per column
+        if (++s == RING) s = 0, ph ^= 1u;
+        if (cs & 1) {
+            // end of a 128-row block (two stages): hi + lo * 2^-11, then the block's activation scale
 #pragma unroll
-            for (int t = 0; t < MT; t++) {
-                if (t < T) {
-                    float a = tot0[t], b = tot1[t];
-                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
-                    b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 1));
-                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
-                    b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, 2));
-                    if ((lane & 3) == 0) {
-                        float* pp = part + (((size_t)slot * S + sp0 + spi) * T + t) * n + (size_t)(nb0 + warp) * 16 + (lane >> 2);
-                        pp[0] = a;
-                        pp[8] = b;
-                    }
-                    tot0[t] = tot1[t] = 0.0f;
-                }
+            for (int i = 0; i < NM; i++) {
+                const float inv = xil[i][blk];
+                tot0[i] = fmaf(fmaf(acc[i][1], 4.8828125e-4f, acc[i][0]), inv, tot0[i]);
+                tot1[i] = fmaf(fmaf(acc[i][3], 4.8828125e-4f, acc[i][2]), inv, tot1[i]);
+                acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
             }
+            blk++;
+        }
+        if (++cs == nst1) {
+            // end of a split: lane (g, t) stores outputs g and g + 8 of its tile column for activation row t (+ 4)
+#pragma unroll
+            for (int i = 0; i < NM; i++) {
+                const int t = 4 * i + t4;
+                if (t < T) {
+                    float* pp = part + (((size_t)slot * S + sp0 + spi) * T + t) * n + (size_t)(nb0 + warp) * 16 + g;
+                    pp[0] = tot0[i];
+                    pp[8] = tot1[i];
+                }
+                tot0[i] = tot1[i] = 0.0f;
+            }
+            cs = 0;
+            spi++;
         }
     }
 }
@@ -460,20 +481,21 @@ int launch_had_in(const unsigned long long* ptrs, const void* x, uint16_t* xh, f
 int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float* xinv, float* part, const Mul1Spec& s, int slots, int T,
                 size_t plane, cudaStream_t st) {
     const int S = ksplit(s.k), tps = (s.k / 16) / S;
+    if (tps % 8 != 0) CN_FAIL(CN_ERR_SHAPE, "mul1 gemv: k = %d does not split into whole 128-row blocks", s.k);  // the kernel's stage / block counters rely on it
     // k-splits per CTA: as many as still leave about four CTAs per SM (the splits keep separate partial sums, so
     // this only moves work between CTAs) and fit the staged activations
     int spc = 1;
     for (int c = S; c > 1; c--) {
         if (S % c) continue;
         const long long ctas = (long long)(s.n / 128) * (S / c) * slots;
-        const size_t need = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * (c * tps * 16) * 2 + 8 + (size_t)T * (c * tps / 8) * 4;
+        const size_t need = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * (c * tps * 16 + XPAD) * 2 + 8 + (size_t)T * (c * tps / 8) * 4;
         if (ctas >= 592 && need <= 160 * 1024) {
             spc = c;
             break;
         }
     }
     const int rows = spc * tps * 16;
-    const size_t smem = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * rows * 2 + 8 + (size_t)T * (rows / 128) * 4;
+    const size_t smem = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * (rows + XPAD) * 2 + 8 + (size_t)T * (rows / 128) * 4;
     dim3 grid(s.n / 128, S / spc, slots);
     if (smem > 160 * 1024) CN_FAIL(CN_ERR_LIMIT, "mul1 gemv: %zu B of shared memory per block", smem);
     const bool k3 = s.bits == 3 && !s.half;

@@ -44,12 +44,6 @@ constexpr int LUT_OFF = 2304;
 constexpr int RED_OFF = LUT_OFF + 2048;  // [RED_DEPTH][NW][16] f32
 static_assert(ZERO2_OFF + 16 <= LUT_OFF && TBAR_OFF + RED_DEPTH * 8 <= ZERO_OFF, "header regions overlap");
 constexpr int ROWS = 16;
-// not volatile: a pure function of its operands, free to be scheduled between the shared-memory loads
-__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // ---- two-CTA cluster helpers (K range of a tile shared between the CTAs of a pair)
 constexpr int XCH_OFF = 256, XCH_SLOTS = 8, XBAR_OFF = XCH_OFF + XCH_SLOTS * 64;  // f32 [8][16] sums from the peer + a barrier per slot

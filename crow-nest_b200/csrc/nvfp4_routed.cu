@@ -52,11 +52,6 @@ struct RoutedParams {
     uint32_t xs_off, stage_off;
 };
 
-__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // MT: row slots per group (1 or 4); TXB: 36-byte blocks per row and stage; RT: row tiles per stage
 template <int MT, int TXB, int RT>
