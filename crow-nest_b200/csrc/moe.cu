@@ -70,12 +70,12 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int32_t* __rest
     }
 }
 
-// Sort the combos by expert and cut every expert's run into groups of up to four rows (one CTA of 1024 threads):
+// Sort the combos by expert and cut every expert's run into groups of up to gmax rows, gmax 4 or 8 (one CTA of 1024 threads):
 //   order[]           the combos sorted by expert, stable; combos without a resident expert (id outside 0..E-1, or a
 //                     null entry of `tab`) last and in no group
 //   ga[] / counts[0]  positions (in order[]) of the one-row groups: an expert's single row, or the one left over after
-//                     its groups of four
-//   gb[], gbrows[] / counts[1]  first positions and row counts (2..4) of the other groups
+//                     its groups of gmax
+//   gb[], gbrows[] / counts[1]  first positions and row counts (2..gmax) of the other groups
 //   gd[], gdrows[] / counts[2]  the same runs cut into groups of one or two rows (for f32 activations, which take two
 //                     of the kernel's four row slots each: a high and a low f16 plane)
 // Placement is done by one warp walking the combos in order (match.any finds the lanes of a step that share an expert),
@@ -83,7 +83,7 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int32_t* __rest
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restrict__ ids, const unsigned long long* __restrict__ tab, int n, int E,
                                                          int32_t* __restrict__ order, int* __restrict__ ga, int* __restrict__ gb,
                                                          int* __restrict__ gbrows, int* __restrict__ gd, int* __restrict__ gdrows,
-                                                         int* __restrict__ counts) {
+                                                         int* __restrict__ counts, int gmax) {
     extern __shared__ int sm[];  // [E + 1] counts, [E + 1] starts, [E + 1] running, [n] bins
     int* cnt = sm;
     int* start = sm + (E + 1);
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restri
     for (int i = i0; i < i1; i++) {
         const int k = cnt[i];
         rows += k;
-        if (i < E) na += (k & 3) == 1, nb += (k >> 2) + ((k & 3) >= 2), nd += (k + 1) >> 1;
+        if (i < E) na += (k % gmax) == 1, nb += k / gmax + ((k % gmax) >= 2), nd += (k + 1) >> 1;
     }
     int ir = rows, ia = na, ib = nb, id = nd;
 #pragma unroll
@@ -139,8 +139,8 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t* __restri
         start[i] = pr;
         run[i] = pr;
         if (i < E) {
-            for (int q = 0; q < (k >> 2); q++) gb[pb] = pr + 4 * q, gbrows[pb] = 4, pb++;
-            const int rem = k & 3, at = pr + (k & ~3);
+            for (int q = 0; q < k / gmax; q++) gb[pb] = pr + gmax * q, gbrows[pb] = gmax, pb++;
+            const int rem = k % gmax, at = pr + k - rem;
             if (rem == 1) ga[pa++] = at;
             if (rem >= 2) gb[pb] = at, gbrows[pb] = rem, pb++;
             for (int q = 0; q < k; q += 2) gd[pd] = pr + q, gdrows[pd] = k - q >= 2 ? 2 : 1, pd++;
@@ -226,11 +226,12 @@ struct MoePlan {
 
 // the grouping step for other operators of the library (declared in nvfp4_gemv.cuh): lists of `combos` ints each, counts of 3
 int cn_moe_group_launch(const int32_t* ids, const unsigned long long* tab, int combos, int experts, int32_t* order, int* ga, int* gb, int* gbrows,
-                        int* gd, int* gdrows, int* counts, cudaStream_t stream) {
+                        int* gd, int* gdrows, int* counts, int gmax, cudaStream_t stream) {
+    if (gmax != 4 && gmax != 8) CN_FAIL(CN_ERR_SHAPE, "grouping: groups of %d rows (4 or 8)", gmax);
     const size_t smem = (size_t)(3 * (experts + 1) + combos) * sizeof(int);
     if (smem > 160 * 1024) CN_FAIL(CN_ERR_LIMIT, "grouping %d combos over %d experts needs %zu B of shared memory", combos, experts, smem);
     CN_ALLOW_SMEM(moe_group_kernel, 160 * 1024);
-    CN_CUDA(cn_launch_pdl(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, tab, combos, experts, order, ga, gb, gbrows, gd, gdrows, counts));
+    CN_CUDA(cn_launch_pdl(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, tab, combos, experts, order, ga, gb, gbrows, gd, gdrows, counts, gmax));
     return CN_OK;
 }
 
@@ -341,7 +342,7 @@ int routed_experts(MoePlan* p, const unsigned long long* table_gu, const unsigne
             int* gd = gbrows + combos;
             int* gdrows = gd + combos;
             int* counts = gdrows + combos;
-            if (int rc = cn_moe_group_launch(ids, table_gu, combos, p->experts, p->order, ga, gb, gbrows, gd, gdrows, counts, stream)) return rc;
+            if (int rc = cn_moe_group_launch(ids, table_gu, combos, p->experts, p->order, ga, gb, gbrows, gd, gdrows, counts, 4, stream)) return rc;
             RoutedCall a = {};
             a.ids = ids, a.order = p->order, a.tab0 = table_gu, a.tab1 = table_up, a.fused_up_rows = table_up ? 0 : p->inter, a.gs0 = gs_gu;
             a.gs1 = gs_up ? gs_up : gs_gu, a.x = x, a.x_div = x_div, a.x_f32 = dtype == CN_F32, a.y = p->h, a.ldy = p->inter, a.rows = p->inter, a.k = p->hidden;

@@ -27,7 +27,7 @@
 namespace {
 
 constexpr int MUL1_MAXT = CN_MAX_M;  // activation rows per slot
-constexpr int MUL1_GT = 4;           // rows of a group when the MoE step bundles the combos of an expert
+constexpr int MUL1_GT = 8;           // most rows of a group when the MoE step bundles the combos of an expert (groups of 4 or 8)
 constexpr int RING = 4;              // stages of the tile ring
 constexpr int UROWS = 4;             // tile rows per stage
 constexpr int XPAD = 8;              // f16 elements added to the pitch of a staged activation row
@@ -440,7 +440,7 @@ struct Mul1Plan {
     int* groups;               // [5 * slots + 8] the group lists and counts of cn_moe_group_launch
     int* rowsrc;               // [slots * MUL1_GT] x row of every (group slot, row), -1 = unused
     int* rowdst;               // [slots * MUL1_GT] combo (output row) of every (group slot, row), -1 = unused
-    int grp_rows;              // rows the scratch holds per slot: max(max_t, MUL1_GT)
+    int grp_rows;              // rows the scratch holds per slot: max(max_t, 4)
     float* eo;                 // [slots][T][hidden] expert outputs (MoE form)
     // the up projection does not depend on the gate projection: it runs on a side stream between two events
     cudaStream_t side;
@@ -527,11 +527,12 @@ __global__ void mul1_gather_kernel(const unsigned long long* __restrict__ table,
     if (c < n) ptrs[c] = (ids[c] < 0 || (experts > 0 && ids[c] >= experts)) ? 0ull : table[ids[c]];
 }
 
-// Slot s of the grouped MoE form: the groups of two to four rows first, then the one-row groups, then empty slots (null
-// record). Fills the slot's record address and, per row, where its x row comes from and which combo's output row it is.
+// Slot s of the grouped MoE form (gt rows per slot, 4 or 8): the groups of two or more rows first, then the one-row
+// groups, then empty slots (null record). Fills the slot's record address and, per row, where its x row comes from and
+// which combo's output row it is.
 __global__ void mul1_slots_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ ids, const int32_t* __restrict__ order,
                                   const int* __restrict__ ga, const int* __restrict__ gb, const int* __restrict__ gbrows, const int* __restrict__ counts,
-                                  unsigned long long* __restrict__ ptrs, int* __restrict__ rowsrc, int* __restrict__ rowdst, int slots, int x_div) {
+                                  unsigned long long* __restrict__ ptrs, int* __restrict__ rowsrc, int* __restrict__ rowdst, int slots, int x_div, int gt) {
     pdl_launch_dependents();
     pdl_wait();
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
@@ -541,10 +542,10 @@ __global__ void mul1_slots_kernel(const unsigned long long* __restrict__ table, 
     if (s < nb) pos = gb[s], rows = gbrows[s];
     else if (s < nb + na) pos = ga[s - nb], rows = 1;
     ptrs[s] = pos < 0 ? 0ull : table[ids[order[pos]]];
-    for (int t = 0; t < MUL1_GT; t++) {
+    for (int t = 0; t < gt; t++) {
         const int c = t < rows ? order[pos + t] : -1;
-        rowsrc[s * MUL1_GT + t] = c < 0 ? -1 : c / x_div;
-        rowdst[s * MUL1_GT + t] = c;
+        rowsrc[s * gt + t] = c < 0 ? -1 : c / x_div;
+        rowdst[s * gt + t] = c;
     }
 }
 
@@ -560,8 +561,9 @@ extern "C" int cn_mul1_plan_create(void** plan_out, int hidden, int inter, int b
     Mul1Plan* p = new Mul1Plan();
     p->hidden = hidden, p->inter = inter, p->bits = bits, p->half = half, p->n32 = 8 * bits + (half ? 4 : 0), p->max_slots = max_slots, p->max_t = max_t;
     p->kmax = hidden > inter ? hidden : inter;
-    // the grouped MoE form runs every slot with MUL1_GT rows: the scratch is sized for that
-    p->grp_rows = max_t > MUL1_GT ? max_t : MUL1_GT;
+    // the grouped MoE form runs its slots with four or eight rows: the scratch holds four rows per slot, which covers
+    // eight-row groups whenever there are few enough of them (see cn_moe_mul1_experts)
+    p->grp_rows = max_t > 4 ? max_t : 4;
     const size_t rows = (size_t)max_slots * p->grp_rows;
     p->plane = rows * p->kmax;
     // a failure part-way frees what the earlier steps got (the destroy call takes a half-built plan)
@@ -667,21 +669,29 @@ extern "C" int cn_moe_mul1_experts(void* plan, const unsigned long long* table, 
     if (x_div < 1 || !eo) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_experts: x_div %d, eo %p", x_div, (void*)eo);
     if (dtype != CN_F32 && dtype != CN_BF16) CN_FAIL(CN_ERR_SHAPE, "cn_moe_mul1_experts: dtype %d is neither CN_F32 nor CN_BF16", dtype);
     cudaStream_t st = (cudaStream_t)stream;
-    if (experts > 0 && combos >= 16 * experts && p->max_t <= MUL1_GT) {
-        // A long batch (sixteen combo slots per expert or more; measured: with four rows per expert the four-row kernel at two CTAs per
-        // SM is no faster than four one-row slots at four CTAs per SM): the combos are sorted by
-        // expert and bundled into groups of up to four rows that share one decode of the expert's trellis
-        int* ga = p->groups;
-        int* gb = ga + combos;
-        int* gbrows = gb + combos;
-        int* gd = gbrows + combos;
-        int* gdrows = gd + combos;
-        int* counts = gdrows + combos;
-        if (int rc = cn_moe_group_launch(ids, table, combos, experts, p->order, ga, gb, gbrows, gd, gdrows, counts, st)) return rc;
-        CN_CUDA(cn_launch_pdl(mul1_slots_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->order, ga, gb, gbrows, counts, p->ptrs, p->rowsrc,
-                              p->rowdst, combos, x_div));
-        // every slot beyond the groups is a null record, which all kernels skip; a group's unused rows are zero rows
-        return mul1_ffn(p, p->ptrs, x, eo, combos, MUL1_GT, 1, limit, dtype, 1, st, p->rowsrc, p->rowdst);
+    if (experts > 0 && 2 * combos >= experts) {
+        // Enough combos that experts repeat: the combos are sorted by expert and bundled into groups that share one
+        // decode of the expert's trellis (a group of up to four rows is one MMA per tile like a single row, eight rows
+        // are two). Groups of eight when the batch is long (four combo slots per expert or more) and the plan's scratch
+        // holds them; the slots launched are bounded by experts + combos / rows, the rest of the combo slots do not exist.
+        const long long cap_rows = (long long)p->max_slots * p->grp_rows;
+        int gt = 4;
+        if (combos >= 4 * experts && ((long long)experts + combos / 8) * 8 <= cap_rows) gt = 8;
+        long long ng = (long long)experts + combos / gt;  // every expert ends in at most one short group
+        if (ng > combos) ng = combos;
+        if (ng * gt <= cap_rows && ng <= p->max_slots) {
+            int* ga = p->groups;
+            int* gb = ga + combos;
+            int* gbrows = gb + combos;
+            int* gd = gbrows + combos;
+            int* gdrows = gd + combos;
+            int* counts = gdrows + combos;
+            if (int rc = cn_moe_group_launch(ids, table, combos, experts, p->order, ga, gb, gbrows, gd, gdrows, counts, gt, st)) return rc;
+            CN_CUDA(cn_launch_pdl(mul1_slots_kernel, dim3(((int)ng + 127) / 128), dim3(128), 0, st, table, ids, p->order, ga, gb, gbrows, counts, p->ptrs,
+                                  p->rowsrc, p->rowdst, (int)ng, x_div, gt));
+            // a slot beyond the groups is a null record, which all kernels skip; a group's unused rows are zero rows
+            return mul1_ffn(p, p->ptrs, x, eo, (int)ng, gt, 1, limit, dtype, 1, st, p->rowsrc, p->rowdst);
+        }
     }
     CN_CUDA(cn_launch_pdl(mul1_gather_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->ptrs, combos, experts));
     CN_CUDA(cudaGetLastError());

@@ -51,10 +51,11 @@ struct RoutedCall {
 int cn_routed_launch(const RoutedCall& a, cudaStream_t stream, const char* who);
 
 // Sort combos by expert and cut every expert's run into groups (moe.cu): order [combos]; ga = positions (in order) of the
-// one-row groups, counts[0] of them; gb / gbrows = positions and row counts (2..4) of the larger groups, counts[1]; gd /
-// gdrows = the same runs cut into groups of one or two rows, counts[2]. Combos without a resident expert are in no group.
+// one-row groups, counts[0] of them; gb / gbrows = positions and row counts (2..gmax, gmax 4 or 8) of the larger groups,
+// counts[1]; gd / gdrows = the same runs cut into groups of one or two rows, counts[2]. Combos without a resident expert
+// are in no group.
 int cn_moe_group_launch(const int32_t* ids, const unsigned long long* tab, int combos, int experts, int32_t* order, int* ga, int* gb, int* gbrows,
-                        int* gd, int* gdrows, int* counts, cudaStream_t stream);
+                        int* gd, int* gdrows, int* counts, int gmax, cudaStream_t stream);
 
 // Kernel-side parameters shared by the CUDA-core and the tensor-core GEMV kernels.
 struct GemvParams {
