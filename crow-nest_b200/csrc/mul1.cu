@@ -81,7 +81,7 @@ __device__ __forceinline__ void store_hi_lo(uint16_t* xh, size_t plane, size_t a
 }
 
 // xh16[slot][t][k] = the hi / lo planes of H128(x * suh) * mul, xinv[slot][t][k/128] = 1/mul.
-// grid (k/128, T, slots), block 32. XT: 0 f32, 1 bf16 input. x row of slot: x + (slot / x_div) * T * k.
+// grid (k/128, 1, slots), block 32 T (warp t = activation row t). XT: 0 f32, 1 bf16 input. x row of slot: x + (slot / x_div) * T * k.
 // rowsrc (optional): the x row of (slot, t) as an index into x [rows][k], negative = an unused row slot (stored as zeros)
 template <int XT>
 __global__ void mul1_had_in_kernel(const unsigned long long* __restrict__ ptrs, const void* __restrict__ x, uint16_t* __restrict__ xh,
@@ -89,7 +89,7 @@ __global__ void mul1_had_in_kernel(const unsigned long long* __restrict__ ptrs, 
                                    const int* __restrict__ rowsrc) {
     pdl_launch_dependents();
     pdl_wait();  // everything below may read what earlier kernels of the stream wrote
-    const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
+    const int slot = blockIdx.z, t = threadIdx.x >> 5, blk = blockIdx.x, lane = threadIdx.x & 31;  // one warp per activation row
     if (ptrs[slot] == 0ull) return;  // a null record: nothing to read or write
     const uint16_t* suh = (const uint16_t*)(ptrs[slot] + (unsigned long long)suh_off);
     const int src = rowsrc ? rowsrc[slot * T + t] : 0;
@@ -344,14 +344,14 @@ __device__ __forceinline__ void out_block(float v[4], const float* __restrict__ 
     for (int j = 0; j < 4; j++) v[j] = __fmul_rn(__fmul_rn(v[j], 0.0078125f), h2f(svh[c0 + j]));
 }
 
-// grid (n/128, T, slots), block 32. YT: 0 f32, 1 bf16 output; y row = slot * T + t
+// grid (n/128, 1, slots), block 32 T (warp t = activation row t). YT: 0 f32, 1 bf16 output; y row = slot * T + t
 // rowdst (optional): the y row of (slot, t) as an index into y [rows][n], negative = nothing to store
 template <int YT>
 __global__ void mul1_had_out_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part, void* __restrict__ y, int n,
                                     int S, int T, long long svh_off, const int* __restrict__ rowdst) {
     pdl_launch_dependents();
     pdl_wait();  // everything below may read what earlier kernels of the stream wrote
-    const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
+    const int slot = blockIdx.z, t = threadIdx.x >> 5, blk = blockIdx.x, lane = threadIdx.x & 31;  // one warp per activation row
     if (ptrs[slot] == 0ull) return;
     const int dst = rowdst ? rowdst[slot * T + t] : 0;
     if (dst < 0) return;
@@ -368,13 +368,13 @@ __global__ void mul1_had_out_kernel(const unsigned long long* __restrict__ ptrs,
 }
 
 // The middle of the FFN in one launch: had_out of gate and of up, h = act(g, u), had_in of down.
-// grid (inter/128, T, slots), block 32.
+// grid (inter/128, 1, slots), block 32 T (warp t = activation row t).
 __global__ void mul1_act_had_in_kernel(const unsigned long long* __restrict__ ptrs, const float* __restrict__ part_g,
                                        const float* __restrict__ part_u, uint16_t* __restrict__ xh_d, float* __restrict__ xinv_d, int inter, int S,
                                        int T, long long svh_g, long long svh_u, long long suh_d, float limit, size_t plane) {
     pdl_launch_dependents();
     pdl_wait();  // everything below may read what earlier kernels of the stream wrote
-    const int slot = blockIdx.z, t = blockIdx.y, blk = blockIdx.x, lane = threadIdx.x;
+    const int slot = blockIdx.z, t = threadIdx.x >> 5, blk = blockIdx.x, lane = threadIdx.x & 31;  // one warp per activation row
     if (ptrs[slot] == 0ull) return;
     float g[4], u[4], v[4];
     out_block(g, part_g, (const uint16_t*)(ptrs[slot] + (unsigned long long)svh_g), slot, S, T, t, inter, blk, lane);
@@ -469,17 +469,19 @@ Mul1Spec spec_of(const Mul1Plan* p, int which) {
 
 int launch_had_in(const unsigned long long* ptrs, const void* x, uint16_t* xh, float* xinv, const Mul1Spec& s, int slots, int T, int x_div,
                   int dtype, size_t plane, cudaStream_t st, const int* rowsrc = nullptr) {
-    dim3 grid(s.k / 128, T, slots);
+    dim3 grid(s.k / 128, 1, slots);
     if (dtype == CN_BF16)
-        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane, rowsrc));
+        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<1>), dim3(grid), dim3(32 * T), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane, rowsrc));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane, rowsrc));
+        CN_CUDA(cn_launch_pdl((mul1_had_in_kernel<0>), dim3(grid), dim3(32 * T), 0, st, ptrs, x, xh, xinv, s.k, T, s.suh_off, x_div, plane, rowsrc));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
 
+// live: how many of the slots are expected to hold a record (the grouped MoE form launches more slots than it fills)
 int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float* xinv, float* part, const Mul1Spec& s, int slots, int T,
-                size_t plane, cudaStream_t st) {
+                size_t plane, cudaStream_t st, int live = 0) {
+    if (live < 1 || live > slots) live = slots;
     const int S = ksplit(s.k), tps = (s.k / 16) / S;
     if (tps % 8 != 0) CN_FAIL(CN_ERR_SHAPE, "mul1 gemv: k = %d does not split into whole 128-row blocks", s.k);  // the kernel's stage / block counters rely on it
     // k-splits per CTA: as many as still leave about four CTAs per SM (the splits keep separate partial sums, so
@@ -487,7 +489,7 @@ int launch_gemv(const unsigned long long* ptrs, const uint16_t* xh, const float*
     int spc = 1;
     for (int c = S; c > 1; c--) {
         if (S % c) continue;
-        const long long ctas = (long long)(s.n / 128) * (S / c) * slots;
+        const long long ctas = (long long)(s.n / 128) * (S / c) * live;
         const size_t need = 128 + (size_t)RING * UROWS * 32 * s.n32 + (size_t)2 * T * (c * tps * 16 + XPAD) * 2 + 8 + (size_t)T * (c * tps / 8) * 4;
         if (ctas >= 592 && need <= 160 * 1024) {
             spc = c;
@@ -614,38 +616,38 @@ extern "C" int cn_mul1_gemv(void* plan, int which, const unsigned long long* ptr
     const Mul1Spec s = spec_of(p, which);
     if (int rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, s, slots, t, x_div, dtype, p->plane, st)) return rc;
     if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, s, slots, t, p->plane, st)) return rc;
-    dim3 grid(s.n / 128, t, slots);
+    dim3 grid(s.n / 128, 1, slots);
     if (dtype == CN_BF16)
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32 * t), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32 * t), 0, st, ptrs, p->part_a, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
 
 // y[slot][t] = down(act(gate x, up x)) as f32 when out_f32, else in `dtype`
 static int mul1_ffn(Mul1Plan* p, const unsigned long long* ptrs, const void* x, void* y, int slots, int t, int x_div, float limit, int dtype,
-                    int out_f32, cudaStream_t st, const int* rowsrc = nullptr, const int* rowdst = nullptr) {
+                    int out_f32, cudaStream_t st, const int* rowsrc = nullptr, const int* rowdst = nullptr, int live = 0) {
     const Mul1Spec g = spec_of(p, 0), u = spec_of(p, 1), d = spec_of(p, 2);
     // up branch on the side stream; it is joined again on every path, so a capture of `st` stays valid
     CN_CUDA(cudaEventRecord(p->fork, st));
     CN_CUDA(cudaStreamWaitEvent(p->side, p->fork, 0));
     int rc = launch_had_in(ptrs, x, p->xh_b, p->xinv_b, u, slots, t, x_div, dtype, p->plane, p->side, rowsrc);
-    if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, p->plane, p->side);
+    if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_b, p->xinv_b, p->part_b, u, slots, t, p->plane, p->side, live);
     CN_CUDA(cudaEventRecord(p->join, p->side));
     if (rc == CN_OK) rc = launch_had_in(ptrs, x, p->xh_a, p->xinv_a, g, slots, t, x_div, dtype, p->plane, st, rowsrc);
-    if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, p->plane, st);
+    if (rc == CN_OK) rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, g, slots, t, p->plane, st, live);
     CN_CUDA(cudaStreamWaitEvent(st, p->join, 0));
     if (rc != CN_OK) return rc;
-    CN_CUDA(cn_launch_pdl(mul1_act_had_in_kernel, dim3(p->inter / 128, t, slots), dim3(32), 0, st, ptrs, p->part_a, p->part_b, p->xh_a, p->xinv_a, p->inter, ksplit(p->hidden), t,
+    CN_CUDA(cn_launch_pdl(mul1_act_had_in_kernel, dim3(p->inter / 128, 1, slots), dim3(32 * t), 0, st, ptrs, p->part_a, p->part_b, p->xh_a, p->xinv_a, p->inter, ksplit(p->hidden), t,
                                                                          g.svh_off, u.svh_off, d.suh_off, limit, p->plane));
     CN_CUDA(cudaGetLastError());
-    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, d, slots, t, p->plane, st)) return rc;
-    dim3 grid(d.n / 128, t, slots);
+    if (int rc = launch_gemv(ptrs, p->xh_a, p->xinv_a, p->part_a, d, slots, t, p->plane, st, live)) return rc;
+    dim3 grid(d.n / 128, 1, slots);
     if (dtype == CN_BF16 && !out_f32)
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off, rowdst));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32 * t), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off, rowdst));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off, rowdst));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32 * t), 0, st, ptrs, p->part_a, y, d.n, ksplit(d.k), t, d.svh_off, rowdst));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }
@@ -690,7 +692,8 @@ extern "C" int cn_moe_mul1_experts(void* plan, const unsigned long long* table, 
             CN_CUDA(cn_launch_pdl(mul1_slots_kernel, dim3(((int)ng + 127) / 128), dim3(128), 0, st, table, ids, p->order, ga, gb, gbrows, counts, p->ptrs,
                                   p->rowsrc, p->rowdst, (int)ng, x_div, gt));
             // a slot beyond the groups is a null record, which all kernels skip; a group's unused rows are zero rows
-            return mul1_ffn(p, p->ptrs, x, eo, (int)ng, gt, 1, limit, dtype, 1, st, p->rowsrc, p->rowdst);
+            // (the work per CTA is sized as if a quarter of the launched slots were filled: measured best at 45 of 64 and at 8 of 128)
+            return mul1_ffn(p, p->ptrs, x, eo, (int)ng, gt, 1, limit, dtype, 1, st, p->rowsrc, p->rowdst, (int)((ng + 3) / 4));
         }
     }
     CN_CUDA(cn_launch_pdl(mul1_gather_kernel, dim3((combos + 127) / 128), dim3(128), 0, st, table, ids, p->ptrs, combos, experts));
@@ -782,11 +785,11 @@ extern "C" int cn_mul1_gemv_noalloc(int which, int hidden, int inter, int bits, 
     // slots, the GEMV fills every partial that had_out sums), so nothing has to start at zero
     if (int rc = launch_had_in(ptrs, x, xh, xinv, s, slots, t, x_div, dtype, plane, st)) return rc;
     if (int rc = launch_gemv(ptrs, xh, xinv, part, s, slots, t, plane, st)) return rc;
-    dim3 grid(s.n / 128, t, slots);
+    dim3 grid(s.n / 128, 1, slots);
     if (dtype == CN_BF16)
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<1>), dim3(grid), dim3(32 * t), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     else
-        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
+        CN_CUDA(cn_launch_pdl((mul1_had_out_kernel<0>), dim3(grid), dim3(32 * t), 0, st, ptrs, part, y, s.n, ksplit(s.k), t, s.svh_off, (const int*)nullptr));
     CN_CUDA(cudaGetLastError());
     return CN_OK;
 }

@@ -86,6 +86,9 @@ struct GemvParams {
     const unsigned long long* yptrs;  // output row address per combo (null: y + combo * ldy)
     int red_depth;  // multi-row tensor-core kernel: tile-sum slots in flight
     int ksplit;     // 2: launched as two-CTA clusters, each CTA of a pair over half of K (one activation row only)
+#ifdef CN_M1_TRACE
+    unsigned long long* trace;  // [8] globaltimer stamps per CTA of this launch (diagnostic build only), or null
+#endif
 };
 
 __device__ __forceinline__ float act_gu(float g, float u, float limit) {

@@ -78,12 +78,27 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     }
 }
 
+// Diagnostic build (-DCN_M1_TRACE): every CTA stamps %globaltimer at entry (0), after the wait on the predecessor grid (1),
+// after the activations are staged (2), when its first stage has landed (3), at the end of its consumers (4), and its
+// producer warp at its first (5) and after its last (6) bulk copy. Off in the product build.
+#ifdef CN_M1_TRACE
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define CN_STAMP(i) if (p.trace) p.trace[(size_t)blockIdx.x * 8 + (i)] = gtime()
+#else
+#define CN_STAMP(i)
+#endif
+
 // TX: 36-byte blocks per row and stage (32 or 16); the last chunk of a row may be shorter
 // CPS: CTAs per SM the register allocation must allow; MT: activation rows (1, 2, 4 or 8; p.m of them live)
 // KS: 1, or 2 = launched as two-CTA clusters, the CTAs of a pair sharing every tile's K range (MT = 1 only)
 template <int TX, int CPS, int MT, int KS = 1>
 __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    if (threadIdx.x == 0) { CN_STAMP(0); }
     const float gs0_early = __ldg(p.gs0), gs1_early = __ldg(p.gs1);  // tensor scales: asked for first, used late
     constexpr int pstride = TX * 36 + 16;  // padded: the eight rows of a quad column hit distinct banks
     constexpr int stage_bytes = ROWS * pstride;
@@ -180,6 +195,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 }
                 __syncwarp();
                 if (src) bulk_g2s_stream(st + (size_t)lane * pstride, src + (size_t)c * TX * 36, piece, &full[s], pol);
+                if (lane == 0 && first_round && s == 0) { CN_STAMP(5); }
                 if (++s == S) {
                     s = 0;
                     par ^= 1u;
@@ -187,6 +203,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 }
             }
         }
+        if (lane == 0) { CN_STAMP(6); }
         if (KS == 2) cluster_sync_all();  // nobody leaves while the peer may still send or receive
         return;
     }
@@ -196,6 +213,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     // fly; each later load is issued before the previous chunk is converted.
     pdl_launch_dependents();
     pdl_wait();  // the activations may come from the previous kernel of the stream
+    if (threadIdx.x == 0) { CN_STAMP(1); }
     const int ntask = MT * bpr * 8;
     auto load_x = [&](int task) -> uint4 {
         // task = (row * bpr + block) * 8 + chunk; rows beyond p.m read as zero
@@ -256,6 +274,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
       }
     }
     asm volatile("bar.sync 2, %0;" ::"n"(NTHREADS) : "memory");  // staging done, and the ring's barriers are initialised
+    if (threadIdx.x == 0) { CN_STAMP(2); }
 
     // ---------------------------------------------------------------- main loop
     const int g = lane >> 2, t = lane & 3;
@@ -307,6 +326,9 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 ok = false;
                 break;
             }
+#ifdef CN_M1_TRACE
+            if (threadIdx.x == 0 && titer == 0 && c == 0) { CN_STAMP(3); }
+#endif
             const uint8_t* pa0 = stage0 + (size_t)s * stage_bytes + aoff;
             const uint32_t xoff = xoff_lane + (uint32_t)(c * TX * XB);
             if constexpr (MT == 1) {
@@ -478,6 +500,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             rpar ^= 1u;
         }
     }
+    if (threadIdx.x == 0) { CN_STAMP(4); }
     if (KS == 2) cluster_sync_all();  // nobody leaves while the peer may still send or receive
 }
 
@@ -489,6 +512,13 @@ int launch_m1(const cudaLaunchConfig_t& cfg, const GemvParams& p) {
 }
 
 }  // namespace
+
+#ifdef CN_M1_TRACE
+// diagnostic build: launch i after the call (i = 0, 1, ...) stamps into buf + i * 512 * 8 words; `launches` of them
+static unsigned long long* g_m1_trace = nullptr;
+static int g_m1_trace_n = 0, g_m1_trace_i = 0;
+extern "C" void cn_m1_trace(unsigned long long* buf, int launches) { g_m1_trace = buf, g_m1_trace_n = launches, g_m1_trace_i = 0; }
+#endif
 
 int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     const int rows = a.rows, k = a.k, m = a.m;
@@ -581,6 +611,9 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.red_depth = red_depth;
     p.ksplit = ksplit;
     p.experts = a.experts, p.yptrs = a.yptrs;
+#ifdef CN_M1_TRACE
+    p.trace = (g_m1_trace && g_m1_trace_i < g_m1_trace_n && !routed) ? g_m1_trace + (size_t)(g_m1_trace_i++) * 512 * 8 : nullptr;
+#endif
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid, (unsigned)(routed ? a.combos : 1));
     cfg.blockDim = dim3(NTHREADS);
