@@ -461,6 +461,64 @@ def gemv_arm(args, rank, world, local):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------- interval table
+def intervals_arm(args):
+    """`--workload intervals`: where the time of a projection goes inside the dense stack. Needs the diagnostic build of the
+    library (`make -C crow-nest_b200/csrc trace`), whose one-row GEMV kernel stamps %globaltimer per CTA at entry, after the
+    wait on the predecessor grid, after the activations are staged, when its first stage has landed, at its end, and in the
+    producer warp at its first and after its last bulk copy. Prints a markdown table (ns after the previous launch's last
+    CTA ended; medians over the CTAs of a launch, mean over the last layers) and one JSON line with the same figures."""
+    import numpy as np
+    import torch
+    from crownest_b200 import _lib
+    _lib.use_trace_library()
+    from crownest_b200 import dense
+    layers = max(3, min(args.layers, 8))
+    st = dense.DenseStack(layers=layers, seed=0)
+    st.x.copy_(torch.randn((1, st.hidden), device="cuda").to(torch.bfloat16))
+    n = 4 * layers
+    tr = torch.zeros((n, 512, 8), dtype=torch.int64, device="cuda")
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            st.run_layers(1)
+        s.synchronize()
+        _lib.lib().cn_m1_trace(tr.data_ptr(), n)  # the launches captured next keep their slot of the buffer in the graph
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            st.run_layers(1)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    tr.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    t = tr.cpu().numpy().astype(np.float64)
+    names = ["qkv 7168x5120", "o 5120x5120", "gate/up 2x17408x5120", "down 5120x17408"]
+    cols = ["ctas", "entry", "predecessor_wait_over", "activations_staged", "first_stage_landed", "first_cta_ends", "median_cta_ends", "last_cta_ends",
+            "first_bulk_copy", "last_bulk_copy_median", "last_bulk_copy_max"]
+    rows = {nm: [] for nm in names}
+    prev_end = None
+    for i in range(n):
+        a = t[i][t[i][:, 0] > 0]
+        end = a[:, 4].max()
+        if prev_end is not None and i >= 8:
+            pr = a[a[:, 5] > 0]
+            rel = lambda c: float(np.median(a[:, c] - prev_end))
+            rows[names[i % 4]].append([len(a), rel(0), rel(1), rel(2), rel(3), a[:, 4].min() - prev_end, rel(4), end - prev_end,
+                                       float(np.median(pr[:, 5] - prev_end)), float(np.median(pr[:, 6] - prev_end)), float(np.max(pr[:, 6] - prev_end))])
+        prev_end = end
+    print("| projection | " + " | ".join(cols) + " |")
+    print("|---|" + "---|" * len(cols))
+    out = {}
+    for nm in names:
+        v = np.mean(np.array(rows[nm]), axis=0)
+        out[nm] = {c: float(x) for c, x in zip(cols, v)}
+        print(f"| {nm} | " + " | ".join(f"{x:.0f}" for x in v) + " |")
+    print(json.dumps({"metric": "m1_gemv_intervals_ns", "layers": layers, "unit": "ns after the previous launch's last CTA ended", "intervals": out,
+                      "device_status": _lib.device_status()}), flush=True)
+
+
 # ---------------------------------------------------------------------------------------------- batched GEMM
 def gemm_arm(args, rank, world, local):
     """`--workload gemm`: the batched NVFP4 GEMM (W [17408 x 5120] then [5120 x 17408], --m rows), output columns split over
@@ -623,7 +681,7 @@ def main():
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
     ap.add_argument("--fuse", default="none", choices=["none", "gemv", "layer", "token"],
                     help="dense, one GPU, M = 1: projections through the balanced-share kernel, one launch per projection / layer / token")
-    ap.add_argument("--workload", default="dense", choices=["dense", "gemv", "moe", "mul1", "gemm"],
+    ap.add_argument("--workload", default="dense", choices=["dense", "gemv", "moe", "mul1", "gemm", "intervals"],
                     help="dense = the headline (layer stack); gemv = one matrix (default 4096 x 4096); moe / mul1 = routed experts; gemm = batched rows")
     ap.add_argument("--tokens", type=int, default=8, help="moe / mul1: token rows per rank")
     ap.add_argument("--engine", default="auto", choices=["auto", "fp4", "f16"], help="gemm: block-scaled FP4 MMA, f16 MMA on widened weights, or by row count")
@@ -637,6 +695,8 @@ def main():
     if args.impl == "reference":
         return reference_arm(args, rank)
     args.warmup = max(args.warmup, 3)
+    if args.workload == "intervals":
+        return intervals_arm(args)
     if args.workload == "gemm":
         return gemm_arm(args, rank, world, local)
     if args.workload == "gemv":

@@ -107,6 +107,19 @@ def register(name, argtypes, restype=C.c_int):
         _RESTYPES[name] = restype
 
 
+def use_trace_library():
+    """Load the diagnostic build instead (``make -C crow-nest_b200/csrc trace``): the same entry points plus
+    ``cn_m1_trace(buf, launches)``, after which the next `launches` one-row GEMV launches write eight %globaltimer stamps
+    per CTA into buf [launches][512][8] (u64). Must be called before the first call into the library."""
+    global SO_PATH
+    if _lib is not None:
+        raise CrownestError("the library is already loaded")
+    SO_PATH = os.path.join(_HERE, "libcrownest_b200_trace.so")
+    if not os.path.exists(SO_PATH):
+        raise CrownestError(f"{SO_PATH} is missing: run `make -C {CSRC} trace`")
+    register("cn_m1_trace", [C.c_void_p, C.c_int], None)
+
+
 def lib():
     global _lib
     if _lib is None:

@@ -152,16 +152,17 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     // The producer warp sets up the ring's barriers itself and starts streaming at once (the weights do not
     // depend on the previous kernel); the consumers meet it on named barrier 2 before their first wait.
     if (warp == NW) {
-        if (lane == 0) {
-            for (int s = 0; s < S; s++) {
-                mbar_init(&full[s], 1);
-                mbar_init(&empty[s], NW);
-            }
-            for (int i = 0; i < RD; i++) mbar_init(&tbar[i], NW);
-            if (KS == 2)
-                for (int i = 0; i < XCH_SLOTS; i++) mbar_init((uint64_t*)(smem + XBAR_OFF) + i, 1);
-            mbar_fence_init();
+        // one barrier per lane and round: S full + S empty + RD tile-sum (+ the pair's exchange slots), side by side
+        for (int i = lane; i < 2 * S + RD + (KS == 2 ? XCH_SLOTS : 0); i += 32) {
+            if (i < S) mbar_init(&full[i], 1);
+            else if (i < 2 * S) mbar_init(&empty[i - S], NW);
+            else if (i < 2 * S + RD) mbar_init(&tbar[i - 2 * S], NW);
+            else mbar_init((uint64_t*)(smem + XBAR_OFF) + (i - 2 * S - RD), 1);
         }
+#ifdef CN_M1_TRACE
+        if (lane == 0) { CN_STAMP(7); }
+#endif
+        mbar_fence_init();
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
         pdl_launch_dependents();
