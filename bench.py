@@ -462,42 +462,61 @@ def gemv_arm(args, rank, world, local):
 
 
 # ---------------------------------------------------------------------------------------------- interval table
-def intervals_arm(args):
+def intervals_arm(args, rank=0, world=1, local=0):
     """`--workload intervals`: where the time of a projection goes inside the dense stack. Needs the diagnostic build of the
     library (`make -C crow-nest_b200/csrc trace`), whose one-row GEMV kernel stamps %globaltimer per CTA at entry, after the
     wait on the predecessor grid, after the activations are staged, when its first stage has landed, at its end, and in the
-    producer warp at its first and after its last bulk copy. Prints a markdown table (ns after the previous launch's last
-    CTA ended; medians over the CTAs of a launch, mean over the last layers) and one JSON line with the same figures."""
+    producer warp at its first and after its last bulk copy; under torchrun the exchange kernel of the tensor-parallel stack
+    stamps its own steps too. Prints markdown tables (ns after the previous launch's last CTA ended; medians over the CTAs
+    of a launch, mean over the last layers) and one JSON line with the same figures."""
     import numpy as np
     import torch
+    import torch.distributed as dist
     from crownest_b200 import _lib
     _lib.use_trace_library()
     from crownest_b200 import dense
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = dist.group.WORLD
     layers = max(3, min(args.layers, 8))
-    st = dense.DenseStack(layers=layers, seed=0)
-    st.x.copy_(torch.randn((1, st.hidden), device="cuda").to(torch.bfloat16))
+    st = dense.DenseStack(layers=layers, seed=0, device=f"cuda:{local}", rank=rank, world=world, group=group, exchange="peer")
+    if world > 1 and st.peer is None:
+        raise SystemExit("intervals: the peer-memory exchange is not available between these GPUs")
+    st.x.copy_(torch.randn((1, st.hidden), device=f"cuda:{local}").to(torch.bfloat16))
     n = 4 * layers
-    tr = torch.zeros((n, 512, 8), dtype=torch.int64, device="cuda")
+    tr = torch.zeros((n, 512, 8), dtype=torch.int64, device=f"cuda:{local}")
+    tx = torch.zeros((n, 8), dtype=torch.int64, device=f"cuda:{local}")
     s = torch.cuda.Stream()
     with torch.cuda.stream(s):
         for _ in range(3):
             st.run_layers(1)
         s.synchronize()
-        _lib.lib().cn_m1_trace(tr.data_ptr(), n)  # the launches captured next keep their slot of the buffer in the graph
+        # the launches captured next keep their slot of the buffers in the graph
+        _lib.lib().cn_m1_trace(tr.data_ptr(), n)
+        _lib.lib().cn_tp_trace(tx.data_ptr(), n)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             st.run_layers(1)
     for _ in range(3):
         g.replay()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     tr.zero_()
+    tx.zero_()
     g.replay()
     torch.cuda.synchronize()
     t = tr.cpu().numpy().astype(np.float64)
-    names = ["qkv 7168x5120", "o 5120x5120", "gate/up 2x17408x5120", "down 5120x17408"]
+    x = tx.cpu().numpy().astype(np.float64)
+    shapes = [("qkv", 7168, 5120), ("o", 5120, 5120), ("gate/up", 2 * 17408, 5120), ("down", 5120, 17408)]
+    names = [f"{nm} {r // world}x{k}" for nm, r, k in shapes]
     cols = ["ctas", "entry", "predecessor_wait_over", "activations_staged", "first_stage_landed", "first_cta_ends", "median_cta_ends", "last_cta_ends",
             "first_bulk_copy", "last_bulk_copy_median", "last_bulk_copy_max"]
+    xcols = ["entry", "predecessor_wait_over", "slice_stores_issued", "flag_stored", "peer_flag_seen", "all_flags_seen", "next_gemv_wait_over"]
     rows = {nm: [] for nm in names}
+    xrows = {nm: [] for nm in names}
     prev_end = None
     for i in range(n):
         a = t[i][t[i][:, 0] > 0]
@@ -507,16 +526,32 @@ def intervals_arm(args):
             rel = lambda c: float(np.median(a[:, c] - prev_end))
             rows[names[i % 4]].append([len(a), rel(0), rel(1), rel(2), rel(3), a[:, 4].min() - prev_end, rel(4), end - prev_end,
                                        float(np.median(pr[:, 5] - prev_end)), float(np.median(pr[:, 6] - prev_end)), float(np.max(pr[:, 6] - prev_end))])
-        prev_end = end
-    print("| projection | " + " | ".join(cols) + " |")
-    print("|---|" + "---|" * len(cols))
-    out = {}
-    for nm in names:
-        v = np.mean(np.array(rows[nm]), axis=0)
-        out[nm] = {c: float(x) for c, x in zip(cols, v)}
-        print(f"| {nm} | " + " | ".join(f"{x:.0f}" for x in v) + " |")
-    print(json.dumps({"metric": "m1_gemv_intervals_ns", "layers": layers, "unit": "ns after the previous launch's last CTA ended", "intervals": out,
-                      "device_status": _lib.device_status()}), flush=True)
+        if world > 1 and i >= 8 and i + 1 < n:
+            # the exchange that follows launch i, against the end of launch i's last CTA; then the next launch's wait
+            nxt = t[i + 1][t[i + 1][:, 0] > 0]
+            xrows[names[i % 4]].append([x[i][c] - end for c in range(6)] + [float(np.median(nxt[:, 1])) - end])
+        prev_end = end if world == 1 else (x[i][5] if x[i][5] > 0 else end)
+    out = {"gemv": {}, "exchange": {}}
+    if rank == 0:
+        print("| projection | " + " | ".join(cols) + " |")
+        print("|---|" + "---|" * len(cols))
+        for nm in names:
+            v = np.mean(np.array(rows[nm]), axis=0)
+            out["gemv"][nm] = {c: float(q) for c, q in zip(cols, v)}
+            print(f"| {nm} | " + " | ".join(f"{q:.0f}" for q in v) + " |")
+        if world > 1:
+            print()
+            print("| exchange after | " + " | ".join(xcols) + " |")
+            print("|---|" + "---|" * len(xcols))
+            for nm in names:
+                v = np.mean(np.array(xrows[nm]), axis=0)
+                out["exchange"][nm] = {c: float(q) for c, q in zip(xcols, v)}
+                print(f"| {nm} | " + " | ".join(f"{q:.0f}" for q in v) + " |")
+        print(json.dumps({"metric": "m1_gemv_intervals_ns", "n_gpus": world, "layers": layers,
+                          "unit": "ns after the previous launch's last CTA ended (N > 1: after the previous exchange ended; exchange table: after the GEMV's last CTA ended)",
+                          "intervals": out, "device_status": _lib.device_status()}), flush=True)
+    if world > 1:
+        leave(world, st)
 
 
 # ---------------------------------------------------------------------------------------------- batched GEMM
@@ -696,7 +731,7 @@ def main():
         return reference_arm(args, rank)
     args.warmup = max(args.warmup, 3)
     if args.workload == "intervals":
-        return intervals_arm(args)
+        return intervals_arm(args, rank, world, local)
     if args.workload == "gemm":
         return gemm_arm(args, rank, world, local)
     if args.workload == "gemv":

@@ -118,6 +118,7 @@ def use_trace_library():
     if not os.path.exists(SO_PATH):
         raise CrownestError(f"{SO_PATH} is missing: run `make -C {CSRC} trace`")
     register("cn_m1_trace", [C.c_void_p, C.c_int], None)
+    register("cn_tp_trace", [C.c_void_p, C.c_int], None)  # the same for the tensor-parallel exchange kernel: buf [launches][8]
 
 
 def lib():

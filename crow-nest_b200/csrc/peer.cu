@@ -42,9 +42,25 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 // world 8: two warps for each of the seven): a group stores this rank's slice into its peer's buffer, makes it visible
 // system-wide, meets on its own named barrier, and its first thread publishes the sequence number right behind the data and
 // waits for that peer's slice of the same exchange. The peers are served side by side.
+// Diagnostic build (-DCN_M1_TRACE): thread 0 (which serves the first peer) stamps %globaltimer at entry (0), after the wait on
+// the predecessor grid (1), after its stores are issued (2), after its flag store (3), when its peer's flag
+// has arrived (4) and when every group has seen its peer's (5).
+#ifdef CN_M1_TRACE
+#define CN_TP_STAMP(i) if (threadIdx.x == 0 && trace) trace[i] = tp_gtime()
+__device__ __forceinline__ unsigned long long tp_gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#else
+#define CN_TP_STAMP(i)
+#endif
+
 __global__ void __launch_bounds__(512) tp_allgather_kernel(PeerPtrs peers, int rank, int world, size_t data_off, size_t slice_bytes,
-                                                           size_t flag_off) {
+                                                           size_t flag_off, unsigned long long* trace) {
+    CN_TP_STAMP(0);
     pdl_wait();  // the slice comes from the kernel before this one
+    CN_TP_STAMP(1);
     unsigned char* mine = peers.base[rank];
     unsigned int* my_flags = (unsigned int*)(mine + flag_off);
     const unsigned int seq = my_flags[MAX_WORLD] + 1u;  // read by everybody before anybody can advance it (barrier below)
@@ -56,10 +72,14 @@ __global__ void __launch_bounds__(512) tp_allgather_kernel(PeerPtrs peers, int r
         uint4* dst = (uint4*)(peers.base[p] + data_off + (size_t)rank * slice_bytes);
         const size_t n16 = slice_bytes >> 4;
         for (size_t i = gt; i < n16; i += gsz) dst[i] = src[i];
-        __threadfence_system();
+        CN_TP_STAMP(2);
+        // The group's stores are ordered before its first thread's release by the barrier, and a release at system scope
+        // is cumulative: the peer that acquires the flag sees the whole slice. One fence (inside the release) instead of one
+        // per thread and another behind it.
         asm volatile("bar.sync %0, %1;" ::"r"(gi + 1), "r"(gsz) : "memory");
         if (gt == 0) {
             st_release_sys((unsigned int*)(peers.base[p] + flag_off) + rank, seq);
+            CN_TP_STAMP(3);
             const long long t0 = clock64();
             while ((int)(ld_acquire_sys(my_flags + p) - seq) < 0) {
                 if (clock64() - t0 > 2000000000LL) {
@@ -67,9 +87,11 @@ __global__ void __launch_bounds__(512) tp_allgather_kernel(PeerPtrs peers, int r
                     break;
                 }
             }
+            CN_TP_STAMP(4);
         }
     }
     __syncthreads();
+    CN_TP_STAMP(5);
     if (threadIdx.x == 0) my_flags[MAX_WORLD] = seq;
     pdl_launch_dependents();
 }
@@ -115,6 +137,13 @@ extern "C" int cn_peer_close(void* ptr, size_t offset) {
     return CN_OK;
 }
 
+#ifdef CN_M1_TRACE
+// diagnostic build: exchange i after the call (i = 0, 1, ...) stamps into buf + 8 i words; `launches` of them
+static unsigned long long* g_tp_trace = nullptr;
+static int g_tp_trace_n = 0, g_tp_trace_i = 0;
+extern "C" void cn_tp_trace(unsigned long long* buf, int launches) { g_tp_trace = buf, g_tp_trace_n = launches, g_tp_trace_i = 0; }
+#endif
+
 extern "C" int cn_tp_allgather(const void* const* peer_bases, int rank, int world, size_t data_off, size_t slice_bytes, size_t flag_off,
                                cn_stream_t stream) {
     if (world < 2 || world > MAX_WORLD || rank < 0 || rank >= world) CN_FAIL(CN_ERR_SHAPE, "cn_tp_allgather: rank %d of %d", rank, world);
@@ -131,6 +160,10 @@ extern "C" int cn_tp_allgather(const void* const* peer_bases, int rank, int worl
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at, cfg.numAttrs = 1;
-    CN_CUDA(cudaLaunchKernelEx(&cfg, tp_allgather_kernel, pp, rank, world, data_off, slice_bytes, flag_off));
+    unsigned long long* trace = nullptr;
+#ifdef CN_M1_TRACE
+    if (g_tp_trace && g_tp_trace_i < g_tp_trace_n) trace = g_tp_trace + (size_t)(g_tp_trace_i++) * 8;
+#endif
+    CN_CUDA(cudaLaunchKernelEx(&cfg, tp_allgather_kernel, pp, rank, world, data_off, slice_bytes, flag_off, trace));
     return CN_OK;
 }
