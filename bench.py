@@ -712,7 +712,9 @@ def main():
     ap.add_argument("--min-time", type=float, default=MIN_TIMED_S,
                     help="seconds of device time the timed blocks cover (0 = one block: for a profiler capture of a few launches)")
     ap.add_argument("--no-moe", action="store_true", help="dense workload: leave the MoE block out of the line")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="tensor parallel: slices pushed over peer memory, or NCCL all-gather")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer-lines", "peer-flags", "nccl"],
+                    help="tensor parallel: output rows stored by the GEMV itself as 16-byte lines that carry a sequence number into the peers' memory (peer), "
+                         "the same lines pushed by a separate kernel (peer-lines), data followed by a flag (peer-flags), or NCCL all-gather")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
     ap.add_argument("--fuse", default="none", choices=["none", "gemv", "layer", "token"],
                     help="dense, one GPU, M = 1: projections through the balanced-share kernel, one launch per projection / layer / token")

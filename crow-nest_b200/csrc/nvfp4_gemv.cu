@@ -508,6 +508,7 @@ int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     if (routed && (m != 1 || a.combos < 1 || a.x_div < 1)) CN_FAIL(CN_ERR_SHAPE, "%s: the routed form takes one row per combo", who);
     // bf16 activations: the tensor-core kernel
     if (a.dtype == CN_BF16) return cn_gemv_m1_launch(a, stream, who);
+    if (a.line_bases) CN_FAIL(CN_ERR_SHAPE, "%s: line output takes bf16 activations", who);
     const bool gu = a.w1 != nullptr || a.tab1 != nullptr || a.fused_up_rows > 0;
     const int bpr = k / 64;
     const int tx = bpr % 16 == 0 ? 16 : (bpr % 8 == 0 ? 8 : 4);
@@ -575,6 +576,27 @@ extern "C" int cn_nvfp4_gemv_gu(const void* wg, const void* wu, const float* gs_
     a.w0 = wg, a.w1 = wu, a.gs0 = gs_g, a.gs1 = gs_u, a.x = x, a.y = h, a.rows = inter, a.k = k, a.m = m, a.ldy = ldh, a.limit = limit,
     a.dtype = dtype;
     return cn_gemv_launch(a, (cudaStream_t)stream, "cn_nvfp4_gemv_gu");
+}
+
+extern "C" int cn_nvfp4_gemv_lines(const void* w, const float* gs, const void* x, void* y, int rows, int k, const unsigned long long* line_bases,
+                                   int world, int row0, size_t line_stride, const unsigned int* line_seq, cn_stream_t stream) {
+    if (!line_bases || !line_seq) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_lines: null line buffers or counter");
+    GemvCall a = {};
+    a.w0 = w, a.gs0 = gs, a.x = x, a.y = y, a.rows = rows, a.k = k, a.m = 1, a.ldy = rows, a.dtype = CN_BF16;
+    a.line_bases = line_bases, a.line_world = world, a.line_row0 = row0, a.line_stride = line_stride, a.line_seq = line_seq;
+    return cn_gemv_launch(a, (cudaStream_t)stream, "cn_nvfp4_gemv_lines");
+}
+
+extern "C" int cn_nvfp4_gemv_gu_lines(const void* wg, const void* wu, const float* gs_g, const float* gs_u, const void* x, void* h, int inter, int k,
+                                      float limit, const unsigned long long* line_bases, int world, int row0, size_t line_stride,
+                                      const unsigned int* line_seq, cn_stream_t stream) {
+    if (!wu) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_gu_lines: the up matrix is null");
+    if (!line_bases || !line_seq) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_gu_lines: null line buffers or counter");
+    GemvCall a = {};
+    a.w0 = wg, a.w1 = wu, a.gs0 = gs_g, a.gs1 = gs_u, a.x = x, a.y = h, a.rows = inter, a.k = k, a.m = 1, a.ldy = inter, a.limit = limit,
+    a.dtype = CN_BF16;
+    a.line_bases = line_bases, a.line_world = world, a.line_row0 = row0, a.line_stride = line_stride, a.line_seq = line_seq;
+    return cn_gemv_launch(a, (cudaStream_t)stream, "cn_nvfp4_gemv_gu_lines");
 }
 
 extern "C" int cn_nvfp4_dequant(const void* w, const float* gs, float* out, int rows, int k, int rule, cn_stream_t stream) {

@@ -23,6 +23,13 @@ struct GemvCall {
     int fused_up_rows, x_div, combos;
     int experts;  // entries of the tables (0 = unknown: ids are trusted); an id beyond them skips the combo
     const unsigned long long* yptrs;  // routed form: output row address per combo (null: y + combo * ldy); may name peer memory
+    // Tensor-parallel line output (one bf16 activation row, plain or gate/up form): besides y, the output rows go out as
+    // 16-byte lines {two rows, number, two rows, number} to the line buffers of the other ranks, where number = *line_seq + 1
+    // and the buffer used is number & 1. line_bases: host array [line_world] of device addresses (0 = this rank).
+    const unsigned long long* line_bases;
+    int line_world, line_row0;       // ranks; global index of output row 0 (a multiple of 4)
+    size_t line_stride;              // bytes between the two line buffers of a rank
+    const unsigned int* line_seq;    // this rank's exchange counter of the vector (advanced by cn_tp_recv_lines)
 };
 
 int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who);
@@ -86,6 +93,11 @@ struct GemvParams {
     const unsigned long long* yptrs;  // output row address per combo (null: y + combo * ldy)
     int red_depth;  // multi-row tensor-core kernel: tile-sum slots in flight
     int ksplit;     // 2: launched as two-CTA clusters, each CTA of a pair over half of K (one activation row only)
+    // tensor-parallel line output (see GemvCall): line buffer of every rank (0 = none), first global row, the counter
+    unsigned long long yl[8];
+    int yl_world, yl_row0;
+    unsigned long long yl_stride;
+    const unsigned int* yl_seq;
 #ifdef CN_M1_TRACE
     unsigned long long* trace;  // [8] globaltimer stamps per CTA of this launch (diagnostic build only), or null
 #endif

@@ -92,6 +92,21 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define CN_STAMP(i)
 #endif
 
+// Tensor-parallel line output, called by all lanes of warp 0: lane l < 16 holds output row row0 + l as r. Four rows make one
+// 16-byte line {rows 0-1, number, rows 2-3, number}; lane (d, j) = (lane >> 2, lane & 3) stores line j of the tile into
+// rank d's line buffer. Plain stores: the receiver polls the numbers, nothing waits for an acknowledgement here.
+__device__ __forceinline__ void push_lines(const GemvParams& p, int row0, int nrows, float r, int lane, unsigned int seq) {
+    const uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r));
+    const uint32_t pair = b | (__shfl_down_sync(0xffffffffu, b, 1) << 16);  // even lanes: rows l, l + 1
+    const uint32_t next = __shfl_down_sync(0xffffffffu, pair, 2);           // lanes 4 j: rows 4 j + 2, 4 j + 3
+    const int j = lane & 3, d = lane >> 2;
+    const uint32_t a0 = __shfl_sync(0xffffffffu, pair, 4 * j), a1 = __shfl_sync(0xffffffffu, next, 4 * j);
+    if (d < p.yl_world && p.yl[d] != 0ull && 4 * j < nrows) {
+        uint4* dst = (uint4*)(uintptr_t)(p.yl[d] + (unsigned long long)(seq & 1u) * p.yl_stride) + ((p.yl_row0 + row0) >> 2) + j;
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(a0), "r"(seq), "r"(a1), "r"(seq) : "memory");
+    }
+}
+
 // TX: 36-byte blocks per row and stage (32 or 16); the last chunk of a row may be shorter
 // CPS: CTAs per SM the register allocation must allow; MT: activation rows (1, 2, 4 or 8; p.m of them live)
 // KS: 1, or 2 = launched as two-CTA clusters, the CTAs of a pair sharing every tile's K range (MT = 1 only)
@@ -215,6 +230,8 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     pdl_launch_dependents();
     pdl_wait();  // the activations may come from the previous kernel of the stream
     if (threadIdx.x == 0) { CN_STAMP(1); }
+    // the number of this exchange (tensor-parallel line output): the counter was last advanced a layer ago
+    const unsigned int line_seq = (MT == 1 && p.yl_world > 0) ? *(volatile const unsigned int*)p.yl_seq + 1u : 0u;
     const int ntask = MT * bpr * 8;
     auto load_x = [&](int task) -> uint4 {
         // task = (row * bpr + block) * 8 + chunk; rows beyond p.m read as zero
@@ -468,15 +485,30 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                         if (lane < 16) v += xch[lane];  // first half of K + second half: a fixed order
                         const float up = __shfl_down_sync(0xffffffffu, v, 8);
                         const int row = tile * per_cta + lane;
+                        const float r = gu ? act_gu(v, up, p.limit) : v;
                         if (lane < per_cta && row < p.rows) {
-                            const float r = gu ? act_gu(v, up, p.limit) : v;
                             if (p.out_f32)
                                 ((float*)ybase)[row] = r;
                             else
                                 ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(r);
                         }
+                        if (p.yl_world > 0) push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), r, lane, line_seq);
                     }
                 }
+            } else if (MT == 1 && p.yl_world > 0) {
+                // one activation row with line output: every lane of the warp takes part in the shuffles
+                const int row = tile * per_cta + lane;
+                float v0 = 0.0f, v1 = 0.0f;
+                if (lane < per_cta) {
+                    v0 = rb[lane], v1 = gu ? rb[lane + 8] : 0.0f;
+                    for (int w = 1; w < NW; w++) {  // warps in order: deterministic
+                        v0 += rb[w * 16 + lane];
+                        if (gu) v1 += rb[w * 16 + lane + 8];
+                    }
+                }
+                const float v = gu ? act_gu(v0, v1, p.limit) : v0;
+                if (lane < per_cta && row < p.rows) ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(v);
+                push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), v, lane, line_seq);
             } else if (lane < per_cta) {
                 const int row = tile * per_cta + lane;
 #pragma unroll
@@ -612,6 +644,15 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.red_depth = red_depth;
     p.ksplit = ksplit;
     p.experts = a.experts, p.yptrs = a.yptrs;
+    p.yl_world = 0, p.yl_row0 = 0, p.yl_stride = 0, p.yl_seq = nullptr;
+    for (int d = 0; d < 8; d++) p.yl[d] = 0ull;
+    if (a.line_bases) {
+        if (routed || m != 1 || a.out_f32 || a.line_world < 2 || a.line_world > 8 || (rows & 3) || (a.line_row0 & 3) || !a.line_seq)
+            CN_FAIL(CN_ERR_SHAPE, "%s: line output needs one bf16 row, 2..8 ranks and row counts in multiples of 4 (rows %d, first row %d, ranks %d)", who,
+                    rows, a.line_row0, a.line_world);
+        p.yl_world = a.line_world, p.yl_row0 = a.line_row0, p.yl_stride = (unsigned long long)a.line_stride, p.yl_seq = a.line_seq;
+        for (int d = 0; d < a.line_world; d++) p.yl[d] = a.line_bases[d];
+    }
 #ifdef CN_M1_TRACE
     p.trace = (g_m1_trace && g_m1_trace_i < g_m1_trace_n && !routed) ? g_m1_trace + (size_t)(g_m1_trace_i++) * 512 * 8 : nullptr;
 #endif

@@ -96,6 +96,108 @@ __global__ void __launch_bounds__(512) tp_allgather_kernel(PeerPtrs peers, int r
     pdl_launch_dependents();
 }
 
+// The same exchange without a flag behind the data: every two 32-bit words of the slice travel as a 16-byte line {word,
+// sequence number, word, sequence number} into the peer's line buffer (each 8-byte half carries its own number, so the
+// line may arrive in two pieces); the receiver reads its own line buffer until both halves of a line carry the current
+// sequence number and writes the words into its copy of the vector. No release has to wait for the peer to
+// acknowledge the data, so an exchange costs one trip over NVLink instead of two. Two line buffers are used in turn
+// (sequence number odd / even): a peer can be one exchange ahead of this rank, never two, because its exchange after next
+// needs this rank's lines of the next one.
+__device__ __forceinline__ void st_line(uint4* p, unsigned int w0, unsigned int w1, unsigned int seq) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(w0), "r"(seq), "r"(w1), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint4 ld_line(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(512) tp_allgather_ll_kernel(PeerPtrs peers, int rank, int world, size_t data_off, size_t slice_bytes,
+                                                              size_t ll_off, size_t flag_off, unsigned long long* trace) {
+    CN_TP_STAMP(0);
+    pdl_wait();  // the slice comes from the kernel before this one
+    CN_TP_STAMP(1);
+    unsigned char* mine = peers.base[rank];
+    unsigned int* my_flags = (unsigned int*)(mine + flag_off);
+    const unsigned int seq = my_flags[MAX_WORLD] + 1u;  // read by everybody before anybody can advance it (barrier below)
+    const size_t nl = slice_bytes >> 3;                 // lines of a slice: two 32-bit words each
+    const size_t line_slice = slice_bytes * 2;          // the same slice as lines
+    const size_t par_off = ll_off + (size_t)(seq & 1u) * (size_t)world * line_slice;
+    const int gsz = (512 / (world - 1)) & ~31;  // threads per peer
+    const int gi = threadIdx.x / gsz, gt = threadIdx.x - gi * gsz;
+    if (gi < world - 1) {
+        const int p = gi < rank ? gi : gi + 1;  // the peers in rank order, this rank left out
+        const uint2* src = (const uint2*)(mine + data_off + (size_t)rank * slice_bytes);
+        uint4* dst = (uint4*)(peers.base[p] + par_off + (size_t)rank * line_slice);
+        for (size_t i = gt; i < nl; i += gsz) {
+            const uint2 w = src[i];
+            st_line(dst + i, w.x, w.y, seq);
+        }
+        CN_TP_STAMP(2);
+        const uint4* in = (const uint4*)(mine + par_off + (size_t)p * line_slice);
+        uint2* out = (uint2*)(mine + data_off + (size_t)p * slice_bytes);
+        const long long t0 = clock64();
+        bool ok = true;
+        for (size_t i = gt; i < nl && ok; i += gsz) {
+            uint4 v = ld_line(in + i);
+            while (v.y != seq || v.w != seq) {
+                if (clock64() - t0 > 2000000000LL) {
+                    cn_dev_fail(CN_DEV_WAIT_FULL);
+                    ok = false;
+                    break;
+                }
+                v = ld_line(in + i);
+            }
+            out[i] = make_uint2(v.x, v.z);
+        }
+        CN_TP_STAMP(4);
+    }
+    __syncthreads();
+    CN_TP_STAMP(5);
+    if (threadIdx.x == 0) my_flags[MAX_WORLD] = seq;
+    pdl_launch_dependents();
+}
+
+// The receiving half of an exchange whose lines were stored by the producing GEMV itself (cn_nvfp4_gemv_lines): polls this
+// rank's line buffer for the peers' slices, writes them into its copy of the vector and advances the exchange counter.
+// Resident long before the producing kernels end (it lets its successor start at once and waits for its predecessor only
+// before it leaves), so the vector is complete one NVLink trip after the slowest rank's last tile.
+__global__ void __launch_bounds__(512) tp_recv_lines_kernel(unsigned char* mine, int rank, int world, size_t data_off, size_t slice_bytes,
+                                                            size_t line_off, size_t flag_off, unsigned long long* trace) {
+    CN_TP_STAMP(0);
+    pdl_launch_dependents();
+    unsigned int* my_flags = (unsigned int*)(mine + flag_off);
+    const unsigned int seq = *(volatile unsigned int*)(my_flags + MAX_WORLD) + 1u;  // last advanced a layer ago by this kernel
+    const size_t nl = slice_bytes >> 3, line_slice = slice_bytes * 2;
+    const size_t par_off = line_off + (size_t)(seq & 1u) * (size_t)world * line_slice;
+    const int gsz = (512 / (world - 1)) & ~31;  // threads per peer
+    const int gi = threadIdx.x / gsz, gt = threadIdx.x - gi * gsz;
+    if (gi < world - 1) {
+        const int p = gi < rank ? gi : gi + 1;  // the peers in rank order, this rank left out
+        const uint4* in = (const uint4*)(mine + par_off + (size_t)p * line_slice);
+        uint2* out = (uint2*)(mine + data_off + (size_t)p * slice_bytes);
+        const long long t0 = clock64();
+        bool ok = true;
+        for (size_t i = gt; i < nl && ok; i += gsz) {
+            uint4 v = ld_line(in + i);
+            while (v.y != seq || v.w != seq) {
+                if (clock64() - t0 > 2000000000LL || *(volatile int*)&g_cn_status != 0) {
+                    cn_dev_fail(CN_DEV_WAIT_FULL);
+                    ok = false;
+                    break;
+                }
+                v = ld_line(in + i);
+            }
+            out[i] = make_uint2(v.x, v.z);
+        }
+        CN_TP_STAMP(4);
+    }
+    __syncthreads();
+    pdl_wait();  // this rank's own slice comes from the kernel before this one: the grid ends only after it has
+    CN_TP_STAMP(5);
+    if (threadIdx.x == 0) my_flags[MAX_WORLD] = seq;
+}
+
 }  // namespace
 
 extern "C" int cn_peer_export(const void* ptr, void* handle64, size_t* offset) {
@@ -165,5 +267,47 @@ extern "C" int cn_tp_allgather(const void* const* peer_bases, int rank, int worl
     if (g_tp_trace && g_tp_trace_i < g_tp_trace_n) trace = g_tp_trace + (size_t)(g_tp_trace_i++) * 8;
 #endif
     CN_CUDA(cudaLaunchKernelEx(&cfg, tp_allgather_kernel, pp, rank, world, data_off, slice_bytes, flag_off, trace));
+    return CN_OK;
+}
+
+extern "C" int cn_tp_allgather_ll(const void* const* peer_bases, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off,
+                                  size_t flag_off, cn_stream_t stream) {
+    if (world < 2 || world > MAX_WORLD || rank < 0 || rank >= world) CN_FAIL(CN_ERR_SHAPE, "cn_tp_allgather_ll: rank %d of %d", rank, world);
+    if (!peer_bases || (data_off & 15) || (slice_bytes & 15) || (line_off & 15) || (flag_off & 15) || slice_bytes == 0)
+        CN_FAIL(CN_ERR_SHAPE, "cn_tp_allgather_ll: offsets and the slice size must be multiples of 16 bytes");
+    PeerPtrs pp;
+    for (int r = 0; r < MAX_WORLD; r++) pp.base[r] = r < world ? (unsigned char*)peer_bases[r] : nullptr;
+    for (int r = 0; r < world; r++)
+        if (!pp.base[r]) CN_FAIL(CN_ERR_SHAPE, "cn_tp_allgather_ll: null base pointer for rank %d", r);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1), cfg.blockDim = dim3(512), cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = 1;
+    unsigned long long* trace = nullptr;
+#ifdef CN_M1_TRACE
+    if (g_tp_trace && g_tp_trace_i < g_tp_trace_n) trace = g_tp_trace + (size_t)(g_tp_trace_i++) * 8;
+#endif
+    CN_CUDA(cudaLaunchKernelEx(&cfg, tp_allgather_ll_kernel, pp, rank, world, data_off, slice_bytes, line_off, flag_off, trace));
+    return CN_OK;
+}
+
+extern "C" int cn_tp_recv_lines(void* base, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off, size_t flag_off,
+                                cn_stream_t stream) {
+    if (world < 2 || world > MAX_WORLD || rank < 0 || rank >= world) CN_FAIL(CN_ERR_SHAPE, "cn_tp_recv_lines: rank %d of %d", rank, world);
+    if (!base || (data_off & 15) || (slice_bytes & 15) || (line_off & 15) || (flag_off & 15) || slice_bytes == 0)
+        CN_FAIL(CN_ERR_SHAPE, "cn_tp_recv_lines: offsets and the slice size must be multiples of 16 bytes");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1), cfg.blockDim = dim3(512), cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at, cfg.numAttrs = 1;
+    unsigned long long* trace = nullptr;
+#ifdef CN_M1_TRACE
+    if (g_tp_trace && g_tp_trace_i < g_tp_trace_n) trace = g_tp_trace + (size_t)(g_tp_trace_i++) * 8;
+#endif
+    CN_CUDA(cudaLaunchKernelEx(&cfg, tp_recv_lines_kernel, (unsigned char*)base, rank, world, data_off, slice_bytes, line_off, flag_off, trace));
     return CN_OK;
 }

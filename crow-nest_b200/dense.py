@@ -54,10 +54,16 @@ class PeerExchange:
     """One buffer per rank, visible to every peer over NVLink (CUDA IPC), holding the replicated activation vectors
     of the tensor-parallel stack, plus the arrival counters of each exchange point (`cn_tp_allgather`)."""
 
-    def __init__(self, vectors, rank, world, device, group=None):
-        """vectors: {name: elements}, bf16, one row; every vector's length divides by `world`."""
+    LINE_SLICE_MAX = 8192  # bytes: pushed by the exchange kernel, a 17 KB slice is faster as data + flag, 5 - 7 KB slices as lines (two GPUs)
+
+    def __init__(self, vectors, rank, world, device, group=None, lines=True):
+        """vectors: {name: elements}, bf16, one row; every vector's length divides by `world`. lines: slices up to
+        LINE_SLICE_MAX bytes are exchanged as 16-byte lines that carry their sequence number (`cn_tp_allgather_ll`)
+        instead of data followed by a flag."""
         from .peer import PeerBuffer
-        self.rank, self.world = rank, world
+        self.rank, self.world, self.lines = rank, world, lines
+        self.fused = lines == "fused"  # the producing GEMV stores the lines itself
+        self._line_args = {}
         self.off, at = {}, 0
         for name, n in vectors.items():
             self.off[name] = (at, n * 2 // world)
@@ -66,6 +72,13 @@ class PeerExchange:
         for name in vectors:
             self.flag_off[name] = at
             at += 64
+        self.line_off = {}
+        if lines:
+            for name, n in vectors.items():
+                if lines != "fused" and n * 2 // world > self.LINE_SLICE_MAX:
+                    continue  # a long slice pushed by the exchange kernel goes as data followed by a flag: half the stores
+                self.line_off[name] = at  # two line buffers (odd / even exchanges) of world slices, each twice the slice
+                at += (2 * 2 * n * 2 + 255) // 256 * 256
         self.mem = PeerBuffer(at, rank, world, device, group)
         self.buf, self.bases = self.mem.buf, self.mem.bases
 
@@ -74,11 +87,35 @@ class PeerExchange:
         at, _ = self.off[name]
         return self.buf[at:at + 2 * n].view(torch.bfloat16).view(1, n)
 
+    def line_args(self, name):
+        """What the producing GEMV needs to store its output rows as lines into the peers' buffers, or None when the vector
+        is exchanged as data followed by a flag: (addresses of the ranks' line buffers with 0 for this rank, ranks, global
+        index of this rank's first row, bytes between the two line buffers, address of this rank's exchange counter)."""
+        if name not in self.line_off or not self.fused:
+            return None
+        if name not in self._line_args:
+            import ctypes as C
+            at, slice_bytes = self.off[name]
+            arr = (C.c_ulonglong * self.world)()
+            for r in range(self.world):
+                arr[r] = 0 if r == self.rank else int(self.bases[r]) + self.line_off[name]
+            self._line_args[name] = (arr, self.world, self.rank * (slice_bytes // 2), self.world * slice_bytes * 2,
+                                     int(self.bases[self.rank]) + self.flag_off[name] + 4 * 8)
+        return self._line_args[name]
+
     def exchange(self, name):
         from ._lib import check, lib
         at, slice_bytes = self.off[name]
-        check(lib().cn_tp_allgather(self.bases, self.rank, self.world, at, slice_bytes, self.flag_off[name],
-                                    torch.cuda.current_stream().cuda_stream))
+        if name in self.line_off and self.fused:
+            # the lines were stored by the GEMV that produced the slice: only the receiving half is left
+            check(lib().cn_tp_recv_lines(int(self.bases[self.rank]), self.rank, self.world, at, slice_bytes, self.line_off[name], self.flag_off[name],
+                                         torch.cuda.current_stream().cuda_stream))
+        elif name in self.line_off:
+            check(lib().cn_tp_allgather_ll(self.bases, self.rank, self.world, at, slice_bytes, self.line_off[name], self.flag_off[name],
+                                           torch.cuda.current_stream().cuda_stream))
+        else:
+            check(lib().cn_tp_allgather(self.bases, self.rank, self.world, at, slice_bytes, self.flag_off[name],
+                                        torch.cuda.current_stream().cuda_stream))
 
 
 class DenseStack:
@@ -114,11 +151,11 @@ class DenseStack:
             # per-rank slices land here, then one all-gather per projection
             self.part = {n: torch.empty((m, r // world), dtype=dtype, device=device) for n, r in
                          (("q", self.qkv), ("o", self.hidden), ("h", self.inter), ("y", self.hidden))}
-            if exchange == "peer" and max_m == 1 and dtype == torch.bfloat16:
+            if exchange in ("peer", "peer-lines", "peer-flags") and max_m == 1 and dtype == torch.bfloat16:
                 # one activation row: the slices are written straight into a peer-visible buffer and pushed to the peers
                 sizes = {"q": self.qkv, "o": self.hidden, "h": self.inter, "y": self.hidden}
                 try:
-                    self.peer = PeerExchange(sizes, rank, world, device, group)  # raises on every rank or on none
+                    self.peer = PeerExchange(sizes, rank, world, device, group, lines={"peer": "fused", "peer-lines": True, "peer-flags": False}[exchange])  # raises on every rank or on none
                     self.q, self.o, self.h, self.y = (self.peer.vector(n, r) for n, r in sizes.items())
                 except CrownestError as e:  # no peer access between these GPUs: NCCL all-gather instead
                     self.peer, self.peer_error = None, str(e)
@@ -174,7 +211,10 @@ class DenseStack:
             out = full[:, lo:hi]  # this rank's slice of the replicated vector, in place
         else:
             out = full[:m] if self.world == 1 else self.part[name][:m]
-        if gu is None:
+        lines = self.peer.line_args(name) if self.peer is not None and m == 1 else None
+        if lines is not None:
+            ops.launch_gemv_lines(w, x, out, lines, gu=gu)
+        elif gu is None:
             ops.launch_gemv(w, x, out)
         else:
             ops.launch_gemv_gu(w, gu, x, out)

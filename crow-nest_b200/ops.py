@@ -125,6 +125,22 @@ def act_cascade(x, levels=3):
 dense_proj = launch_gemv  # Engine::dense_proj (engine/src/gen.rs:3915): same operator at t == 1 and t <= 4
 
 
+def launch_gemv_lines(w: Fp4, x, y, lines, gu: Fp4 = None, limit=0.0):
+    """The one-row bf16 GEMV (or fused gate/up) of a tensor-parallel rank whose output rows also go out as 16-byte lines to
+    the other ranks' line buffers (cn_nvfp4_gemv_lines / _gu_lines); `lines` = (bases, world, row0, stride, counter address)
+    as `PeerExchange.line_args` gives them. The receiving side is cn_tp_recv_lines."""
+    bases, world, row0, stride, seq = lines
+    if x.dtype != torch.bfloat16 or x.numel() != w.cols:
+        raise CrownestError("line output takes one bf16 activation row")
+    if gu is None:
+        check(lib().cn_nvfp4_gemv_lines(w.w.data_ptr(), w.gs.data_ptr(), x.data_ptr(), y.data_ptr(), w.rows, w.cols, bases, world, row0, stride, seq,
+                                        _stream()))
+    else:
+        check(lib().cn_nvfp4_gemv_gu_lines(w.w.data_ptr(), gu.w.data_ptr(), w.gs.data_ptr(), gu.gs.data_ptr(), x.data_ptr(), y.data_ptr(), w.rows,
+                                           w.cols, float(limit), bases, world, row0, stride, seq, _stream()))
+    return y
+
+
 def launch_gemv_gu(gate: Fp4, up: Fp4, x, h=None, limit=0.0):
     """h = act(gate x, up x): gemv_nvfp4_gu / _gum, the first half of Engine::dense_ffn_w
     (engine/src/gen.rs:3974-3981). limit > 0 selects the clamped SwiGLU."""

@@ -335,6 +335,27 @@ int cn_peer_open(const void* handle64, size_t offset, void** ptr);
 int cn_peer_close(void* ptr, size_t offset);
 int cn_tp_allgather(const void* const* peer_bases, int rank, int world, size_t data_off, size_t slice_bytes, size_t flag_off,
                     cn_stream_t stream);
+/* The same exchange as 16-byte lines {word, sequence number, word, sequence number} through a line buffer at line_off
+ * (2 x world x 2 x slice_bytes bytes in every rank's buffer, zero before the first use): no flag has to wait for the
+ * data to be acknowledged, so an exchange is one trip over NVLink; meant for slices of a few KB. The result in [data_off, + world * slice_bytes) is the same
+ * bytes; flag_off as above (only its sequence counter is used). */
+int cn_tp_allgather_ll(const void* const* peer_bases, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off,
+                       size_t flag_off, cn_stream_t stream);
+/* The exchange fused into the GEMV that produces the slice (no counterpart in the reference). cn_nvfp4_gemv_lines /
+ * cn_nvfp4_gemv_gu_lines are cn_nvfp4_gemv / cn_nvfp4_gemv_gu for one bf16 activation row (y / h hold `rows` / `inter`
+ * values) whose epilogue also stores the output rows as lines into the other ranks' line buffers: line_bases[r] is the
+ * device address of rank r's line buffer of this vector (0 for the calling rank), row0 the global index of the call's
+ * first output row (rows and row0 multiples of 4), line_stride the bytes between a rank's two line buffers
+ * (world x 2 x slice_bytes), line_seq the address of the calling rank's exchange counter of the vector (flag_off + 32 in
+ * its buffer). cn_tp_recv_lines is the receiving half on every rank: it polls the rank's own line buffer for the peers'
+ * slices, writes them into [data_off, ...) and advances the counter. It lets its successor in the stream start at once
+ * and waits for its predecessor only before it ends, so it may be enqueued right behind the producing GEMV. */
+int cn_nvfp4_gemv_lines(const void* w, const float* gs, const void* x, void* y, int rows, int k, const unsigned long long* line_bases, int world,
+                        int row0, size_t line_stride, const unsigned int* line_seq, cn_stream_t stream);
+int cn_nvfp4_gemv_gu_lines(const void* wg, const void* wu, const float* gs_g, const float* gs_u, const void* x, void* h, int inter, int k,
+                           float limit, const unsigned long long* line_bases, int world, int row0, size_t line_stride,
+                           const unsigned int* line_seq, cn_stream_t stream);
+int cn_tp_recv_lines(void* base, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off, size_t flag_off, cn_stream_t stream);
 
 #ifdef __cplusplus
 }

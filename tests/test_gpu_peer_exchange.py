@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, protocol):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -28,7 +28,7 @@ def _worker(rank, world, port, out):
     res = "ok"
     try:
         a = dense.DenseStack(layers=3, device=f"cuda:{rank}", seed=5, rank=rank, world=world, exchange="nccl")
-        b = dense.DenseStack(layers=3, device=f"cuda:{rank}", seed=5, rank=rank, world=world, exchange="peer")
+        b = dense.DenseStack(layers=3, device=f"cuda:{rank}", seed=5, rank=rank, world=world, exchange=protocol)
         assert b.peer is not None
         x = torch.randn((1, a.hidden), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
         a.x.copy_(x), b.x.copy_(x)
@@ -52,14 +52,16 @@ def _worker(rank, world, port, out):
     os._exit(0)
 
 
-def test_peer_exchange_matches_the_all_gather():
+# lines stored by the GEMV itself / lines pushed by the exchange kernel / data followed by a flag
+@pytest.mark.parametrize("protocol", ["peer", "peer-lines", "peer-flags"])
+def test_peer_exchange_matches_the_all_gather(protocol):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, protocol)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in procs]
