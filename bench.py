@@ -100,6 +100,7 @@ class Timer:
 
     def run(self, step, steps, warmup):
         import torch
+        self.barrier()  # the ranks start their first step together (set-up times differ, device-side waits are bounded)
         for _ in range(warmup):
             step()
         self.barrier()
@@ -481,7 +482,8 @@ def intervals_arm(args, rank=0, world=1, local=0):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         group = dist.group.WORLD
     layers = max(3, min(args.layers, 8))
-    st = dense.DenseStack(layers=layers, seed=0, device=f"cuda:{local}", rank=rank, world=world, group=group, exchange="peer")
+    st = dense.DenseStack(layers=layers, seed=0, device=f"cuda:{local}", rank=rank, world=world, group=group,
+                          exchange=args.exchange if args.exchange != "nccl" else "peer")
     if world > 1 and st.peer is None:
         raise SystemExit("intervals: the peer-memory exchange is not available between these GPUs")
     st.x.copy_(torch.randn((1, st.hidden), device=f"cuda:{local}").to(torch.bfloat16))

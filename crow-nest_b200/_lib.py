@@ -71,9 +71,10 @@ _SIGS = {
     "cn_peer_close": [_vp, C.c_size_t],
     "cn_tp_allgather": [C.POINTER(C.c_void_p), _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, _vp],
     "cn_tp_allgather_ll": [C.POINTER(C.c_void_p), _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _vp],
-    "cn_tp_recv_lines": [_vp, _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _vp],
-    "cn_nvfp4_gemv_lines": [_vp, _vp, _vp, _vp, _i, _i, C.POINTER(C.c_ulonglong), _i, _i, C.c_size_t, _vp, _vp],
-    "cn_nvfp4_gemv_gu_lines": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, C.POINTER(C.c_ulonglong), _i, _i, C.c_size_t, _vp, _vp],
+    "cn_tp_epoch_advance": [_vp, _vp],
+    "cn_tp_recv_lines": [_vp, _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, _vp, _i, _i, _i, _vp],
+    "cn_nvfp4_gemv_lines": [_vp, _vp, _vp, _vp, _i, _i, C.POINTER(C.c_ulonglong), _i, _i, C.c_size_t, _vp, _i, _i, _i, _vp],
+    "cn_nvfp4_gemv_gu_lines": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, C.POINTER(C.c_ulonglong), _i, _i, C.c_size_t, _vp, _i, _i, _i, _vp],
     "cn_mul1_plan_create": [C.POINTER(C.c_void_p), _i, _i, _i, _i, _i, _i],
     "cn_mul1_plan_destroy": [_vp],
     "cn_mul1_gemv": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],

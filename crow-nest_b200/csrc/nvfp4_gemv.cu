@@ -579,23 +579,25 @@ extern "C" int cn_nvfp4_gemv_gu(const void* wg, const void* wu, const float* gs_
 }
 
 extern "C" int cn_nvfp4_gemv_lines(const void* w, const float* gs, const void* x, void* y, int rows, int k, const unsigned long long* line_bases,
-                                   int world, int row0, size_t line_stride, const unsigned int* line_seq, cn_stream_t stream) {
-    if (!line_bases || !line_seq) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_lines: null line buffers or counter");
+                                   int world, int row0, size_t line_stride, const unsigned int* epoch, int tag, int buf, int flip, cn_stream_t stream) {
+    if (!line_bases || !epoch) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_lines: null line buffers or step counter");
     GemvCall a = {};
     a.w0 = w, a.gs0 = gs, a.x = x, a.y = y, a.rows = rows, a.k = k, a.m = 1, a.ldy = rows, a.dtype = CN_BF16;
-    a.line_bases = line_bases, a.line_world = world, a.line_row0 = row0, a.line_stride = line_stride, a.line_seq = line_seq;
+    a.line_bases = line_bases, a.line_world = world, a.line_row0 = row0, a.line_stride = line_stride, a.line_epoch = epoch;
+    a.line_tag = tag, a.line_buf = buf, a.line_flip = flip;
     return cn_gemv_launch(a, (cudaStream_t)stream, "cn_nvfp4_gemv_lines");
 }
 
 extern "C" int cn_nvfp4_gemv_gu_lines(const void* wg, const void* wu, const float* gs_g, const float* gs_u, const void* x, void* h, int inter, int k,
                                       float limit, const unsigned long long* line_bases, int world, int row0, size_t line_stride,
-                                      const unsigned int* line_seq, cn_stream_t stream) {
+                                      const unsigned int* epoch, int tag, int buf, int flip, cn_stream_t stream) {
     if (!wu) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_gu_lines: the up matrix is null");
-    if (!line_bases || !line_seq) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_gu_lines: null line buffers or counter");
+    if (!line_bases || !epoch) CN_FAIL(CN_ERR_SHAPE, "cn_nvfp4_gemv_gu_lines: null line buffers or step counter");
     GemvCall a = {};
     a.w0 = wg, a.w1 = wu, a.gs0 = gs_g, a.gs1 = gs_u, a.x = x, a.y = h, a.rows = inter, a.k = k, a.m = 1, a.ldy = inter, a.limit = limit,
     a.dtype = CN_BF16;
-    a.line_bases = line_bases, a.line_world = world, a.line_row0 = row0, a.line_stride = line_stride, a.line_seq = line_seq;
+    a.line_bases = line_bases, a.line_world = world, a.line_row0 = row0, a.line_stride = line_stride, a.line_epoch = epoch;
+    a.line_tag = tag, a.line_buf = buf, a.line_flip = flip;
     return cn_gemv_launch(a, (cudaStream_t)stream, "cn_nvfp4_gemv_gu_lines");
 }
 

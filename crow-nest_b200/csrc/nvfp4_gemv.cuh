@@ -24,12 +24,14 @@ struct GemvCall {
     int experts;  // entries of the tables (0 = unknown: ids are trusted); an id beyond them skips the combo
     const unsigned long long* yptrs;  // routed form: output row address per combo (null: y + combo * ldy); may name peer memory
     // Tensor-parallel line output (one bf16 activation row, plain or gate/up form): besides y, the output rows go out as
-    // 16-byte lines {two rows, number, two rows, number} to the line buffers of the other ranks, where number = *line_seq + 1
-    // and the buffer used is number & 1. line_bases: host array [line_world] of device addresses (0 = this rank).
+    // 16-byte lines {two rows, number, two rows, number} to the line buffers of the other ranks, where number =
+    // *line_epoch * 4096 + line_tag and the buffer used is line_buf ^ (line_flip & *line_epoch & 1).
+    // line_bases: host array [line_world] of device addresses (0 = this rank).
     const unsigned long long* line_bases;
-    int line_world, line_row0;       // ranks; global index of output row 0 (a multiple of 4)
-    size_t line_stride;              // bytes between the two line buffers of a rank
-    const unsigned int* line_seq;    // this rank's exchange counter of the vector (advanced by cn_tp_recv_lines)
+    int line_world, line_row0;        // ranks; global index of output row 0 (a multiple of 4)
+    size_t line_stride;               // bytes between the two line buffers of a rank
+    const unsigned int* line_epoch;   // this rank's step counter (cn_tp_epoch_advance)
+    int line_tag, line_buf, line_flip;
 };
 
 int cn_gemv_launch(const GemvCall& a, cudaStream_t stream, const char* who);
@@ -97,7 +99,8 @@ struct GemvParams {
     unsigned long long yl[8];
     int yl_world, yl_row0;
     unsigned long long yl_stride;
-    const unsigned int* yl_seq;
+    const unsigned int* yl_epoch;
+    int yl_tag, yl_buf, yl_flip;
 #ifdef CN_M1_TRACE
     unsigned long long* trace;  // [8] globaltimer stamps per CTA of this launch (diagnostic build only), or null
 #endif

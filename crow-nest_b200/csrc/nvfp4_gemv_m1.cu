@@ -95,14 +95,14 @@ __device__ __forceinline__ unsigned long long gtime() {
 // Tensor-parallel line output, called by all lanes of warp 0: lane l < 16 holds output row row0 + l as r. Four rows make one
 // 16-byte line {rows 0-1, number, rows 2-3, number}; lane (d, j) = (lane >> 2, lane & 3) stores line j of the tile into
 // rank d's line buffer. Plain stores: the receiver polls the numbers, nothing waits for an acknowledgement here.
-__device__ __forceinline__ void push_lines(const GemvParams& p, int row0, int nrows, float r, int lane, unsigned int seq) {
+__device__ __forceinline__ void push_lines(const GemvParams& p, int row0, int nrows, float r, int lane, unsigned int seq, unsigned int buf) {
     const uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(r));
     const uint32_t pair = b | (__shfl_down_sync(0xffffffffu, b, 1) << 16);  // even lanes: rows l, l + 1
     const uint32_t next = __shfl_down_sync(0xffffffffu, pair, 2);           // lanes 4 j: rows 4 j + 2, 4 j + 3
     const int j = lane & 3, d = lane >> 2;
     const uint32_t a0 = __shfl_sync(0xffffffffu, pair, 4 * j), a1 = __shfl_sync(0xffffffffu, next, 4 * j);
     if (d < p.yl_world && p.yl[d] != 0ull && 4 * j < nrows) {
-        uint4* dst = (uint4*)(uintptr_t)(p.yl[d] + (unsigned long long)(seq & 1u) * p.yl_stride) + ((p.yl_row0 + row0) >> 2) + j;
+        uint4* dst = (uint4*)(uintptr_t)(p.yl[d] + (unsigned long long)buf * p.yl_stride) + ((p.yl_row0 + row0) >> 2) + j;
         asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(a0), "r"(seq), "r"(a1), "r"(seq) : "memory");
     }
 }
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         const uint64_t pol = l2_policy_evict_first();
         int s = 0;
         uint32_t par = 0;  // parity of the current use of stage s
-        bool first_round = true, pfail = false;
+        bool first_round = true, pfail = false, waited_pred = p.ids != nullptr;  // the routed form has waited already
         for (int tile = cid; tile < ntiles && !pfail; tile += ncl) {
             const int row0 = tile * per_cta;
             const int row = gu ? row0 + (lane & 7) : row0 + lane;
@@ -199,6 +199,13 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             for (int c = 0; c < nch; c++) {
                 const int nblk = min(TX, bpr - c * TX);
                 const uint32_t piece = (uint32_t)nblk * 36u;
+                if (!first_round && !waited_pred) {
+                    // The ring is full: a slot frees only once the consumers run, and they wait for the predecessor grid.
+                    // The producer waits for it too (a dependency wait, not a spin) so that the bounded wait below
+                    // times the consumers alone, however long a predecessor that waits for other GPUs takes.
+                    pdl_wait();
+                    waited_pred = true;
+                }
                 if (!first_round && !mbar_wait(&empty[s], par ^ 1u)) {
                     cn_dev_fail(CN_DEV_WAIT_EMPTY);
                     pfail = true;
@@ -230,8 +237,9 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     pdl_launch_dependents();
     pdl_wait();  // the activations may come from the previous kernel of the stream
     if (threadIdx.x == 0) { CN_STAMP(1); }
-    // the number of this exchange (tensor-parallel line output): the counter was last advanced a layer ago
-    const unsigned int line_seq = (MT == 1 && p.yl_world > 0) ? *(volatile const unsigned int*)p.yl_seq + 1u : 0u;
+    // the number of this exchange (tensor-parallel line output) from the step counter, which was advanced at the step's start
+    const unsigned int line_epoch = (MT == 1 && p.yl_world > 0) ? *(volatile const unsigned int*)p.yl_epoch : 0u;
+    const unsigned int line_seq = line_epoch * 4096u + (unsigned int)p.yl_tag, line_buf = (unsigned int)p.yl_buf ^ ((unsigned int)p.yl_flip & line_epoch & 1u);
     const int ntask = MT * bpr * 8;
     auto load_x = [&](int task) -> uint4 {
         // task = (row * bpr + block) * 8 + chunk; rows beyond p.m read as zero
@@ -492,7 +500,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                             else
                                 ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(r);
                         }
-                        if (p.yl_world > 0) push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), r, lane, line_seq);
+                        if (p.yl_world > 0) push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), r, lane, line_seq, line_buf);
                     }
                 }
             } else if (MT == 1 && p.yl_world > 0) {
@@ -508,7 +516,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                 }
                 const float v = gu ? act_gu(v0, v1, p.limit) : v0;
                 if (lane < per_cta && row < p.rows) ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(v);
-                push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), v, lane, line_seq);
+                push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), v, lane, line_seq, line_buf);
             } else if (lane < per_cta) {
                 const int row = tile * per_cta + lane;
 #pragma unroll
@@ -644,13 +652,15 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     p.red_depth = red_depth;
     p.ksplit = ksplit;
     p.experts = a.experts, p.yptrs = a.yptrs;
-    p.yl_world = 0, p.yl_row0 = 0, p.yl_stride = 0, p.yl_seq = nullptr;
+    p.yl_world = 0, p.yl_row0 = 0, p.yl_stride = 0, p.yl_epoch = nullptr, p.yl_tag = 0, p.yl_buf = 0, p.yl_flip = 0;
     for (int d = 0; d < 8; d++) p.yl[d] = 0ull;
     if (a.line_bases) {
-        if (routed || m != 1 || a.out_f32 || a.line_world < 2 || a.line_world > 8 || (rows & 3) || (a.line_row0 & 3) || !a.line_seq)
+        if (routed || m != 1 || a.out_f32 || a.line_world < 2 || a.line_world > 8 || (rows & 3) || (a.line_row0 & 3) || !a.line_epoch ||
+            a.line_tag < 1 || a.line_tag > 4095 || (a.line_buf & ~1))
             CN_FAIL(CN_ERR_SHAPE, "%s: line output needs one bf16 row, 2..8 ranks and row counts in multiples of 4 (rows %d, first row %d, ranks %d)", who,
                     rows, a.line_row0, a.line_world);
-        p.yl_world = a.line_world, p.yl_row0 = a.line_row0, p.yl_stride = (unsigned long long)a.line_stride, p.yl_seq = a.line_seq;
+        p.yl_world = a.line_world, p.yl_row0 = a.line_row0, p.yl_stride = (unsigned long long)a.line_stride, p.yl_epoch = a.line_epoch;
+        p.yl_tag = a.line_tag, p.yl_buf = a.line_buf, p.yl_flip = a.line_flip ? 1 : 0;
         for (int d = 0; d < a.line_world; d++) p.yl[d] = a.line_bases[d];
     }
 #ifdef CN_M1_TRACE

@@ -159,17 +159,21 @@ __global__ void __launch_bounds__(512) tp_allgather_ll_kernel(PeerPtrs peers, in
 }
 
 // The receiving half of an exchange whose lines were stored by the producing GEMV itself (cn_nvfp4_gemv_lines): polls this
-// rank's line buffer for the peers' slices, writes them into its copy of the vector and advances the exchange counter.
+// rank's line buffer for the peers' slices and writes them into its copy of the vector. The exchange number comes from the
+// rank's step counter (advanced once at the start of a step by cn_tp_epoch_advance, long before this kernel can start) and a
+// tag fixed at launch, not from anything an earlier exchange writes: with every kernel letting its successor start early,
+// kernels many exchanges ahead can be resident at once.
 // Resident long before the producing kernels end (it lets its successor start at once and waits for its predecessor only
 // before it leaves), so the vector is complete one NVLink trip after the slowest rank's last tile.
 __global__ void __launch_bounds__(512) tp_recv_lines_kernel(unsigned char* mine, int rank, int world, size_t data_off, size_t slice_bytes,
-                                                            size_t line_off, size_t flag_off, unsigned long long* trace) {
+                                                            size_t line_off, const unsigned int* epoch_ptr, int tag, int buf, int flip,
+                                                            unsigned long long* trace) {
     CN_TP_STAMP(0);
     pdl_launch_dependents();
-    unsigned int* my_flags = (unsigned int*)(mine + flag_off);
-    const unsigned int seq = *(volatile unsigned int*)(my_flags + MAX_WORLD) + 1u;  // last advanced a layer ago by this kernel
+    const unsigned int epoch = *(volatile const unsigned int*)epoch_ptr;
+    const unsigned int seq = epoch * 4096u + (unsigned int)tag;
     const size_t nl = slice_bytes >> 3, line_slice = slice_bytes * 2;
-    const size_t par_off = line_off + (size_t)(seq & 1u) * (size_t)world * line_slice;
+    const size_t par_off = line_off + (size_t)((unsigned int)buf ^ ((unsigned int)flip & epoch & 1u)) * (size_t)world * line_slice;
     const int gsz = (512 / (world - 1)) & ~31;  // threads per peer
     const int gi = threadIdx.x / gsz, gt = threadIdx.x - gi * gsz;
     if (gi < world - 1) {
@@ -195,8 +199,9 @@ __global__ void __launch_bounds__(512) tp_recv_lines_kernel(unsigned char* mine,
     __syncthreads();
     pdl_wait();  // this rank's own slice comes from the kernel before this one: the grid ends only after it has
     CN_TP_STAMP(5);
-    if (threadIdx.x == 0) my_flags[MAX_WORLD] = seq;
 }
+
+__global__ void tp_epoch_kernel(unsigned int* epoch) { *epoch = *epoch + 1u; }
 
 }  // namespace
 
@@ -293,11 +298,19 @@ extern "C" int cn_tp_allgather_ll(const void* const* peer_bases, int rank, int w
     return CN_OK;
 }
 
-extern "C" int cn_tp_recv_lines(void* base, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off, size_t flag_off,
-                                cn_stream_t stream) {
+extern "C" int cn_tp_epoch_advance(void* epoch, cn_stream_t stream) {
+    if (!epoch || ((uintptr_t)epoch & 3)) CN_FAIL(CN_ERR_SHAPE, "cn_tp_epoch_advance: null or unaligned counter");
+    // a plain launch: it neither starts before its predecessor has ended nor lets its successor start before it has
+    tp_epoch_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((unsigned int*)epoch);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+extern "C" int cn_tp_recv_lines(void* base, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off, const void* epoch,
+                                int tag, int buf, int flip, cn_stream_t stream) {
     if (world < 2 || world > MAX_WORLD || rank < 0 || rank >= world) CN_FAIL(CN_ERR_SHAPE, "cn_tp_recv_lines: rank %d of %d", rank, world);
-    if (!base || (data_off & 15) || (slice_bytes & 15) || (line_off & 15) || (flag_off & 15) || slice_bytes == 0)
-        CN_FAIL(CN_ERR_SHAPE, "cn_tp_recv_lines: offsets and the slice size must be multiples of 16 bytes");
+    if (!base || !epoch || (data_off & 15) || (slice_bytes & 15) || (line_off & 15) || slice_bytes == 0 || tag < 1 || tag > 4095 || (buf & ~1))
+        CN_FAIL(CN_ERR_SHAPE, "cn_tp_recv_lines: offsets and the slice size must be multiples of 16 bytes, the tag in 1..4095, the buffer 0 or 1");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1), cfg.blockDim = dim3(512), cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute at[1];
@@ -308,6 +321,7 @@ extern "C" int cn_tp_recv_lines(void* base, int rank, int world, size_t data_off
 #ifdef CN_M1_TRACE
     if (g_tp_trace && g_tp_trace_i < g_tp_trace_n) trace = g_tp_trace + (size_t)(g_tp_trace_i++) * 8;
 #endif
-    CN_CUDA(cudaLaunchKernelEx(&cfg, tp_recv_lines_kernel, (unsigned char*)base, rank, world, data_off, slice_bytes, line_off, flag_off, trace));
+    CN_CUDA(cudaLaunchKernelEx(&cfg, tp_recv_lines_kernel, (unsigned char*)base, rank, world, data_off, slice_bytes, line_off,
+                               (const unsigned int*)epoch, tag, buf, flip ? 1 : 0, trace));
     return CN_OK;
 }

@@ -63,7 +63,8 @@ class PeerExchange:
         from .peer import PeerBuffer
         self.rank, self.world, self.lines = rank, world, lines
         self.fused = lines == "fused"  # the producing GEMV stores the lines itself
-        self._line_args = {}
+        self._line_bases, self._tag, self._count, self._pending = {}, 0, {}, None
+        self.per_step = {}  # exchanges of each vector per step (set by the owner of the step; odd counts alternate with the step counter)
         self.off, at = {}, 0
         for name, n in vectors.items():
             self.off[name] = (at, n * 2 // world)
@@ -72,6 +73,8 @@ class PeerExchange:
         for name in vectors:
             self.flag_off[name] = at
             at += 64
+        self.epoch_off = at  # the rank's step counter
+        at += 64
         self.line_off = {}
         if lines:
             for name, n in vectors.items():
@@ -87,28 +90,46 @@ class PeerExchange:
         at, _ = self.off[name]
         return self.buf[at:at + 2 * n].view(torch.bfloat16).view(1, n)
 
+    def begin_step(self):
+        """Start of a step (fused line exchange): advance the rank's step counter, from which every exchange of the step
+        takes its number, and restart the tags."""
+        from ._lib import check, lib
+        if not self.fused:
+            return
+        check(lib().cn_tp_epoch_advance(int(self.bases[self.rank]) + self.epoch_off, torch.cuda.current_stream().cuda_stream))
+        self._tag = 0
+        self._count = {n: 0 for n in self.line_off}
+
     def line_args(self, name):
         """What the producing GEMV needs to store its output rows as lines into the peers' buffers, or None when the vector
-        is exchanged as data followed by a flag: (addresses of the ranks' line buffers with 0 for this rank, ranks, global
-        index of this rank's first row, bytes between the two line buffers, address of this rank's exchange counter)."""
+        is exchanged by a separate kernel: (addresses of the ranks' line buffers with 0 for this rank, ranks, global index
+        of this rank's first row, bytes between the two line buffers, address of this rank's step counter, the exchange's
+        tag within the step, its buffer, whether the buffer alternates with the step counter). exchange(name) must follow."""
         if name not in self.line_off or not self.fused:
             return None
-        if name not in self._line_args:
+        if name not in self._line_bases:
             import ctypes as C
-            at, slice_bytes = self.off[name]
             arr = (C.c_ulonglong * self.world)()
             for r in range(self.world):
                 arr[r] = 0 if r == self.rank else int(self.bases[r]) + self.line_off[name]
-            self._line_args[name] = (arr, self.world, self.rank * (slice_bytes // 2), self.world * slice_bytes * 2,
-                                     int(self.bases[self.rank]) + self.flag_off[name] + 4 * 8)
-        return self._line_args[name]
+            self._line_bases[name] = arr
+        at, slice_bytes = self.off[name]
+        self._tag += 1
+        buf = self._count[name] & 1
+        self._count[name] += 1
+        self._pending = (name, self._tag, buf)
+        return (self._line_bases[name], self.world, self.rank * (slice_bytes // 2), self.world * slice_bytes * 2,
+                int(self.bases[self.rank]) + self.epoch_off, self._tag, buf, self.per_step.get(name, 0) & 1)
 
     def exchange(self, name):
         from ._lib import check, lib
         at, slice_bytes = self.off[name]
         if name in self.line_off and self.fused:
             # the lines were stored by the GEMV that produced the slice: only the receiving half is left
-            check(lib().cn_tp_recv_lines(int(self.bases[self.rank]), self.rank, self.world, at, slice_bytes, self.line_off[name], self.flag_off[name],
+            pname, tag, buf = self._pending
+            assert pname == name
+            check(lib().cn_tp_recv_lines(int(self.bases[self.rank]), self.rank, self.world, at, slice_bytes, self.line_off[name],
+                                         int(self.bases[self.rank]) + self.epoch_off, tag, buf, self.per_step.get(name, 0) & 1,
                                          torch.cuda.current_stream().cuda_stream))
         elif name in self.line_off:
             check(lib().cn_tp_allgather_ll(self.bases, self.rank, self.world, at, slice_bytes, self.line_off[name], self.flag_off[name],
@@ -157,6 +178,7 @@ class DenseStack:
                 try:
                     self.peer = PeerExchange(sizes, rank, world, device, group, lines={"peer": "fused", "peer-lines": True, "peer-flags": False}[exchange])  # raises on every rank or on none
                     self.q, self.o, self.h, self.y = (self.peer.vector(n, r) for n, r in sizes.items())
+                    self.peer.per_step = {n: self.layers for n in sizes}  # every vector is exchanged once per layer
                 except CrownestError as e:  # no peer access between these GPUs: NCCL all-gather instead
                     self.peer, self.peer_error = None, str(e)
         self.launches_per_step = 4 * self.layers
@@ -230,6 +252,8 @@ class DenseStack:
                 c.run()
             return self.y[:1]
         x = self.x[:m]
+        if self.peer is not None and m == 1:
+            self.peer.begin_step()
         for mats in self.w:
             self._proj(mats["qkv"], x, "q", self.q, m)
             self._proj(mats["o"], x, "o", self.o, m)

@@ -127,17 +127,17 @@ dense_proj = launch_gemv  # Engine::dense_proj (engine/src/gen.rs:3915): same op
 
 def launch_gemv_lines(w: Fp4, x, y, lines, gu: Fp4 = None, limit=0.0):
     """The one-row bf16 GEMV (or fused gate/up) of a tensor-parallel rank whose output rows also go out as 16-byte lines to
-    the other ranks' line buffers (cn_nvfp4_gemv_lines / _gu_lines); `lines` = (bases, world, row0, stride, counter address)
-    as `PeerExchange.line_args` gives them. The receiving side is cn_tp_recv_lines."""
-    bases, world, row0, stride, seq = lines
+    the other ranks' line buffers (cn_nvfp4_gemv_lines / _gu_lines); `lines` = (bases, world, row0, stride, step counter
+    address, tag, buffer, flip) as `PeerExchange.line_args` gives them. The receiving side is cn_tp_recv_lines."""
+    bases, world, row0, stride, epoch, tag, buf, flip = lines
     if x.dtype != torch.bfloat16 or x.numel() != w.cols:
         raise CrownestError("line output takes one bf16 activation row")
     if gu is None:
-        check(lib().cn_nvfp4_gemv_lines(w.w.data_ptr(), w.gs.data_ptr(), x.data_ptr(), y.data_ptr(), w.rows, w.cols, bases, world, row0, stride, seq,
-                                        _stream()))
+        check(lib().cn_nvfp4_gemv_lines(w.w.data_ptr(), w.gs.data_ptr(), x.data_ptr(), y.data_ptr(), w.rows, w.cols, bases, world, row0, stride, epoch,
+                                        tag, buf, flip, _stream()))
     else:
         check(lib().cn_nvfp4_gemv_gu_lines(w.w.data_ptr(), gu.w.data_ptr(), w.gs.data_ptr(), gu.gs.data_ptr(), x.data_ptr(), y.data_ptr(), w.rows,
-                                           w.cols, float(limit), bases, world, row0, stride, seq, _stream()))
+                                           w.cols, float(limit), bases, world, row0, stride, epoch, tag, buf, flip, _stream()))
     return y
 
 

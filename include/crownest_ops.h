@@ -344,18 +344,25 @@ int cn_tp_allgather_ll(const void* const* peer_bases, int rank, int world, size_
 /* The exchange fused into the GEMV that produces the slice (no counterpart in the reference). cn_nvfp4_gemv_lines /
  * cn_nvfp4_gemv_gu_lines are cn_nvfp4_gemv / cn_nvfp4_gemv_gu for one bf16 activation row (y / h hold `rows` / `inter`
  * values) whose epilogue also stores the output rows as lines into the other ranks' line buffers: line_bases[r] is the
- * device address of rank r's line buffer of this vector (0 for the calling rank), row0 the global index of the call's
+ * device address of rank r's line buffers of this vector (0 for the calling rank), row0 the global index of the call's
  * first output row (rows and row0 multiples of 4), line_stride the bytes between a rank's two line buffers
- * (world x 2 x slice_bytes), line_seq the address of the calling rank's exchange counter of the vector (flag_off + 32 in
- * its buffer). cn_tp_recv_lines is the receiving half on every rank: it polls the rank's own line buffer for the peers'
- * slices, writes them into [data_off, ...) and advances the counter. It lets its successor in the stream start at once
- * and waits for its predecessor only before it ends, so it may be enqueued right behind the producing GEMV. */
+ * (world x 2 x slice_bytes). The number a line carries is *epoch x 4096 + tag: epoch is the rank's step counter, which
+ * cn_tp_epoch_advance increments once at the start of every step (all ranks run the same steps), tag (1..4095) names the
+ * exchange within the step and is the same on every rank. The lines go to buffer buf ^ (flip & *epoch & 1): consecutive
+ * exchanges of a vector must alternate between its two buffers (a peer can be one exchange ahead, never two), also across
+ * steps, so a vector that is exchanged an odd number of times per step passes flip = 1.
+ * cn_tp_recv_lines is the receiving half on every rank, with the same tag / buf / flip: it polls the rank's own line
+ * buffer for the peers' slices and writes them into [data_off, ...). It lets its successor in the stream start at once
+ * and waits for its predecessor only before it ends, so it is enqueued right behind the producing GEMV; the wait for the
+ * peers is bounded. */
+int cn_tp_epoch_advance(void* epoch, cn_stream_t stream);
 int cn_nvfp4_gemv_lines(const void* w, const float* gs, const void* x, void* y, int rows, int k, const unsigned long long* line_bases, int world,
-                        int row0, size_t line_stride, const unsigned int* line_seq, cn_stream_t stream);
+                        int row0, size_t line_stride, const unsigned int* epoch, int tag, int buf, int flip, cn_stream_t stream);
 int cn_nvfp4_gemv_gu_lines(const void* wg, const void* wu, const float* gs_g, const float* gs_u, const void* x, void* h, int inter, int k,
                            float limit, const unsigned long long* line_bases, int world, int row0, size_t line_stride,
-                           const unsigned int* line_seq, cn_stream_t stream);
-int cn_tp_recv_lines(void* base, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off, size_t flag_off, cn_stream_t stream);
+                           const unsigned int* epoch, int tag, int buf, int flip, cn_stream_t stream);
+int cn_tp_recv_lines(void* base, int rank, int world, size_t data_off, size_t slice_bytes, size_t line_off, const void* epoch, int tag,
+                     int buf, int flip, cn_stream_t stream);
 
 #ifdef __cplusplus
 }
