@@ -50,6 +50,18 @@ def gather_rows(part, full, m, world, group=None):
         full[:m].copy_(tmp.permute(1, 0, 2).reshape(m, -1))
 
 
+def line_buffer(epoch, occurrence, per_step):
+    """Which of a vector's two line buffers the `occurrence`-th exchange of the vector in step `epoch` uses, as the kernels
+    compute it: buf ^ (flip & epoch & 1) with buf = occurrence & 1 and flip = per_step & 1. Consecutive exchanges of a
+    vector alternate, also from the last one of a step to the first of the next."""
+    return (occurrence & 1) ^ ((per_step & 1) & epoch & 1)
+
+
+def line_number(epoch, tag):
+    """The number the lines of exchange `tag` (1..4095) of step `epoch` carry."""
+    return (epoch * 4096 + tag) & 0xFFFFFFFF
+
+
 class PeerExchange:
     """One buffer per rank, visible to every peer over NVLink (CUDA IPC), holding the replicated activation vectors
     of the tensor-parallel stack, plus the arrival counters of each exchange point (`cn_tp_allgather`)."""
