@@ -46,7 +46,9 @@ static_assert(ZERO2_OFF + 16 <= LUT_OFF && TBAR_OFF + RED_DEPTH * 8 <= ZERO_OFF,
 constexpr int ROWS = 16;
 
 // ---- two-CTA cluster helpers (K range of a tile shared between the CTAs of a pair)
-constexpr int XCH_OFF = 256, XCH_SLOTS = 8, XBAR_OFF = XCH_OFF + XCH_SLOTS * 64;  // f32 [8][16] sums from the peer + a barrier per slot
+// f32 [8 slots][up to 3 senders][16] sums from the other CTAs of a cluster of two or four, then a barrier per slot
+constexpr int XCH_OFF = 256, XCH_SLOTS = 8, XBAR_OFF = XCH_OFF + XCH_SLOTS * 3 * 64;
+static_assert(XBAR_OFF + XCH_SLOTS * 8 <= ZERO2_OFF, "the cluster exchange overlaps the header");
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
 }
@@ -110,8 +112,10 @@ __device__ __forceinline__ void push_lines(const GemvParams& p, int row0, int nr
 // TX: 36-byte blocks per row and stage (32 or 16); the last chunk of a row may be shorter
 // CPS: CTAs per SM the register allocation must allow; MT: activation rows (1, 2, 4 or 8; p.m of them live)
 // KS: 1, or 2 = launched as two-CTA clusters, the CTAs of a pair sharing every tile's K range (MT = 1 only)
-template <int TX, int CPS, int MT, int KS = 1>
+// LN: tensor-parallel line output compiled in (one activation row only); without it the kernel carries none of that code
+template <int TX, int CPS, int MT, int KS = 1, bool LN = false>
 __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const GemvParams p) {
+    static_assert(!LN || MT == 1, "line output takes one activation row");
     extern __shared__ __align__(128) uint8_t smem[];
     if (threadIdx.x == 0) { CN_STAMP(0); }
     const float gs0_early = __ldg(p.gs0), gs1_early = __ldg(p.gs1);  // tensor scales: asked for first, used late
@@ -120,8 +124,8 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     constexpr int GPW = TX / 2 / NW > 0 ? TX / 2 / NW : 1;  // groups per warp and full chunk
     // KS = 2 (one activation row only): the CTAs of a cluster pair walk the same tiles, each over half of K
     static_assert(KS == 1 || MT == 1, "the K range is shared between CTAs for one activation row only");
-    const int crank = KS == 2 ? (int)(blockIdx.x & 1) : 0;
-    const int cid = KS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, ncl = KS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int crank = KS > 1 ? (int)(blockIdx.x % KS) : 0;
+    const int cid = KS > 1 ? (int)(blockIdx.x / KS) : (int)blockIdx.x, ncl = KS > 1 ? (int)(gridDim.x / KS) : (int)gridDim.x;
     const int bpr_all = p.k >> 6;
     const int bpr = bpr_all / KS, b0 = crank * bpr;  // this CTA's blocks of every row: [b0, b0 + bpr)
     const size_t row_bytes = (size_t)bpr_all * 36;
@@ -168,11 +172,11 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     // depend on the previous kernel); the consumers meet it on named barrier 2 before their first wait.
     if (warp == NW) {
         // one barrier per lane and round: S full + S empty + RD tile-sum (+ the pair's exchange slots), side by side
-        for (int i = lane; i < 2 * S + RD + (KS == 2 ? XCH_SLOTS : 0); i += 32) {
+        for (int i = lane; i < 2 * S + RD + (KS > 1 ? XCH_SLOTS : 0); i += 32) {
             if (i < S) mbar_init(&full[i], 1);
             else if (i < 2 * S) mbar_init(&empty[i - S], NW);
             else if (i < 2 * S + RD) mbar_init(&tbar[i - 2 * S], NW);
-            else mbar_init((uint64_t*)(smem + XBAR_OFF) + (i - 2 * S - RD), 1);
+            else mbar_init((uint64_t*)(smem + XBAR_OFF) + (i - 2 * S - RD), KS - 1);  // one arrival per other CTA of the cluster
         }
 #ifdef CN_M1_TRACE
         if (lane == 0) { CN_STAMP(7); }
@@ -182,7 +186,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         asm volatile("bar.arrive 2, %0;" ::"n"(NTHREADS) : "memory");
         pdl_launch_dependents();
     }
-    if (KS == 2) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+    if (KS > 1) cluster_sync_all();  // the first CTA's barriers exist before anything is sent to them
 
     if (warp == NW) {
         // ------------------------------------------------------------ weight producer warp
@@ -199,7 +203,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             for (int c = 0; c < nch; c++) {
                 const int nblk = min(TX, bpr - c * TX);
                 const uint32_t piece = (uint32_t)nblk * 36u;
-                if (!first_round && !waited_pred) {
+                if (LN && !first_round && !waited_pred) {
                     // The ring is full: a slot frees only once the consumers run, and they wait for the predecessor grid.
                     // The producer waits for it too (a dependency wait, not a spin) so that the bounded wait below
                     // times the consumers alone, however long a predecessor that waits for other GPUs takes.
@@ -227,7 +231,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             }
         }
         if (lane == 0) { CN_STAMP(6); }
-        if (KS == 2) cluster_sync_all();  // nobody leaves while the peer may still send or receive
+        if (KS > 1) cluster_sync_all();  // nobody leaves while a CTA of the cluster may still send or receive
         return;
     }
 
@@ -238,7 +242,7 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
     pdl_wait();  // the activations may come from the previous kernel of the stream
     if (threadIdx.x == 0) { CN_STAMP(1); }
     // the number of this exchange (tensor-parallel line output) from the step counter, which was advanced at the step's start
-    const unsigned int line_epoch = (MT == 1 && p.yl_world > 0) ? *(volatile const unsigned int*)p.yl_epoch : 0u;
+    const unsigned int line_epoch = LN ? *(volatile const unsigned int*)p.yl_epoch : 0u;
     const unsigned int line_seq = line_epoch * 4096u + (unsigned int)p.yl_tag, line_buf = (unsigned int)p.yl_buf ^ ((unsigned int)p.yl_flip & line_epoch & 1u);
     const int ntask = MT * bpr * 8;
     auto load_x = [&](int task) -> uint4 {
@@ -471,18 +475,18 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
             if (!mbar_wait(&tbar[rslot], rpar)) {
                 cn_dev_fail(CN_DEV_WAIT_FULL);
                 ok = false;
-            } else if (MT == 1 && KS == 2) {
-                // lane l < 16: row slot l of the tile over this CTA's half of K, the eight warps in order
+            } else if (MT == 1 && KS > 1) {
+                // lane l < 16: row slot l of the tile over this CTA's part of K, the eight warps in order
                 float v = 0.0f;
                 if (lane < 16) {
                     v = rb[lane];
                     for (int w = 1; w < NW; w++) v += rb[w * 16 + lane];
                 }
-                float* xch = (float*)(smem + XCH_OFF) + titer * 16;
+                float* xch = (float*)(smem + XCH_OFF) + titer * (KS - 1) * 16;
                 uint64_t* xb = (uint64_t*)(smem + XBAR_OFF) + titer;
-                if (crank == 1) {
-                    // hand the sums to the pair's first CTA: into its slot, then one arrival on its barrier
-                    if (lane < 16) st_peer_f32(peer_addr(xch + lane, 0), v);
+                if (crank != 0) {
+                    // hand the sums to the cluster's first CTA: into this CTA's place of the slot, then one arrival on its barrier
+                    if (lane < 16) st_peer_f32(peer_addr(xch + (crank - 1) * 16 + lane, 0), v);
                     __syncwarp();
                     if (lane == 0) arrive_peer(peer_addr(xb, 0));
                 } else {
@@ -490,7 +494,8 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                         cn_dev_fail(CN_DEV_WAIT_FULL);
                         ok = false;
                     } else {
-                        if (lane < 16) v += xch[lane];  // first half of K + second half: a fixed order
+                        if (lane < 16)
+                            for (int c = 0; c < KS - 1; c++) v += xch[c * 16 + lane];  // the parts of K in order: a fixed sum
                         const float up = __shfl_down_sync(0xffffffffu, v, 8);
                         const int row = tile * per_cta + lane;
                         const float r = gu ? act_gu(v, up, p.limit) : v;
@@ -500,10 +505,10 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
                             else
                                 ((__nv_bfloat16*)ybase)[row] = __float2bfloat16_rn(r);
                         }
-                        if (p.yl_world > 0) push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), r, lane, line_seq, line_buf);
+                        if (LN) push_lines(p, tile * per_cta, min(per_cta, p.rows - tile * per_cta), r, lane, line_seq, line_buf);
                     }
                 }
-            } else if (MT == 1 && p.yl_world > 0) {
+            } else if (LN) {
                 // one activation row with line output: every lane of the warp takes part in the shuffles
                 const int row = tile * per_cta + lane;
                 float v0 = 0.0f, v1 = 0.0f;
@@ -542,13 +547,13 @@ __global__ void __launch_bounds__(NTHREADS, CPS) nvfp4_gemv_m1_kernel(const Gemv
         }
     }
     if (threadIdx.x == 0) { CN_STAMP(4); }
-    if (KS == 2) cluster_sync_all();  // nobody leaves while the peer may still send or receive
+    if (KS > 1) cluster_sync_all();  // nobody leaves while a CTA of the cluster may still send or receive
 }
 
-template <int TX, int CPS, int MT, int KS = 1>
+template <int TX, int CPS, int MT, int KS = 1, bool LN = false>
 int launch_m1(const cudaLaunchConfig_t& cfg, const GemvParams& p) {
-    CN_ALLOW_SMEM((nvfp4_gemv_m1_kernel<TX, CPS, MT, KS>), 226 * 1024);
-    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS, MT, KS>, p));
+    CN_ALLOW_SMEM((nvfp4_gemv_m1_kernel<TX, CPS, MT, KS, LN>), 226 * 1024);
+    CN_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemv_m1_kernel<TX, CPS, MT, KS, LN>, p));
     return CN_OK;
 }
 
@@ -605,24 +610,36 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
         }
         grid = (ntiles + ((ntiles + grid - 1) / grid) - 1) / ((ntiles + grid - 1) / grid);  // the same tiles per CTA, fewer CTAs
     }
-    // When the tiles do not fill the last wave, pairs of CTAs (a cluster of two) share every tile, each over half of
-    // K, and the pair's second CTA hands its 16 sums to the first through distributed shared memory: the wave
-    // quantum drops from a tile to half a tile. Taken when that shortens the longest CTA by a tenth or more.
+    // Clusters of two or four CTAs can share every tile, each CTA over its part of K, the others handing their 16 sums to
+    // the first through distributed shared memory: the wave quantum drops from a tile to a half or a quarter, and a
+    // matrix of few, long rows (a tensor-parallel rank's share of a down projection) gets CTAs enough to stream it.
+    // Taken when it shortens the longest CTA by a tenth or more and either the machine is not filled otherwise or a CTA's
+    // share stays long enough to hide the hand-over (measured on full machines: 235 KB yes, 69 KB no).
     int ksplit = 1;
-    if (!routed && mt == 1 && tx == 32 && cps <= 3 && bpr % 8 == 0) {
-        const int slots = 148 * cps, pairs = slots / 2;
-        const int waves1 = (ntiles + slots - 1) / slots, waves2 = (ntiles + pairs - 1) / pairs;  // tiles / CTA, half tiles / CTA
-        // worth it only when a CTA's share is long enough to hide the pair's hand-over (measured: 235 KB yes, 69 KB no)
-        const long long share = (long long)waves2 * ROWS * bpr * 36 / 2;
-        if (waves2 <= XCH_SLOTS && 10 * waves2 <= 18 * waves1 && share >= 160 * 1024) {
-            ksplit = 2;
-            grid = 2 * (ntiles < pairs ? ntiles : pairs);
-        }
-    }
     size_t xbytes_l = xbytes;
-    if (ksplit == 2) {
-        nch = (bpr / 2 + tx - 1) / tx;
-        xbytes_l = (size_t)(bpr / 2) * XB + (size_t)((bpr / 2 + 3) & ~3) * 4;
+    if (!routed && mt == 1 && tx == 32) {
+        double best = (double)((ntiles + 148 * cps - 1) / (148 * cps));  // tiles per CTA without a split
+        int best_cps = cps;
+        for (int ks = 2; ks <= 4; ks *= 2) {
+            if (bpr % (4 * ks) != 0) continue;  // every part starts on a 16-byte boundary of the row
+            const int bk = bpr / ks, nchk = (bk + tx - 1) / tx;
+            const long long xk = (long long)bk * XB + (long long)((bk + 3) & ~3) * 4;
+            int ck = 2;
+            if ((227 * 1024) / 3 - 1024 - ((long long)RED_OFF + (long long)((3 + nchk) / nchk + 1) * NW * 64 + xk) >= 3 * (long long)stage_bytes) ck = 3;
+            const int clusters = 148 * ck / ks;
+            const int waves = (ntiles + clusters - 1) / clusters;
+            const long long share = (long long)waves * ROWS * bk * 36;
+            const bool underfilled = (long long)ntiles * ks <= 148LL * ck;
+            if (waves > XCH_SLOTS || share < 32 * 1024 || !(underfilled || share >= 160 * 1024)) continue;
+            const double t = (double)waves / ks;
+            if (t <= 0.9 * best) best = t, ksplit = ks, best_cps = ck, xbytes_l = (size_t)xk;
+        }
+        if (ksplit > 1) {
+            cps = best_cps;
+            const int clusters = 148 * cps / ksplit;
+            grid = ksplit * (ntiles < clusters ? ntiles : clusters);
+            nch = (bpr / ksplit + tx - 1) / tx;
+        }
     }
     auto fixed2 = [&](int st) { return (long long)RED_OFF + (long long)((st + nch) / nch + 1) * NW * mt * 64 + (long long)xbytes_l; };
     int fit = MAX_STAGES;  // ring depth that fits beside the fixed part
@@ -676,14 +693,23 @@ int cn_gemv_m1_launch(const GemvCall& a, cudaStream_t stream, const char* who) {
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    if (ksplit == 2) {
+    if (ksplit > 1) {
         at[1].id = cudaLaunchAttributeClusterDimension;
-        at[1].val.clusterDim.x = 2, at[1].val.clusterDim.y = 1, at[1].val.clusterDim.z = 1;
+        at[1].val.clusterDim.x = (unsigned)ksplit, at[1].val.clusterDim.y = 1, at[1].val.clusterDim.z = 1;
         cfg.numAttrs = 2;
+        if (p.yl_world > 0) {
+            if (ksplit == 2) return cps == 2 ? launch_m1<32, 2, 1, 2, true>(cfg, p) : launch_m1<32, 3, 1, 2, true>(cfg, p);
+            return cps == 2 ? launch_m1<32, 2, 1, 4, true>(cfg, p) : launch_m1<32, 3, 1, 4, true>(cfg, p);
+        }
+        if (ksplit == 2) return cps == 2 ? launch_m1<32, 2, 1, 2>(cfg, p) : launch_m1<32, 3, 1, 2>(cfg, p);
+        return cps == 2 ? launch_m1<32, 2, 1, 4>(cfg, p) : launch_m1<32, 3, 1, 4>(cfg, p);
     }
-    if (ksplit == 2) {
-        if (cps == 2) return launch_m1<32, 2, 1, 2>(cfg, p);
-        return launch_m1<32, 3, 1, 2>(cfg, p);
+    if (p.yl_world > 0) {
+        // line output: the shapes of a tensor-parallel rank (32 blocks per stage)
+        if (tx == 32 && cps == 2) return launch_m1<32, 2, 1, 1, true>(cfg, p);
+        if (tx == 32 && cps == 3) return launch_m1<32, 3, 1, 1, true>(cfg, p);
+        if (tx == 32 && cps == 4) return launch_m1<32, 4, 1, 1, true>(cfg, p);
+        CN_FAIL(CN_ERR_SHAPE, "%s: line output needs k >= 2048 (k = %d)", who, k);
     }
 #define CN_M1_CASE(TXV, CPSV, MTV) \
     if (tx == TXV && cps == CPSV && mt == MTV) return launch_m1<TXV, CPSV, MTV>(cfg, p);

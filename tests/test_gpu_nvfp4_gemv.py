@@ -164,11 +164,12 @@ def test_errors_are_named_not_fatal():
         ops.Fp4.from_host(np.zeros(10, np.uint8), 64, 256, 1.0)
 
 
-@pytest.mark.parametrize("rows,cols,gu", [(5120, 17408, False), (6000, 17408, False), (2560, 17408, True)])
+@pytest.mark.parametrize("rows,cols,gu", [(5120, 17408, False), (6000, 17408, False), (2560, 17408, True), (640, 17408, False), (1280, 17408, False),
+                                          (896, 5120, False)])
 def test_k_shared_by_a_cta_pair_matches_the_cpu_reference(rows, cols, gu):
-    """Shapes for which the library launches two-CTA clusters (tiles that do not fill the last wave and a long K, the
-    down projection of the dense stack among them): each CTA of a pair sums half of K and the halves meet through
-    distributed shared memory in a fixed order."""
+    """Shapes for which the library launches clusters of two or four CTAs (tiles that do not fill the last wave and a long
+    K, the down projection of the dense stack among them, and the few long rows of a tensor-parallel rank's share of it):
+    each CTA of a cluster sums its part of K and the parts meet through distributed shared memory in a fixed order."""
     rng, w, fw = make(rows, cols, rows + cols)
     xb, xf = synth.activations(1, cols, rng)
     if gu:
