@@ -689,7 +689,11 @@ def exchange_check(rank, world, local):
                 b.graph.replay()
                 torch.cuda.synchronize()
                 for name in ("q", "o", "h", "y"):
-                    if not torch.equal(getattr(a, name).view(torch.int16), getattr(b, name).view(torch.int16)):
+                    va, vb = getattr(a, name), getattr(b, name)
+                    if name in a.local_only:  # not exchanged: every rank holds its own slice only
+                        lo, hi = dense.tp_rows(va.shape[1], rank, world)
+                        va, vb = va[:, lo:hi].contiguous(), vb[:, lo:hi].contiguous()
+                    if not torch.equal(va.view(torch.int16), vb.view(torch.int16)):
                         res = f"replay {it}: vector {name} differs from the all-gather path"
             if _lib.device_status() != 0:
                 res = "device status"
@@ -718,6 +722,8 @@ def main():
                     help="tensor parallel: output rows stored by the GEMV itself as 16-byte lines that carry a sequence number into the peers' memory (peer), "
                          "the same lines pushed by a separate kernel (peer-lines), data followed by a flag (peer-flags), or NCCL all-gather")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of a CUDA-graph replay")
+    ap.add_argument("--gather-q", action="store_true",
+                    help="tensor parallel: exchange the QKV output as well (by default every rank keeps its heads: attention is per head)")
     ap.add_argument("--fuse", default="none", choices=["none", "gemv", "layer", "token"],
                     help="dense, one GPU, M = 1: projections through the balanced-share kernel, one launch per projection / layer / token")
     ap.add_argument("--workload", default="dense", choices=["dense", "gemv", "moe", "mul1", "gemm", "intervals"],
@@ -752,7 +758,7 @@ def main():
         return moe_arm(args, rank, world, local)
 
     stack = dense.DenseStack(layers=args.layers, device=f"cuda:{local}", seed=0, rank=rank, world=world, group=None, max_m=args.m,
-                             exchange=args.exchange)
+                             exchange=args.exchange, gather_q=args.gather_q)
     m = args.m
     if args.fuse != "none" and world == 1 and m == 1:
         stack.fuse(args.fuse)
@@ -786,7 +792,9 @@ def main():
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic",
                 "config": {"workload": f"nvfp4 dense decode stack 27B-shaped (hidden 5120, qkv 7168, inter 17408, {stack.layers} layers), M={m}",
-                           "activations": "bf16 in/out, f32 accumulate", "parallelism": (f"tp{world} row split + " + ("peer-memory exchange" if stack.peer is not None else "NCCL all-gather")) if world > 1 else "none",
+                           "activations": "bf16 in/out, f32 accumulate", "parallelism": (f"tp{world} row split + " + ("exchange over peer memory fused into the GEMV" if stack.peer is not None and stack.peer.fused
+                                                                        else "peer-memory exchange" if stack.peer is not None else "NCCL all-gather")
+                                           + (" after o, gate/up and down (QKV heads stay on their rank)" if stack.local_only else " after every projection")) if world > 1 else "none",
                            "l2": "inputs larger than L2: %.2f GB of weights streamed per step" % (bytes_step / 1e9),
                            "launch": ("CUDA graph replay" if use_graph else "eager launches") + (f", projections fused per {args.fuse}" if fused else ""),
                            "tokens_per_s": m / (ms_step * 1e-3)},

@@ -71,6 +71,7 @@ _SIGS = {
     "cn_peer_close": [_vp, C.c_size_t],
     "cn_tp_allgather": [C.POINTER(C.c_void_p), _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, _vp],
     "cn_tp_allgather_ll": [C.POINTER(C.c_void_p), _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, _vp],
+    "cn_smem_book": [_vp, _i, _i, _i],
     "cn_tp_epoch_advance": [_vp, _vp],
     "cn_tp_recv_lines": [_vp, _i, _i, C.c_size_t, C.c_size_t, C.c_size_t, _vp, _i, _i, _i, _vp],
     "cn_nvfp4_gemv_lines": [_vp, _vp, _vp, _vp, _i, _i, C.POINTER(C.c_ulonglong), _i, _i, C.c_size_t, _vp, _i, _i, _i, _vp],

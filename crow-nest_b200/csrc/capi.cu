@@ -19,17 +19,26 @@ void cn_set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
-cudaError_t cn_allow_smem(const void* kernel, int bytes) {
+// The book behind cn_allow_smem: the largest dynamic shared-memory size already allowed per (kernel, device). Returns 1
+// when `bytes` is not covered yet (and records it when commit is set), 0 when it is. No CUDA call: testable without a GPU.
+extern "C" int cn_smem_book(const void* kernel, int device, int bytes, int commit) {
     static std::mutex mu;
-    static std::map<std::pair<const void*, int>, int> done;  // (kernel, device) -> largest size allowed so far
+    static std::map<std::pair<const void*, int>, int> done;
+    std::lock_guard<std::mutex> lock(mu);
+    int& have = done[std::make_pair(kernel, device)];
+    if (have >= bytes) return 0;
+    if (commit) have = bytes;
+    return 1;
+}
+
+cudaError_t cn_allow_smem(const void* kernel, int bytes) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    std::lock_guard<std::mutex> lock(mu);
-    int& have = done[std::make_pair(kernel, dev)];
-    if (have >= bytes) return cudaSuccess;
+    if (!cn_smem_book(kernel, dev, bytes, 0)) return cudaSuccess;
+    // the attribute belongs to the device that is current: every GPU of a process gets its own call
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess) have = bytes;
+    if (e == cudaSuccess) cn_smem_book(kernel, dev, bytes, 1);
     return e;
 }
 

@@ -153,11 +153,15 @@ class PeerExchange:
 
 class DenseStack:
     def __init__(self, cfg=None, layers=None, device="cuda", seed=0, rank=0, world=1, group=None, max_m=1, dtype=torch.bfloat16,
-                 exchange="nccl"):
+                 exchange="nccl", gather_q=False):
         cfg = dict(cfg or synth.DENSE_27B)
         self.hidden, self.qkv, self.inter = cfg["hidden"], cfg["qkv"], cfg["inter"]
         self.layers = layers if layers is not None else cfg["layers"]
         self.rank, self.world, self.group, self.device, self.dtype = rank, world, group, device, dtype
+        # Tensor parallel: the fused QKV output is split by heads and attention runs per head, so every rank keeps its own
+        # slice and nothing is exchanged after that projection; o, gate/up and down outputs are needed whole by what follows
+        # them. gather_q = True exchanges q as well (every projection followed by an all-gather).
+        self.local_only = set() if gather_q or world == 1 else {"q"}
         for n in (self.qkv, self.hidden, self.inter):
             if n % world:
                 raise CrownestError(f"tensor parallel: {n} output rows do not split over {world} ranks")
@@ -190,10 +194,13 @@ class DenseStack:
                 try:
                     self.peer = PeerExchange(sizes, rank, world, device, group, lines={"peer": "fused", "peer-lines": True, "peer-flags": False}[exchange])  # raises on every rank or on none
                     self.q, self.o, self.h, self.y = (self.peer.vector(n, r) for n, r in sizes.items())
-                    self.peer.per_step = {n: self.layers for n in sizes}  # every vector is exchanged once per layer
+                    self.peer.per_step = {n: self.layers for n in sizes if n not in self.local_only}  # once per layer each
                 except CrownestError as e:  # no peer access between these GPUs: NCCL all-gather instead
                     self.peer, self.peer_error = None, str(e)
+        # this library's kernels per step: four GEMVs per layer, plus one exchange kernel per exchanged vector and the step counter
         self.launches_per_step = 4 * self.layers
+        if self.peer is not None:
+            self.launches_per_step += (4 - len(self.local_only)) * self.layers + (1 if self.peer.fused else 0)
         self.graph = None
         self.chains = None
 
@@ -240,6 +247,10 @@ class DenseStack:
         gather_rows(self.part[name][:m], full, m, self.world, self.group)
 
     def _proj(self, w, x, name, full, m, gu=None):
+        if name in self.local_only:
+            lo, hi = tp_rows(full.shape[1], self.rank, self.world)
+            ops.launch_gemv(w, x, full[:m, lo:hi])  # the rank's slice stays where it is: its consumer is local
+            return
         if self.peer is not None:
             lo, hi = tp_rows(full.shape[1], self.rank, self.world)
             out = full[:, lo:hi]  # this rank's slice of the replicated vector, in place

@@ -58,6 +58,10 @@ const char* cn_version(void);
  * iteration budget records a code here and the kernel returns. Reads and clears the word
  * (synchronises the device). 0 = no error. */
 int cn_device_status(int* code_out);
+/* Bookkeeping of the per-device kernel attribute (large dynamic shared memory) that every launch path consults: 1 when
+ * (kernel, device) has not been allowed `bytes` yet (recorded when commit != 0), else 0. Makes no CUDA call; exported so
+ * that the per-device rule can be checked without a GPU. */
+int cn_smem_book(const void* kernel, int device, int bytes, int commit);
 
 /* ---------------------------------------------------------------- NVFP4 GEMV, M = 1..8
  * y[m][r] = sum_k W[r][k] * x[m][k], m < M.

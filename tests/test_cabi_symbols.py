@@ -29,3 +29,18 @@ def test_error_string_and_version_need_no_gpu():
     # a refused shape is reported before any CUDA call
     assert L.cn_nvfp4_gemv(None, None, None, None, 4, 100, 1, 4, 1, None) == 1
     assert b"multiple of 256" in L.cn_last_error_string()
+
+
+def test_shared_memory_attribute_is_booked_per_kernel_and_device():
+    """The large dynamic shared-memory attribute belongs to a (kernel, device) pair: a process that launches on a second
+    GPU must set it there again, and a larger request on the same GPU too. cn_smem_book is the book every launch consults."""
+    L = _lib.lib()
+    k1, k2 = ctypes.c_void_p(0x1000), ctypes.c_void_p(0x2000)
+    assert L.cn_smem_book(k1, 0, 100 * 1024, 0) == 1  # asked without committing: still to do
+    assert L.cn_smem_book(k1, 0, 100 * 1024, 1) == 1
+    assert L.cn_smem_book(k1, 0, 100 * 1024, 1) == 0  # covered now
+    assert L.cn_smem_book(k1, 0, 64 * 1024, 1) == 0   # a smaller size is covered by the larger
+    assert L.cn_smem_book(k1, 0, 200 * 1024, 1) == 1  # a larger one is not
+    assert L.cn_smem_book(k1, 1, 100 * 1024, 1) == 1  # another device: its own call
+    assert L.cn_smem_book(k2, 0, 100 * 1024, 1) == 1  # another kernel: its own call
+    assert L.cn_smem_book(k1, 1, 100 * 1024, 1) == 0

@@ -27,8 +27,10 @@ def _worker(rank, world, port, out, protocol):
     from crownest_b200 import _lib, dense
     res = "ok"
     try:
-        a = dense.DenseStack(layers=3, device=f"cuda:{rank}", seed=5, rank=rank, world=world, exchange="nccl")
-        b = dense.DenseStack(layers=3, device=f"cuda:{rank}", seed=5, rank=rank, world=world, exchange=protocol)
+        # the fused form once with the QKV output exchanged too (four exchanges per layer), else with q kept local
+        gq = protocol == "peer-lines"
+        a = dense.DenseStack(layers=3, device=f"cuda:{rank}", seed=5, rank=rank, world=world, exchange="nccl", gather_q=gq)
+        b = dense.DenseStack(layers=3, device=f"cuda:{rank}", seed=5, rank=rank, world=world, exchange=protocol, gather_q=gq)
         assert b.peer is not None
         x = torch.randn((1, a.hidden), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
         a.x.copy_(x), b.x.copy_(x)
@@ -38,7 +40,11 @@ def _worker(rank, world, port, out, protocol):
             b.graph.replay()
             torch.cuda.synchronize()
             for name in ("q", "o", "h", "y"):
-                if not torch.equal(getattr(a, name).view(torch.int16), getattr(b, name).view(torch.int16)):
+                va, vb = getattr(a, name), getattr(b, name)
+                if name in a.local_only:  # not exchanged: every rank holds its own slice only
+                    lo, hi = dense.tp_rows(va.shape[1], rank, world)
+                    va, vb = va[:, lo:hi].contiguous(), vb[:, lo:hi].contiguous()
+                if not torch.equal(va.view(torch.int16), vb.view(torch.int16)):
                     res = f"replay {it}: vector {name} differs from the all-gather path"
         if not torch.equal(ya.view(torch.int16), b.y.view(torch.int16)):
             res = "output differs"
