@@ -695,6 +695,7 @@ def exchange_check(rank, world, local):
                         va, vb = va[:, lo:hi].contiguous(), vb[:, lo:hi].contiguous()
                     if not torch.equal(va.view(torch.int16), vb.view(torch.int16)):
                         res = f"replay {it}: vector {name} differs from the all-gather path"
+                dist.barrier()  # nobody starts the next replay (and overwrites its slices in the peers' copies) before all have looked
             if _lib.device_status() != 0:
                 res = "device status"
     except Exception as e:  # noqa: BLE001 - reported in the line

@@ -73,8 +73,8 @@ __global__ void __launch_bounds__(512) tp_allgather_kernel(PeerPtrs peers, int r
         const size_t n16 = slice_bytes >> 4;
         for (size_t i = gt; i < n16; i += gsz) dst[i] = src[i];
         // Every thread makes its own stores visible system-wide before the barrier. Leaving that to the first thread's release
-        // alone (barrier, then one st.release.sys) was measured 15 % faster per step and failed the bit comparison with the
-        // all-gather once in a handful of runs: the peer saw the flag before the last rows.
+        // alone (barrier, then one st.release.sys) was measured 15 % faster per step, but rests on that release covering the
+        // other threads' stores to another GPU's memory, which was not confirmed beyond a few passing runs.
         __threadfence_system();
         CN_TP_STAMP(2);
         asm volatile("bar.sync %0, %1;" ::"r"(gi + 1), "r"(gsz) : "memory");

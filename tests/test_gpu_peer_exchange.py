@@ -46,6 +46,9 @@ def _worker(rank, world, port, out, protocol):
                     va, vb = va[:, lo:hi].contiguous(), vb[:, lo:hi].contiguous()
                 if not torch.equal(va.view(torch.int16), vb.view(torch.int16)):
                     res = f"replay {it}: vector {name} differs from the all-gather path"
+            # a rank's copy of a peer's slice lives until that peer's next exchange of the vector: nobody starts the next
+            # replay before everybody has looked at this one
+            dist.barrier()
         if not torch.equal(ya.view(torch.int16), b.y.view(torch.int16)):
             res = "output differs"
         if _lib.device_status() != 0:
