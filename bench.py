@@ -483,7 +483,8 @@ def intervals_arm(args, rank=0, world=1, local=0):
         group = dist.group.WORLD
     layers = max(3, min(args.layers, 8))
     st = dense.DenseStack(layers=layers, seed=0, device=f"cuda:{local}", rank=rank, world=world, group=group,
-                          exchange=args.exchange if args.exchange != "nccl" else "peer")
+                          exchange=args.exchange if args.exchange != "nccl" else "peer",
+                          gather_q=True)  # all four vectors exchanged: one exchange kernel per projection in the tables
     if world > 1 and st.peer is None:
         raise SystemExit("intervals: the peer-memory exchange is not available between these GPUs")
     st.x.copy_(torch.randn((1, st.hidden), device=f"cuda:{local}").to(torch.bfloat16))
