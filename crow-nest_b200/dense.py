@@ -62,6 +62,29 @@ def line_number(epoch, tag):
     return (epoch * 4096 + tag) & 0xFFFFFFFF
 
 
+def pack_lines(rows_bf16, number):
+    """The 16-byte lines the GEMV's epilogue stores for output rows (uint16 bf16 bits, a multiple of four of them), as
+    uint32 [lines][4] = {rows 0-1, number, rows 2-3, number}: the host twin of the kernel's packing, for tests."""
+    import numpy as np
+    r = np.asarray(rows_bf16, dtype=np.uint16).reshape(-1, 4).astype(np.uint32)
+    out = np.empty((r.shape[0], 4), dtype=np.uint32)
+    out[:, 0] = r[:, 0] | (r[:, 1] << 16)
+    out[:, 2] = r[:, 2] | (r[:, 3] << 16)
+    out[:, 1] = out[:, 3] = np.uint32(number)
+    return out
+
+
+def unpack_lines(lines, number):
+    """What the receiver does with a slice's lines: None while a half of any line does not carry `number` yet, else the
+    rows as uint16 bf16 bits."""
+    import numpy as np
+    lines = np.asarray(lines, dtype=np.uint32).reshape(-1, 4)
+    if not (np.all(lines[:, 1] == np.uint32(number)) and np.all(lines[:, 3] == np.uint32(number))):
+        return None
+    w = np.stack([lines[:, 0], lines[:, 2]], axis=1).reshape(-1)
+    return np.stack([w & 0xFFFF, w >> 16], axis=1).reshape(-1).astype(np.uint16)
+
+
 class PeerExchange:
     """One buffer per rank, visible to every peer over NVLink (CUDA IPC), holding the replicated activation vectors
     of the tensor-parallel stack, plus the arrival counters of each exchange point (`cn_tp_allgather`)."""

@@ -1,6 +1,7 @@
 """The multi-rank host logic on CPU: two gloo ranks. Tensor parallel: row ranges + all-gather give the
 one-rank result bit for bit. Expert parallel: every expert has one owner, and the all-to-all dispatch and return
-with the device's placement rule reproduce the one-rank layer output bit for bit."""
+with the device's placement rule reproduce the one-rank layer output bit for bit. The tensor-parallel line exchange:
+numbering, buffer choice and acceptance rule of the kernels, restated on the host."""
 import os
 import socket
 import sys
@@ -109,7 +110,61 @@ def _ep_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_tp_worker, _ep_worker])
+def _lines_worker(rank, world, port, out):
+    """The tensor-parallel line exchange on the host: every rank's slice of a vector travels as 16-byte lines that carry
+    the exchange number into the buffer the kernels would pick; the receiver accepts a slice only when every half line
+    carries the number it expects. Over several steps, with a vector exchanged an odd and an even number of times per
+    step, the gathered vector equals the all-gather, a buffer still holding the previous exchange is never accepted, and
+    a peer that is one exchange ahead writes into the other buffer."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from crownest_b200 import dense
+    n = 64
+    rng = np.random.default_rng(100 + rank)
+    res = "ok"
+    for per_step in (3, 4):
+        bufs = [[np.zeros((world, n // world // 4, 4), np.uint32) for _ in range(2)] for _ in range(world)]  # [rank][buffer][source]
+        tag, last_buf = 0, None
+        for epoch in range(1, 4):
+            tag = 0
+            for occ in range(per_step):
+                tag += 1
+                number, buf = dense.line_number(epoch, tag), dense.line_buffer(epoch, occ, per_step)
+                if buf == last_buf:
+                    res = "two consecutive exchanges in one buffer"
+                last_buf = buf
+                mine = rng.integers(0, 1 << 16, n // world, dtype=np.uint16)
+                lo, hi = dense.tp_rows(n, rank, world)
+                # before the peers' lines arrive the buffer holds an older exchange (or zeros): never accepted
+                stale = bufs[rank][buf][(rank + 1) % world]
+                if dense.unpack_lines(stale, number) is not None:
+                    res = "a stale buffer was accepted"
+                lines = torch.from_numpy(dense.pack_lines(mine, number).astype(np.int64))
+                everyone = [torch.zeros_like(lines) for _ in range(world)]
+                dist.all_gather(everyone, lines)  # stands in for the stores into the peers' line buffers
+                full = np.zeros(n, np.uint16)
+                for src in range(world):
+                    bufs[rank][buf][src] = everyone[src].numpy().astype(np.uint32)
+                    got = mine if src == rank else dense.unpack_lines(bufs[rank][buf][src], number)
+                    if got is None:
+                        res = "a complete slice was refused"
+                        got = np.zeros(n // world, np.uint16)
+                    a, b = dense.tp_rows(n, src, world)
+                    full[a:b] = got
+                ref = [torch.zeros(n // world, dtype=torch.int32) for _ in range(world)]
+                dist.all_gather(ref, torch.from_numpy(mine.astype(np.int32)))
+                if not np.array_equal(full, torch.cat(ref).numpy().astype(np.uint16)):
+                    res = f"gathered vector differs (per step {per_step}, step {epoch}, exchange {occ})"
+                # a half-written line (the second half still from two exchanges ago) is not a line yet
+                torn = bufs[rank][buf][(rank + 1) % world].copy()
+                torn[0, 3] = dense.line_number(epoch - 1, tag) if epoch > 1 else 0
+                if dense.unpack_lines(torn, number) is not None:
+                    res = "a torn line was accepted"
+    out.put((rank, res))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_tp_worker, _ep_worker, _lines_worker])
 def test_two_gloo_ranks(worker):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
