@@ -11,8 +11,11 @@
 // With more than one activation row the C columns are packed (four activation rows x the two sub-blocks
 // of a pair: 8 MMAs per group for up to four rows, 16 for eight); row i of an m-row call is summed in
 // exactly the order of a one-row call.
-// When the tiles do not fill the last wave and a CTA's share is long enough (the down projection),
-// the launch is made of two-CTA clusters whose CTAs take half of K each (see the helpers below).
+// When the tiles do not fill the last wave and a CTA's share is long enough (the down projection), or the
+// tiles are too few to fill the machine (a tensor-parallel rank's share of it), the launch is made of
+// clusters of two or four CTAs that take a part of K each (see the helpers below).
+// The LN variant (one activation row) also stores the output rows as 16-byte lines into the line buffers of
+// the other GPUs of a tensor-parallel group: the exchange that follows the projection starts in its epilogue.
 //
 // Inner loop. mma.sync.m16n8k16 (f16 x f16 -> f32) takes the f16x2 registers that
 // cvt.rn.f16x2.e2m1x2 makes: A = 16 weight rows x 16 codes, B = the matching activations. The order

@@ -17,6 +17,12 @@
 // arrived at a later exchange.
 // Peer stores are plain st.global to the peer's address (no multicast, no bulk copy); the wait is bounded
 // (about a second) and reports through the device status word.
+//
+// Two further forms carry the sequence number inside the data instead of behind it: 16-byte lines {word, number,
+// word, number} through two line buffers per vector, pushed by a kernel of this file (tp_allgather_ll_kernel) or by
+// the epilogue of the GEMV that produces the slice (nvfp4_gemv_m1.cu), in which case only the receiving half runs
+// here (tp_recv_lines_kernel). A line is valid when both halves carry the expected number, so nothing waits for
+// a store to be acknowledged and an exchange costs one trip over NVLink.
 #include <string.h>
 
 #include "common.cuh"
